@@ -1,0 +1,318 @@
+#!/usr/bin/env python
+"""Benchmark of the gpt-oss-shaped MoE layer (tokens/s) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2] [--impl reference]
+
+A step is one pass of the MoE layer over one batch of seeded synthetic hidden states.
+Default workload at one GPU is the batched-decode configuration (T=64 tokens, Zipf-skewed
+routing, gpt-oss-20b shapes); batches rotate and the 424 MB of expert weights exceed the
+126 MB L2, so every step streams its weights from HBM.
+
+One JSON line is printed by rank 0:
+  value     tokens/s with inputs resident in HBM (CUDA events on the launching stream)
+  e2e       tokens/s through the host-buffer C-ABI call (pinned host in/out, copies timed)
+  roofline  achieved HBM GB/s of the dominant kernel (gate_up expert product) = its
+            algorithmic bytes / its mean launch duration, against the measured copy peak
+  cpu_baseline  the CPU oracle on a bounded sample of the same workload, on the host cores
+`--impl reference` times the CPU oracle alone (the nominal reference engine has no
+implementation of this path; the oracle is its stand-in on the host cores).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+from neonengine_b200 import synth  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+
+WORKLOADS = {
+    # name: (T, n_experts, zipf, description)
+    "cfg0": (1, 32, False, "gpt-oss-20b MoE layer, decode T=1"),
+    "cfg1": (64, 32, True, "gpt-oss-20b MoE layer, batched decode T=64, Zipf(1.1) router bias"),
+    "cfg2": (4096, 32, False, "gpt-oss-20b MoE layer, prefill T=4096, uniform routing"),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": FALLBACK_HBM_GBS}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, device_index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+        self.period = period_s
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwPowerBrakeSlowdown: "hw_power_brake",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_batches(T, W, zipf, n_batches, base_stream=0):
+    lb = synth.zipf_logit_bias(W.shape.n_experts) if zipf else None
+    return [synth.make_hidden(T, W, 0, logit_bias=lb, stream=base_stream + i) for i in range(n_batches)], lb
+
+
+def cpu_steps(W, batches, lb, seconds_budget, max_tokens_per_step=None):
+    """Times the CPU oracle on whole batches (or their first max_tokens_per_step tokens)."""
+    import oracle
+    oracle.lib()
+    done_tokens, t_total, steps = 0, 0.0, 0
+    while t_total < seconds_budget and steps < 64:
+        hid = batches[steps % len(batches)]
+        if max_tokens_per_step:
+            hid = hid[:max_tokens_per_step]
+        t0 = time.perf_counter()
+        oracle.moe_forward(hid, W, logit_bias=lb)
+        t_total += time.perf_counter() - t0
+        done_tokens += hid.shape[0]
+        steps += 1
+    return done_tokens / t_total, steps, oracle.n_threads()
+
+
+def run_reference(args, rank):
+    """CPU arm: the oracle on the host cores, same workload, bounded sample per step."""
+    if rank != 0:
+        return
+    T, E, zipf, desc = WORKLOADS[args.workload]
+    shape = synth.MoeShape(n_experts=E)
+    W = synth.make_weights(shape, 0)
+    sample_T = min(T, 64)
+    batches, lb = make_batches(sample_T, W, zipf, 4)
+    import oracle
+    oracle.lib()
+    for i in range(min(args.warmup, 1)):
+        oracle.moe_forward(batches[0], W, logit_bias=lb)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        oracle.moe_forward(batches[i % len(batches)], W, logit_bias=lb)
+    dt = time.perf_counter() - t0
+    tps = args.steps * sample_T / dt
+    cores = oracle.n_threads()
+    line = {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": args.workload, "description": desc, "tokens_per_step": sample_T},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                             "sample": f"{args.steps} steps of {sample_T} tokens (CPU oracle, OpenMP, fp64 accumulate)"},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload is None:
+        args.workload = "cfg1"
+    if args.impl == "reference":
+        if args.steps > 64:
+            args.steps = 8
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from neonengine_b200.moe_layer_system import MoeLayerSystem
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU: the MoE layer has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    T, E, zipf, desc = WORKLOADS[args.workload]
+    shape = synth.MoeShape(n_experts=E)
+    W = synth.make_weights(shape, 0)
+    n_batches = 8 if T <= 64 else 2
+    batches, lb = make_batches(T, W, zipf, n_batches, base_stream=100 * rank)
+    layer = MoeLayerSystem(shape, W, max_tokens=T, device=local_rank)
+    dev = torch.device("cuda", local_rank)
+    d_batches = [torch.from_numpy(b.view(np.int16)).to(dev) for b in batches]
+    d_lb = None if lb is None else torch.from_numpy(lb).to(dev)
+    d_out = torch.empty((T, shape.hidden), dtype=torch.float32, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for i in range(steps):
+            fn(i)
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def step_device(i):
+        layer.run(d_batches[i % n_batches], logit_bias=d_lb, out=d_out)
+
+    # pinned host buffers for the end-to-end arm
+    h_in = [torch.from_numpy(b.view(np.int16)).pin_memory() for b in batches]
+    h_out = torch.empty((T, shape.hidden), dtype=torch.float32).pin_memory()
+    h_lb = None if lb is None else torch.from_numpy(lb).pin_memory()
+
+    def step_host(i):
+        layer.run_host_ptr(h_in[i % n_batches].data_ptr(), T, None if h_lb is None else h_lb.data_ptr(),
+                           h_out.data_ptr())
+
+    with ClockSampler(local_rank) as clocks:
+        for i in range(max(args.warmup, 3)):
+            step_device(i)
+        l0 = layer.launch_count
+        ms = timed(step_device, args.steps)
+        launches = layer.launch_count - l0
+        # per-kernel durations over the same steps (CUDA events recorded inside the library)
+        layer.profile(True)
+        prof_steps = min(args.steps, 4000)
+        timed(step_device, prof_steps)
+        stage_ms, n_prof = layer.read_profile()
+        layer.profile(False)
+        # end to end through host buffers
+        e2e_steps = max(3, min(args.steps, 500))
+        for i in range(3):
+            step_host(i)
+        t0 = time.perf_counter()
+        barrier()
+        for i in range(e2e_steps):
+            step_host(i)
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([e2e_s], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+    assert layer.status() == 0
+
+    tokens_per_step = T * world
+    value = tokens_per_step * args.steps / (ms * 1e-3)
+    e2e_value = tokens_per_step * e2e_steps / e2e_s
+
+    # roofline of the dominant kernel: the gate_up expert product streams, per touched
+    # expert, its nibbles + scales + bias once; plus the hidden rows in and the activation out
+    touched = []
+    for b in d_batches:
+        layer.run(b, logit_bias=d_lb, out=d_out)
+        touched.append(int((layer.read_dispatch()[0] > 0).sum()))
+    mean_touched = sum(touched) / len(touched)
+    H, I = shape.hidden, shape.inter
+    gu_expert_bytes = 2 * I * H // 2 + 2 * I * H // 32 + 2 * I * 2
+    gu_bytes = mean_touched * gu_expert_bytes + T * H * 2 + T * shape.top_k * I * 4
+    layer_bytes = mean_touched * shape.expert_bytes + shape.router_bytes + T * H * 2 + T * H * 4
+    peaks, peak_kind = measured_peaks()
+    gu_ms = stage_ms["gate_up"] / max(n_prof, 1)
+    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else None
+    roofline = {"bound": "hbm", "kernel": "expert_mma_kernel<gate_up>", "achieved": achieved,
+                "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": None if achieved is None else achieved / peaks["hbm_gbs"],
+                "traffic": None, "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gu_ms,
+                "stage_ms_per_step": {k: v / max(n_prof, 1) for k, v in stage_ms.items()},
+                "layer_bytes_per_step": layer_bytes,
+                "layer_gbs": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
+                "layer_frac_of_peak": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                "layer_frac_of_8000": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / 8000.0,
+                "experts_touched_mean": mean_touched}
+
+    line = {"metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "description": desc, "tokens_per_step_per_gpu": T,
+                       "hidden": H, "inter": I, "n_experts": E, "top_k": shape.top_k,
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "l2_policy": f"{n_batches} rotating batches; {shape.expert_bytes * E / 1e6:.0f} MB of expert "
+                                    "weights per pass exceed the 126 MB L2"},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2 + (E * 4 if lb is not None else 0),
+                    "d2h_bytes_per_step": T * H * 4, "steps": e2e_steps},
+            "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks.summary()}
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_tps, cpu_steps_done, cores = cpu_steps(W, batches, lb, seconds_budget=12.0,
+                                                   max_tokens_per_step=min(T, 64))
+        line["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                "sample": f"{cpu_steps_done} steps of {min(T, 64)} tokens of the same batches "
+                                          "(CPU oracle, OpenMP, fp64 accumulate)"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    layer.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

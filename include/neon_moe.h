@@ -1,0 +1,132 @@
+/*
+ * neon_moe.h - C ABI of libneon_moe.so: a gpt-oss-shaped mixture-of-experts layer
+ * (router + top-k + softmax, dispatch, grouped MXFP4 expert products with clamped
+ * SwiGLU and routing-weighted combine) as hand-written sm_100a CUDA kernels.
+ *
+ * Relation to the reference engine (paths inside the NeonEngine project).  The engine
+ * has no MoE operator, FFI or plugin interface to bind; its compute workloads are
+ * "system" classes that own their device buffers, record work into the caller's command
+ * stream and expose results as buffer handles.  Every entry point below names the
+ * engine convention it follows, which is what an engine-side `lve::MoeLayerSystem`
+ * (include/lve_moe_layer_system.hpp) binds:
+ *
+ *   - construction owns all device buffers .... NeonEngine/src/water_physics.cpp:23-123
+ *   - stream-ordered, non-blocking execution .. NeonEngine/src/water_physics.hpp:66
+ *                                               NeonEngine/src/raytracing_system.hpp:79
+ *   - explicit, rare host read-back ........... NeonEngine/src/water_app.cpp:601-612
+ *   - failures surface as error values/strings  NeonEngine/src/lve_buffer.hpp:22-28,
+ *     (thrown as std::runtime_error by the C++  NeonEngine/src/water_physics.cpp:617-620
+ *     wrapper, never across this ABI)
+ *
+ * Conventions (this library's own; the engine defines none):
+ *   bf16 tensors are raw 16-bit patterns.  MXFP4 blocks are uint8 [E, rows, cols/2], low
+ *   nibble = even column, code bits s|e|e|m; scales are E8M0 uint8 [E, rows, cols/32]
+ *   (value 2^(byte-127), bytes 2..254 supported).  gate_up rows interleave gate (even) and
+ *   linear (odd).  out[t] = sum_s w[t,s] * (down_s + down_bias), slots summed in order
+ *   s = 0..k-1; outputs are fp32.  Top-k ties go to the lower expert id.
+ *
+ * All functions return 0 on success or a NEON_MOE_E* code; none throws or aborts.
+ * A handle serves one stream at a time and is not thread-safe; distinct handles are
+ * independent (one per GPU for expert parallelism).
+ */
+#ifndef NEON_MOE_H
+#define NEON_MOE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NEON_MOE_OK 0
+#define NEON_MOE_EINVAL 1   /* bad argument or unsupported shape          */
+#define NEON_MOE_ECUDA 2    /* a CUDA runtime call failed                 */
+#define NEON_MOE_ESTATE 3   /* call out of order (e.g. no weights set)    */
+#define NEON_MOE_EDEVICE 4  /* a kernel reported a bounded-wait failure   */
+#define NEON_MOE_ENCCL 5    /* an NCCL call failed / NCCL not loadable    */
+
+typedef struct neon_moe_handle neon_moe_handle;
+
+/* Layer description.  Plays the part of the literal parameters the engine's systems take
+ * in their constructors (NeonEngine/src/water_physics.cpp:23-40). */
+typedef struct neon_moe_config {
+    int hidden;          /* H, multiple of 64 (2880)                              */
+    int inter;           /* I, multiple of 64 (2880)                              */
+    int n_experts;       /* E, global expert count (32 | 128), <= 256            */
+    int top_k;           /* k (4), <= 8                                           */
+    float swiglu_limit;  /* 7.0                                                   */
+    float swiglu_alpha;  /* 1.702                                                 */
+    int max_tokens;      /* largest T of one forward call on this rank            */
+    int ep_rank;         /* expert-parallel rank, 0 when ep_size == 1             */
+    int ep_size;         /* ranks sharing the experts; n_experts % ep_size == 0   */
+    int device;          /* CUDA device ordinal                                   */
+} neon_moe_config;
+
+/* Creates the layer on cfg->device and allocates its workspaces.
+ * Follows: system constructors own their buffers, NeonEngine/src/water_physics.cpp:449-603. */
+int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out);
+
+/* Copies (and re-tiles for the kernels) the weights; the caller may free its arrays
+ * afterwards.  Expert tensors hold this rank's n_experts/ep_size experts; the router is
+ * replicated.  on_device != 0: pointers are device memory on cfg->device.
+ * Follows: initial data handed to the constructor and uploaded once,
+ * NeonEngine/src/water_physics.cpp:41-123 (staging upload of particle data). */
+int neon_moe_set_weights(neon_moe_handle* h, const void* router_w_bf16, const void* router_b_bf16,
+                         const uint8_t* gate_up_blocks, const uint8_t* gate_up_scales,
+                         const void* gate_up_bias_bf16, const uint8_t* down_blocks,
+                         const uint8_t* down_scales, const void* down_bias_bf16, int on_device);
+
+/* One layer pass over T tokens, enqueued on `cuda_stream` (a cudaStream_t; NULL = default
+ * stream).  All pointers are device memory: hidden bf16 [T,H]; logit_bias fp32 [E] or
+ * NULL (added to the router logits); out fp32 [T,H]; topk_idx int32 [T,k] and topk_w
+ * fp32 [T,k] may be NULL.  Returns after enqueueing.  ep_size must be 1.
+ * Follows: RunSimulation(dt, frameInfo) recording dispatches into the caller's command
+ * buffer, NeonEngine/src/water_physics.hpp:66 and .cpp:131,165-436. */
+int neon_moe_forward(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
+                     float* out_f32, int32_t* topk_idx, float* topk_w, void* cuda_stream);
+
+/* The same pass for callers that hold HOST memory: copies hidden (and logit_bias) to the
+ * device, runs the layer, copies out (and idx/w when non-NULL) back and synchronises.
+ * Follows: the explicit host read-back the engine does for its debug buffer,
+ * NeonEngine/src/water_app.cpp:601-612. */
+int neon_moe_forward_host(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
+                          float* out_f32, int32_t* topk_idx, float* topk_w);
+
+/* Host copies of the dispatch arrays of the most recent forward on this handle
+ * (synchronises the handle's last stream): count[E_local], offset[E_local+1],
+ * perm[n] (sorted position -> entry t*k+s) and inv[n], n = *n_entries.  NULLs skipped.
+ * Follows: getters handing out a system's buffers, NeonEngine/src/water_physics.hpp:68-92. */
+int neon_moe_read_dispatch(neon_moe_handle* h, int32_t* count, int32_t* offset, int32_t* perm,
+                           int32_t* inv, int* n_entries);
+
+/* Reads (and clears) the device status word: non-zero when a kernel gave up on a bounded
+ * wait.  Synchronises the handle's last stream. */
+int neon_moe_status(neon_moe_handle* h, int* device_status_word);
+
+/* Per-stage device timing.  enable != 0 makes every following forward record CUDA events
+ * around its stages on the caller's stream; neon_moe_read_profile synchronises, adds the
+ * elapsed times of all forwards since the last read into ms[4] = {router+dispatch, gate_up,
+ * down, combine} (milliseconds), stores the number of forwards in *n_forwards and resets.
+ * At most 4096 forwards are kept between reads.
+ * Follows: the engine timing its own frames, NeonEngine/src/raytracing_app.cpp:648-656. */
+int neon_moe_profile(neon_moe_handle* h, int enable);
+int neon_moe_read_profile(neon_moe_handle* h, double* ms, int* n_forwards);
+
+/* Number of kernel launches the handle has issued since creation (for launch accounting). */
+int64_t neon_moe_launch_count(const neon_moe_handle* h);
+
+/* Text of the last error on this handle (or of the last failed create when h == NULL).
+ * Owned by the library; valid until the next call on the handle. */
+const char* neon_moe_last_error(const neon_moe_handle* h);
+
+/* Frees the layer.  Follows: RAII teardown of system-owned buffers,
+ * NeonEngine/src/lve_buffer.cpp:49-53. */
+int neon_moe_destroy(neon_moe_handle* h);
+
+/* Library version string. */
+const char* neon_moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEON_MOE_H */

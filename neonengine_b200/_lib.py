@@ -1,0 +1,60 @@
+"""ctypes binding of ``libneon_moe.so`` (the C ABI in ``include/neon_moe.h``).
+
+The library is the only compute path: if it is missing or fails to load, importing
+callers get an ImportError; nothing falls back to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(HERE, "libneon_moe.so")
+
+c_int = ctypes.c_int
+c_void_p = ctypes.c_void_p
+c_float_p = ctypes.c_void_p  # raw addresses; device or host depending on the entry point
+
+
+class NeonMoeConfig(ctypes.Structure):
+    """Mirror of ``neon_moe_config``."""
+    _fields_ = [("hidden", c_int), ("inter", c_int), ("n_experts", c_int), ("top_k", c_int),
+                ("swiglu_limit", ctypes.c_float), ("swiglu_alpha", ctypes.c_float),
+                ("max_tokens", c_int), ("ep_rank", c_int), ("ep_size", c_int), ("device", c_int)]
+
+
+# name -> (restype, argtypes); must list every symbol include/neon_moe.h declares
+SIGNATURES = {
+    "neon_moe_create": (c_int, [ctypes.POINTER(NeonMoeConfig), ctypes.POINTER(c_void_p)]),
+    "neon_moe_set_weights": (c_int, [c_void_p] * 9 + [c_int]),
+    "neon_moe_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "neon_moe_forward_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "neon_moe_read_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int)]),
+    "neon_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    "neon_moe_profile": (c_int, [c_void_p, c_int]),
+    "neon_moe_read_profile": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
+    "neon_moe_launch_count": (ctypes.c_int64, [c_void_p]),
+    "neon_moe_last_error": (ctypes.c_char_p, [c_void_p]),
+    "neon_moe_destroy": (c_int, [c_void_p]),
+    "neon_moe_version": (ctypes.c_char_p, []),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library and bind every entry point; raises ImportError when the
+    CUDA extension has not been built (``python -m neonengine_b200.build``)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(SO_PATH):
+        raise ImportError(f"{SO_PATH} is missing: build it with `python -m neonengine_b200.build` "
+                          "(there is no CPU fallback)")
+    lib = ctypes.CDLL(SO_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

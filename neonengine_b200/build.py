@@ -1,0 +1,43 @@
+"""In-tree build of ``libneon_moe.so`` (sm_100a only) with nvcc.
+
+``python -m neonengine_b200.build`` compiles the CUDA sources under ``csrc/`` into
+``neonengine_b200/libneon_moe.so``.  nvcc cross-compiles, so no GPU is needed to build.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+SO = os.path.join(HERE, "libneon_moe.so")
+SOURCES = ["neon_moe.cu"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--use_fast_math=false", "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]
+
+
+def _newest_source() -> float:
+    newest = 0.0
+    for root in (CSRC, os.path.join(os.path.dirname(HERE), "include")):
+        for name in os.listdir(root):
+            newest = max(newest, os.path.getmtime(os.path.join(root, name)))
+    return newest
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and os.path.exists(SO) and os.path.getmtime(SO) >= _newest_source():
+        return SO
+    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    cmd = ["nvcc", *flags, *(["-Xptxas", "-v"] if verbose else []),
+           *[os.path.join(CSRC, s) for s in SOURCES], "-o", SO, "-ldl"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode:
+        raise RuntimeError("nvcc failed: " + " ".join(cmd))
+    return SO
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose="-v" in sys.argv))

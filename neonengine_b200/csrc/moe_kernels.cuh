@@ -1,0 +1,378 @@
+// Kernels of the MoE layer: weight re-tiling, router + top-k + softmax, dispatch
+// (histogram + prefix sum + stable permutation), grouped MXFP4 expert products on
+// mma.m16n8k16 with in-register e2m1 dequantisation, SwiGLU / weighted-combine epilogues.
+#pragma once
+#include "moe_common.cuh"
+
+namespace neon {
+
+constexpr int kMaxExperts = 256;
+constexpr int kMaxTopK = 8;
+
+// ---------------------------------------------------------------------------------------
+// Re-tiling of [E, rows, K/2] nibbles + [E, rows, K/32] scales into the mma16 format.
+// gate_up != 0 maps MMA rows (g, g+8) of tile tl to matrix rows (2*(8tl+g), 2*(8tl+g)+1).
+// One thread per output uint4.  *bad_scale is set when a scale byte exceeds 128.
+// ---------------------------------------------------------------------------------------
+__global__ void repack_mma16_kernel(const uint8_t* __restrict__ blocks, const uint8_t* __restrict__ scales,
+                                    int n_experts, int rows, int K, int gate_up,
+                                    uint4* __restrict__ wq, uint32_t* __restrict__ sq, int* bad_scale) {
+    const int tiles = rows / 16, nbp = K / 64;
+    const long long total = (long long)n_experts * tiles * nbp * 32;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        int lane = (int)(i % 32);
+        long long r = i / 32;
+        int bp = (int)(r % nbp);
+        r /= nbp;
+        int tl = (int)(r % tiles);
+        int e = (int)(r / tiles);
+        int g = lane >> 2, t = lane & 3;
+        int row_lo = gate_up ? 2 * (8 * tl + g) : 16 * tl + g;
+        int row_hi = gate_up ? row_lo + 1 : row_lo + 8;
+        uint32_t words[4];
+        for (int part = 0; part < 4; ++part) {
+            int row = (part & 1) ? row_hi : row_lo;
+            int blk = 2 * bp + (part >> 1);
+            const uint8_t* src = blocks + ((size_t)e * rows + row) * (K / 2) + blk * 16 + 4 * t;
+            uint32_t c[8];
+            for (int b = 0; b < 4; ++b) {
+                c[2 * b] = src[b] & 15u;
+                c[2 * b + 1] = src[b] >> 4;
+            }
+            words[part] = pack8(c);
+        }
+        wq[i] = make_uint4(words[0], words[1], words[2], words[3]);
+        if (t == 0) {
+            uint32_t s = 0;
+            for (int part = 0; part < 4; ++part) {
+                int row = (part & 1) ? row_hi : row_lo;
+                int blk = 2 * bp + (part >> 1);
+                uint32_t byte = scales[((size_t)e * rows + row) * (K / 32) + blk];
+                if (byte > 128u) *bad_scale = 1;
+                s |= ((byte + 126u) & 255u) << (8 * part);
+            }
+            sq[(((size_t)e * tiles + tl) * nbp + bp) * 8 + g] = s;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Router: one CTA per token.  logits = x . Wr[e] + br[e] (+ logit_bias[e]), fp32, every
+// expert reduced in the same order (so equal rows give equal logits); warp 0 then picks the
+// top k (ties to the lower expert id) and the softmax over the selected logits.
+// The last CTA to finish (ticket counter) runs the dispatch when `fuse_dispatch` is set.
+// ---------------------------------------------------------------------------------------
+struct DispatchArrays {
+    int32_t* count;   // [E_local]
+    int32_t* offset;  // [E_local + 1]
+    int32_t* perm;    // [n] sorted position -> entry id
+    int32_t* inv;     // [n] entry id -> sorted position
+};
+
+__device__ __forceinline__ unsigned long long logit_key(float v, int e) {
+    v += 0.0f;  // -0 -> +0 so that equal values compare equal
+    uint32_t u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (uint32_t)(0x7fffffff - e);
+}
+
+// Stable counting sort of n entries by expert, run by one CTA of 1024 threads.
+// Entries whose expert lies outside [e_lo, e_lo + n_local) are skipped (inv = -1).
+// smem: n_local counters + 32*n_local per-warp counters.
+__device__ void dispatch_block(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
+                               DispatchArrays d, int* smem) {
+    int* base = smem;               // running write position per expert
+    int* wc = smem + n_local;       // [32][n_local]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
+    for (int e = tid; e < n_local; e += nthr) base[e] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += nthr) {
+        int e = idx[i] - e_lo;
+        if (e >= 0 && e < n_local) atomicAdd(&base[e], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int e = 0; e < n_local; ++e) {
+            int c = base[e];
+            d.count[e] = c;
+            d.offset[e] = run;
+            base[e] = run;
+            run += c;
+        }
+        d.offset[n_local] = run;
+    }
+    __syncthreads();
+    for (int start = 0; start < n; start += nthr) {
+        for (int j = tid; j < 32 * n_local; j += nthr) wc[j] = 0;
+        __syncthreads();
+        int i = start + tid;
+        int e = -1;
+        if (i < n) {
+            e = idx[i] - e_lo;
+            if (e < 0 || e >= n_local) e = -1;
+        }
+        unsigned peers = __match_any_sync(0xffffffffu, e);
+        int rank = __popc(peers & ((1u << lane) - 1u));
+        if (e >= 0 && rank == 0) wc[warp * n_local + e] = __popc(peers);
+        __syncthreads();
+        for (int ee = tid; ee < n_local; ee += nthr) {
+            int run = base[ee];
+            for (int w = 0; w < 32; ++w) {
+                int c = wc[w * n_local + ee];
+                wc[w * n_local + ee] = run;
+                run += c;
+            }
+            base[ee] = run;
+        }
+        __syncthreads();
+        if (i < n) {
+            if (e >= 0) {
+                int pos = wc[warp * n_local + e] + rank;
+                d.perm[pos] = i;
+                d.inv[i] = pos;
+            } else {
+                d.inv[i] = -1;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(1024) dispatch_kernel(const int32_t* __restrict__ idx, int n, int e_lo,
+                                                        int n_local, DispatchArrays d) {
+    extern __shared__ int dsmem[];
+    dispatch_block(idx, n, e_lo, n_local, d, dsmem);
+}
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+router_topk_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
+                   const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H,
+                   int E, int k, int32_t* __restrict__ idx, float* __restrict__ w) {
+    extern __shared__ __align__(16) unsigned char rsmem[];
+    float* xs = reinterpret_cast<float*>(rsmem);  // [H]
+    float* lg = xs + H;                            // [E]
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = THREADS / 32;
+    const uint32_t* xrow = reinterpret_cast<const uint32_t*>(x + (size_t)t * H);
+    for (int i = tid; i < H / 2; i += THREADS) {
+        uint32_t v = xrow[i];
+        xs[2 * i] = __uint_as_float(v << 16);
+        xs[2 * i + 1] = __uint_as_float(v & 0xffff0000u);
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += NW) {
+        const uint32_t* wrow = reinterpret_cast<const uint32_t*>(wr + (size_t)e * H);
+        float acc = 0.f;
+        for (int i = lane; i < H / 2; i += 32) {
+            uint32_t v = __ldg(wrow + i);
+            acc = fmaf(xs[2 * i], __uint_as_float(v << 16), acc);
+            acc = fmaf(xs[2 * i + 1], __uint_as_float(v & 0xffff0000u), acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            float v = acc + bf16_bits_to_float(br[e]);
+            if (logit_bias) v += logit_bias[e];
+            lg[e] = v;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long keys[kMaxExperts / 32];
+#pragma unroll
+        for (int j = 0; j < kMaxExperts / 32; ++j) {
+            int e = lane + 32 * j;
+            keys[j] = (e < E) ? logit_key(lg[e], e) : 0ull;
+        }
+        float sel[kMaxTopK];
+        int seli[kMaxTopK];
+#pragma unroll
+        for (int s = 0; s < kMaxTopK; ++s) {
+            if (s < k) {
+                unsigned long long best = 0ull;
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j) best = keys[j] > best ? keys[j] : best;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                    best = other > best ? other : best;
+                }
+                int e = 0x7fffffff - (int)(uint32_t)(best & 0xffffffffull);
+                seli[s] = e;
+                sel[s] = lg[e];
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j)
+                    if (lane + 32 * j == e) keys[j] = 0ull;
+            }
+        }
+        if (lane == 0) {
+            float m = sel[0], den = 0.f, p[kMaxTopK];
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    p[s] = expf(sel[s] - m);
+                    den += p[s];
+                }
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    idx[t * k + s] = seli[s];
+                    w[t * k + s] = p[s] / den;
+                }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Grouped MXFP4 expert product on mma.m16n8k16 (weights = the 16-row M operand, tokens =
+// the N operand, 8 per n-tile).  Each warp owns one 16-row tile of one expert and walks
+// the whole K; the expert's weights are read once per chunk of 8*NT tokens (once in total
+// when the expert has at most 8*NT tokens).
+//
+//   GATE_UP: B = bf16 hidden rows gathered through perm; epilogue adds the bias, applies
+//            the clamped SwiGLU and stores the activation as a bf16 (hi, lo) split pair.
+//   DOWN:    B = the (hi, lo) activation planes (two MMAs, fp32-equivalent input);
+//            epilogue adds the bias, multiplies by the routing weight, stores fp32 rows
+//            in sorted order for the fixed-order combine.
+// grid = (ceil(tiles / WARPS), E_local), block = 32*WARPS.
+// ---------------------------------------------------------------------------------------
+struct ExpertParams {
+    const uint4* wq;        // [E][tiles][nbp][32]
+    const uint32_t* sq;     // [E][tiles][nbp][8]
+    const uint16_t* bias;   // [E][rows] original row order
+    const int32_t* offset;  // [E+1]
+    const int32_t* perm;    // [n]
+    int tiles, nbp, rows, K, top_k;
+    // gate_up
+    const uint16_t* x;      // [T][K] bf16
+    uint16_t* a_hi;         // [n][I]
+    uint16_t* a_lo;
+    float limit, alpha;
+    // down
+    const float* route_w;   // [T*k] by entry id
+    float* y;               // [n][rows] fp32, sorted order
+};
+
+template <int NT, bool GATE_UP, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS) expert_mma_kernel(ExpertParams p) {
+    const int e = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tl = blockIdx.x * WARPS + warp;
+    const int row0 = p.offset[e], n_e = p.offset[e + 1] - row0;
+    if (n_e == 0 || tl >= p.tiles) return;
+    const int g = lane >> 2, t = lane & 3;
+    const uint4* wq = p.wq + ((size_t)e * p.tiles + tl) * p.nbp * 32 + lane;
+    const uint32_t* sq = p.sq + ((size_t)e * p.tiles + tl) * p.nbp * 8 + g;
+    const int I = GATE_UP ? p.rows / 2 : p.K;  // intermediate size
+
+    for (int chunk = 0; chunk < n_e; chunk += 8 * NT) {
+        const int nact = min(NT, (n_e - chunk + 7) >> 3);  // n-tiles holding a real token
+        float acc[NT][4];
+        const uint16_t* brow[NT];   // this lane's B row (token column g of n-tile j)
+        const uint16_t* brow2[NT];  // lo plane (down only)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+            int pos = chunk + 8 * j + g;
+            brow[j] = nullptr;
+            brow2[j] = nullptr;
+            if (pos < n_e) {
+                if (GATE_UP) {
+                    int tok = p.perm[row0 + pos] / p.top_k;
+                    brow[j] = p.x + (size_t)tok * p.K + 8 * t;
+                } else {
+                    brow[j] = p.a_hi + (size_t)(row0 + pos) * p.K + 8 * t;
+                    brow2[j] = p.a_lo + (size_t)(row0 + pos) * p.K + 8 * t;
+                }
+            }
+        }
+#pragma unroll 2
+        for (int bp = 0; bp < p.nbp; ++bp) {
+            uint4 wv = ldg_stream(wq + (size_t)bp * 32);
+            uint32_t sv = __ldg(sq + (size_t)bp * 8);
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                uint32_t lo[4], hi[4];
+                unpack8(blk ? wv.z : wv.x, scale_mult((sv >> (16 * blk)) & 255u), lo);
+                unpack8(blk ? wv.w : wv.y, scale_mult((sv >> (16 * blk + 8)) & 255u), hi);
+                const uint32_t a1[4] = {lo[0], hi[0], lo[1], hi[1]};
+                const uint32_t a2[4] = {lo[2], hi[2], lo[3], hi[3]};
+                const int koff = (2 * bp + blk) * 32;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    if (j >= nact) break;
+                    uint4 xb = make_uint4(0, 0, 0, 0);
+                    if (brow[j]) xb = __ldg(reinterpret_cast<const uint4*>(brow[j] + koff));
+                    mma_bf16_16816(acc[j], a1, xb.x, xb.y);
+                    mma_bf16_16816(acc[j], a2, xb.z, xb.w);
+                    if (!GATE_UP) {
+                        uint4 xl = make_uint4(0, 0, 0, 0);
+                        if (brow2[j]) xl = __ldg(reinterpret_cast<const uint4*>(brow2[j] + koff));
+                        mma_bf16_16816(acc[j], a1, xl.x, xl.y);
+                        mma_bf16_16816(acc[j], a2, xl.z, xl.w);
+                    }
+                }
+            }
+        }
+        // Epilogue.  acc[j] = {(row g, tok 2t), (row g, tok 2t+1), (row g+8, tok 2t), (row g+8, tok 2t+1)}
+        if (GATE_UP) {
+            const int ch = 8 * tl + g;
+            const float bg = bf16_bits_to_float(p.bias[(size_t)e * p.rows + 2 * ch]);
+            const float bl = bf16_bits_to_float(p.bias[(size_t)e * p.rows + 2 * ch + 1]);
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    int pos = chunk + 8 * j + 2 * t + c;
+                    if (pos < n_e) {
+                        float gl = fminf(acc[j][c] + bg, p.limit);
+                        float ln = fminf(fmaxf(acc[j][2 + c] + bl, -p.limit), p.limit);
+                        float a = gl / (1.f + expf(-p.alpha * gl)) * (ln + 1.f);
+                        __nv_bfloat16 h = __float2bfloat16_rn(a);
+                        __nv_bfloat16 l = __float2bfloat16_rn(a - __bfloat162float(h));
+                        size_t o = (size_t)(row0 + pos) * I + ch;
+                        p.a_hi[o] = __bfloat16_as_ushort(h);
+                        p.a_lo[o] = __bfloat16_as_ushort(l);
+                    }
+                }
+        } else {
+            const int r_lo = 16 * tl + g, r_hi = r_lo + 8;
+            const float b_lo = bf16_bits_to_float(p.bias[(size_t)e * p.rows + r_lo]);
+            const float b_hi = bf16_bits_to_float(p.bias[(size_t)e * p.rows + r_hi]);
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    int pos = chunk + 8 * j + 2 * t + c;
+                    if (pos < n_e) {
+                        float rw = p.route_w[p.perm[row0 + pos]];
+                        float* yrow = p.y + (size_t)(row0 + pos) * p.rows;
+                        yrow[r_lo] = rw * (acc[j][c] + b_lo);
+                        yrow[r_hi] = rw * (acc[j][2 + c] + b_hi);
+                    }
+                }
+        }
+    }
+}
+
+// out[t, c] = sum over slots s (in order) of y[inv[t*k+s], c]; entries with inv < 0
+// (experts of another rank) are skipped.
+__global__ void combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, int T, int H,
+                               int k, float* __restrict__ out) {
+    const int t = blockIdx.y;
+    const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c4 * 4 >= H) return;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sl = 0; sl < k; ++sl) {
+        int pos = inv[t * k + sl];
+        if (pos < 0) continue;
+        float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * H + 4 * c4);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * H + 4 * c4) = s;
+}
+
+}  // namespace neon

@@ -1,0 +1,369 @@
+// Host side of libneon_moe.so: the C ABI declared in include/neon_moe.h over the kernels
+// in moe_kernels.cuh.  No CPU fallback exists: every compute entry point launches CUDA
+// kernels or fails with an error code.
+#include "../../include/neon_moe.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "moe_kernels.cuh"
+
+using namespace neon;
+
+namespace {
+thread_local std::string g_create_error;
+
+struct DeviceBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+};
+}  // namespace
+
+struct neon_moe_handle {
+    neon_moe_config cfg{};
+    int n_local = 0, e_lo = 0;
+    bool has_weights = false;
+    std::string err;
+    int64_t launches = 0;
+    cudaStream_t last_stream = nullptr;
+    cudaStream_t own_stream = nullptr;
+    int last_n = 0;
+    // weights
+    uint16_t *router_w = nullptr, *router_b = nullptr, *gu_bias = nullptr, *dn_bias = nullptr;
+    uint4 *gu_wq = nullptr, *dn_wq = nullptr;
+    uint32_t *gu_sq = nullptr, *dn_sq = nullptr;
+    // workspaces
+    int32_t *idx = nullptr, *count = nullptr, *offset = nullptr, *perm = nullptr, *inv = nullptr;
+    float *route_w = nullptr, *y = nullptr;
+    uint16_t *a_hi = nullptr, *a_lo = nullptr;
+    int* status = nullptr;
+    // per-stage profiling: 5 events per forward
+    bool profiling = false;
+    std::vector<cudaEvent_t> events;
+    size_t events_used = 0;
+    // staging for the host-buffer entry point
+    uint16_t* st_hidden = nullptr;
+    float *st_out = nullptr, *st_bias = nullptr;
+};
+
+namespace {
+
+int fail(neon_moe_handle* h, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (h) h->err = buf; else g_create_error = buf;
+    return code;
+}
+
+#define CU(h, call)                                                                          \
+    do {                                                                                     \
+        cudaError_t e_ = (call);                                                             \
+        if (e_ != cudaSuccess)                                                               \
+            return fail(h, NEON_MOE_ECUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+template <typename T>
+int dev_alloc(neon_moe_handle* h, T** p, size_t count) {
+    CU(h, cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T) + 16));
+    return NEON_MOE_OK;
+}
+
+void free_all(neon_moe_handle* h) {
+    void* ptrs[] = {h->router_w, h->router_b, h->gu_bias, h->dn_bias, h->gu_wq, h->dn_wq, h->gu_sq, h->dn_sq,
+                    h->idx, h->count, h->offset, h->perm, h->inv, h->route_w, h->y, h->a_hi, h->a_lo,
+                    h->status, h->st_hidden, h->st_out, h->st_bias};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    for (cudaEvent_t ev : h->events) cudaEventDestroy(ev);
+}
+
+constexpr size_t kMaxProfiledForwards = 4096;
+
+// Records the next profiling event on `st` (no-op unless profiling is on and room is left).
+void mark(neon_moe_handle* h, cudaStream_t st, bool active) {
+    if (!active) return;
+    if (h->events_used == h->events.size()) {
+        cudaEvent_t ev;
+        if (cudaEventCreate(&ev) != cudaSuccess) return;
+        h->events.push_back(ev);
+    }
+    cudaEventRecord(h->events[h->events_used++], st);
+}
+
+// Upload (when needed) and re-tile one MXFP4 matrix set.
+int load_matrix(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* scales, int rows, int K, int gate_up,
+                int on_device, uint4** wq, uint32_t** sq) {
+    const int E = h->n_local;
+    const size_t nb = (size_t)E * rows * (K / 2), ns = (size_t)E * rows * (K / 32);
+    const uint8_t *d_blocks = blocks, *d_scales = scales;
+    uint8_t *tmp_b = nullptr, *tmp_s = nullptr;
+    if (!on_device) {
+        CU(h, cudaMalloc(&tmp_b, nb));
+        CU(h, cudaMalloc(&tmp_s, ns));
+        CU(h, cudaMemcpy(tmp_b, blocks, nb, cudaMemcpyHostToDevice));
+        CU(h, cudaMemcpy(tmp_s, scales, ns, cudaMemcpyHostToDevice));
+        d_blocks = tmp_b;
+        d_scales = tmp_s;
+    }
+    const int tiles = rows / 16, nbp = K / 64;
+    if (!*wq) {
+        int rc = dev_alloc(h, wq, (size_t)E * tiles * nbp * 32);
+        if (rc) return rc;
+        rc = dev_alloc(h, sq, (size_t)E * tiles * nbp * 8);
+        if (rc) return rc;
+    }
+    CU(h, cudaMemset(h->status, 0, sizeof(int)));
+    repack_mma16_kernel<<<148 * 8, 256>>>(d_blocks, d_scales, E, rows, K, gate_up, *wq, *sq, h->status);
+    h->launches++;
+    CU(h, cudaGetLastError());
+    int bad = 0;
+    CU(h, cudaMemcpy(&bad, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    CU(h, cudaMemset(h->status, 0, sizeof(int)));
+    if (tmp_b) cudaFree(tmp_b);
+    if (tmp_s) cudaFree(tmp_s);
+    if (bad) return fail(h, NEON_MOE_EINVAL, "MXFP4 scale byte above 128 (scale > 2) is not supported");
+    return NEON_MOE_OK;
+}
+
+int copy_in(neon_moe_handle* h, uint16_t** dst, const void* src, size_t count, int on_device) {
+    if (!*dst) {
+        int rc = dev_alloc(h, dst, count);
+        if (rc) return rc;
+    }
+    CU(h, cudaMemcpy(*dst, src, count * 2, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    return NEON_MOE_OK;
+}
+
+template <bool GATE_UP>
+void launch_expert(neon_moe_handle* h, const ExpertParams& p, int T, cudaStream_t st) {
+    constexpr int WARPS = 4;
+    dim3 grid((p.tiles + WARPS - 1) / WARPS, h->n_local), block(32 * WARPS);
+    if (T <= 8) expert_mma_kernel<1, GATE_UP, WARPS><<<grid, block, 0, st>>>(p);
+    else if (T <= 16) expert_mma_kernel<2, GATE_UP, WARPS><<<grid, block, 0, st>>>(p);
+    else if (T <= 32) expert_mma_kernel<4, GATE_UP, WARPS><<<grid, block, 0, st>>>(p);
+    else expert_mma_kernel<8, GATE_UP, WARPS><<<grid, block, 0, st>>>(p);
+    h->launches++;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* neon_moe_version(void) { return "neon_moe 0.1 (sm_100a)"; }
+
+const char* neon_moe_last_error(const neon_moe_handle* h) { return h ? h->err.c_str() : g_create_error.c_str(); }
+
+int64_t neon_moe_launch_count(const neon_moe_handle* h) { return h ? h->launches : 0; }
+
+int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
+    if (!cfg || !out) return fail(nullptr, NEON_MOE_EINVAL, "null argument");
+    *out = nullptr;
+    if (cfg->hidden <= 0 || cfg->hidden % 64 || cfg->inter <= 0 || cfg->inter % 64)
+        return fail(nullptr, NEON_MOE_EINVAL, "hidden and inter must be positive multiples of 64");
+    if (cfg->n_experts <= 0 || cfg->n_experts > kMaxExperts || cfg->top_k <= 0 || cfg->top_k > kMaxTopK ||
+        cfg->top_k > cfg->n_experts)
+        return fail(nullptr, NEON_MOE_EINVAL, "need 1 <= top_k <= min(8, n_experts) and n_experts <= 256");
+    if (cfg->ep_size <= 0 || cfg->ep_rank < 0 || cfg->ep_rank >= cfg->ep_size || cfg->n_experts % cfg->ep_size)
+        return fail(nullptr, NEON_MOE_EINVAL, "bad expert-parallel rank/size");
+    if (cfg->max_tokens <= 0) return fail(nullptr, NEON_MOE_EINVAL, "max_tokens must be positive");
+    int ndev = 0;
+    cudaError_t ce = cudaGetDeviceCount(&ndev);
+    if (ce != cudaSuccess || ndev == 0)
+        return fail(nullptr, NEON_MOE_ECUDA, "no CUDA device: %s", cudaGetErrorString(ce));
+    if (cfg->device < 0 || cfg->device >= ndev) return fail(nullptr, NEON_MOE_EINVAL, "bad device ordinal");
+    neon_moe_handle* h = new (std::nothrow) neon_moe_handle;
+    if (!h) return fail(nullptr, NEON_MOE_EINVAL, "out of host memory");
+    h->cfg = *cfg;
+    h->n_local = cfg->n_experts / cfg->ep_size;
+    h->e_lo = cfg->ep_rank * h->n_local;
+    auto bail = [&](int rc) {
+        g_create_error = h->err;
+        free_all(h);
+        delete h;
+        return rc;
+    };
+    if (cudaSetDevice(cfg->device) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaSetDevice failed"));
+    const size_t n = (size_t)cfg->max_tokens * cfg->top_k;
+    int rc = 0;
+    if ((rc = dev_alloc(h, &h->idx, n)) || (rc = dev_alloc(h, &h->route_w, n)) ||
+        (rc = dev_alloc(h, &h->count, (size_t)h->n_local)) || (rc = dev_alloc(h, &h->offset, (size_t)h->n_local + 1)) ||
+        (rc = dev_alloc(h, &h->perm, n)) || (rc = dev_alloc(h, &h->inv, n)) ||
+        (rc = dev_alloc(h, &h->a_hi, n * cfg->inter)) || (rc = dev_alloc(h, &h->a_lo, n * cfg->inter)) ||
+        (rc = dev_alloc(h, &h->y, n * cfg->hidden)) || (rc = dev_alloc(h, &h->status, (size_t)4)) ||
+        (rc = dev_alloc(h, &h->st_hidden, (size_t)cfg->max_tokens * cfg->hidden)) ||
+        (rc = dev_alloc(h, &h->st_out, (size_t)cfg->max_tokens * cfg->hidden)) ||
+        (rc = dev_alloc(h, &h->st_bias, (size_t)cfg->n_experts)))
+        return bail(rc);
+    if (cudaMemset(h->status, 0, 16) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
+    if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return bail(fail(h, NEON_MOE_ECUDA, "cudaStreamCreate failed"));
+    *out = h;
+    return NEON_MOE_OK;
+}
+
+int neon_moe_destroy(neon_moe_handle* h) {
+    if (!h) return NEON_MOE_EINVAL;
+    cudaSetDevice(h->cfg.device);
+    cudaDeviceSynchronize();
+    free_all(h);
+    delete h;
+    return NEON_MOE_OK;
+}
+
+int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* router_b,
+                         const uint8_t* gu_blocks, const uint8_t* gu_scales, const void* gu_bias,
+                         const uint8_t* dn_blocks, const uint8_t* dn_scales, const void* dn_bias, int on_device) {
+    if (!h) return NEON_MOE_EINVAL;
+    if (!router_w || !router_b || !gu_blocks || !gu_scales || !gu_bias || !dn_blocks || !dn_scales || !dn_bias)
+        return fail(h, NEON_MOE_EINVAL, "null weight pointer");
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaDeviceSynchronize());
+    const int H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts, EL = h->n_local;
+    h->has_weights = false;
+    int rc;
+    if ((rc = copy_in(h, &h->router_w, router_w, (size_t)E * H, on_device))) return rc;
+    if ((rc = copy_in(h, &h->router_b, router_b, (size_t)E, on_device))) return rc;
+    if ((rc = copy_in(h, &h->gu_bias, gu_bias, (size_t)EL * 2 * I, on_device))) return rc;
+    if ((rc = copy_in(h, &h->dn_bias, dn_bias, (size_t)EL * H, on_device))) return rc;
+    if ((rc = load_matrix(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wq, &h->gu_sq))) return rc;
+    if ((rc = load_matrix(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wq, &h->dn_sq))) return rc;
+    CU(h, cudaDeviceSynchronize());
+    h->has_weights = true;
+    return NEON_MOE_OK;
+}
+
+int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
+                     int32_t* topk_idx, float* topk_w, void* cuda_stream) {
+    if (!h) return NEON_MOE_EINVAL;
+    if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "forward before set_weights");
+    if (h->cfg.ep_size != 1) return fail(h, NEON_MOE_ESTATE, "forward needs ep_size == 1; use the expert-parallel entry points");
+    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
+    if (T == 0) { h->last_n = 0; return NEON_MOE_OK; }
+    if (!hidden || !out) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
+    CU(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const int H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts, k = h->cfg.top_k;
+    const int n = T * k;
+    const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
+
+    mark(h, st, prof);
+    router_topk_kernel<256><<<T, 256, (H + E) * sizeof(float), st>>>(
+        static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, h->idx, h->route_w);
+    h->launches++;
+    DispatchArrays d{h->count, h->offset, h->perm, h->inv};
+    dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->idx, n, 0, E, d);
+    h->launches++;
+
+    ExpertParams p{};
+    p.offset = h->offset;
+    p.perm = h->perm;
+    p.top_k = k;
+    p.x = static_cast<const uint16_t*>(hidden);
+    p.a_hi = h->a_hi;
+    p.a_lo = h->a_lo;
+    p.limit = h->cfg.swiglu_limit;
+    p.alpha = h->cfg.swiglu_alpha;
+    p.route_w = h->route_w;
+    p.y = h->y;
+    // gate_up: rows 2I, K = H
+    p.wq = h->gu_wq; p.sq = h->gu_sq; p.bias = h->gu_bias;
+    p.rows = 2 * I; p.K = H; p.tiles = 2 * I / 16; p.nbp = H / 64;
+    mark(h, st, prof);
+    launch_expert<true>(h, p, T, st);
+    mark(h, st, prof);
+    // down: rows H, K = I
+    p.wq = h->dn_wq; p.sq = h->dn_sq; p.bias = h->dn_bias;
+    p.rows = H; p.K = I; p.tiles = H / 16; p.nbp = I / 64;
+    launch_expert<false>(h, p, T, st);
+    mark(h, st, prof);
+
+    dim3 cgrid((H / 4 + 127) / 128, T);
+    combine_kernel<<<cgrid, 128, 0, st>>>(h->y, h->inv, T, H, k, out);
+    h->launches++;
+    mark(h, st, prof);
+    if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
+    if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
+    CU(h, cudaGetLastError());
+    h->last_stream = st;
+    h->last_n = n;
+    return NEON_MOE_OK;
+}
+
+int neon_moe_forward_host(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
+                          int32_t* topk_idx, float* topk_w) {
+    if (!h) return NEON_MOE_EINVAL;
+    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
+    if (T == 0) return NEON_MOE_OK;
+    if (!hidden || !out) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
+    CU(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = h->own_stream;
+    const size_t nh = (size_t)T * h->cfg.hidden;
+    CU(h, cudaMemcpyAsync(h->st_hidden, hidden, nh * 2, cudaMemcpyHostToDevice, st));
+    if (logit_bias)
+        CU(h, cudaMemcpyAsync(h->st_bias, logit_bias, (size_t)h->cfg.n_experts * 4, cudaMemcpyHostToDevice, st));
+    int rc = neon_moe_forward(h, h->st_hidden, T, logit_bias ? h->st_bias : nullptr, h->st_out, nullptr, nullptr, st);
+    if (rc) return rc;
+    CU(h, cudaMemcpyAsync(out, h->st_out, nh * 4, cudaMemcpyDeviceToHost, st));
+    const size_t n = (size_t)T * h->cfg.top_k;
+    if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, n * 4, cudaMemcpyDeviceToHost, st));
+    if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, n * 4, cudaMemcpyDeviceToHost, st));
+    CU(h, cudaStreamSynchronize(st));
+    return NEON_MOE_OK;
+}
+
+int neon_moe_read_dispatch(neon_moe_handle* h, int32_t* count, int32_t* offset, int32_t* perm, int32_t* inv,
+                           int* n_entries) {
+    if (!h) return NEON_MOE_EINVAL;
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaStreamSynchronize(h->last_stream));
+    const int EL = h->n_local, n = h->last_n;
+    if (n_entries) *n_entries = n;
+    if (n == 0) return NEON_MOE_OK;
+    if (count) CU(h, cudaMemcpy(count, h->count, (size_t)EL * 4, cudaMemcpyDeviceToHost));
+    if (offset) CU(h, cudaMemcpy(offset, h->offset, (size_t)(EL + 1) * 4, cudaMemcpyDeviceToHost));
+    if (perm) CU(h, cudaMemcpy(perm, h->perm, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    if (inv) CU(h, cudaMemcpy(inv, h->inv, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return NEON_MOE_OK;
+}
+
+int neon_moe_profile(neon_moe_handle* h, int enable) {
+    if (!h) return NEON_MOE_EINVAL;
+    h->profiling = enable != 0;
+    return NEON_MOE_OK;
+}
+
+int neon_moe_read_profile(neon_moe_handle* h, double* ms, int* n_forwards) {
+    if (!h || !ms || !n_forwards) return NEON_MOE_EINVAL;
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaStreamSynchronize(h->last_stream));
+    for (int i = 0; i < 4; ++i) ms[i] = 0.0;
+    const size_t nf = h->events_used / 5;
+    for (size_t f = 0; f < nf; ++f)
+        for (int i = 0; i < 4; ++i) {
+            float t = 0.f;
+            CU(h, cudaEventElapsedTime(&t, h->events[5 * f + i], h->events[5 * f + i + 1]));
+            ms[i] += t;
+        }
+    *n_forwards = (int)nf;
+    h->events_used = 0;
+    return NEON_MOE_OK;
+}
+
+int neon_moe_status(neon_moe_handle* h, int* word) {
+    if (!h || !word) return NEON_MOE_EINVAL;
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaStreamSynchronize(h->last_stream));
+    CU(h, cudaMemcpy(word, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    CU(h, cudaMemset(h->status, 0, sizeof(int)));
+    return *word ? NEON_MOE_EDEVICE : NEON_MOE_OK;
+}
+
+}  // extern "C"

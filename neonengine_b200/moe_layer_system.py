@@ -1,0 +1,135 @@
+"""Python mirror of the C++ ``lve::MoeLayerSystem`` wrapper (include/lve_moe_layer_system.hpp).
+
+Same shape as the engine's compute systems (NeonEngine/src/water_physics.hpp:66,
+NeonEngine/src/raytracing_system.hpp:79): the constructor creates the layer and uploads
+the weights, ``run`` enqueues one pass on a stream, a non-zero status becomes a
+``RuntimeError`` (the C++ wrapper throws ``std::runtime_error``).  torch is used only to
+own device memory and streams; all compute happens inside ``libneon_moe.so``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from .synth import MoeShape, MoeWeights
+
+
+class MoeLayerSystem:
+    def __init__(self, shape: MoeShape, weights: MoeWeights, max_tokens: int, device: int = 0,
+                 ep_rank: int = 0, ep_size: int = 1):
+        self._lib = _lib.load()
+        self.shape = shape
+        self.max_tokens = int(max_tokens)
+        self.device = int(device)
+        self.ep_rank, self.ep_size = int(ep_rank), int(ep_size)
+        cfg = _lib.NeonMoeConfig(shape.hidden, shape.inter, shape.n_experts, shape.top_k,
+                                 shape.swiglu_limit, shape.swiglu_alpha, self.max_tokens,
+                                 self.ep_rank, self.ep_size, self.device)
+        handle = ctypes.c_void_p()
+        rc = self._lib.neon_moe_create(ctypes.byref(cfg), ctypes.byref(handle))
+        if rc != 0:
+            raise RuntimeError(f"neon_moe_create failed ({rc}): {self._lib.neon_moe_last_error(None).decode()}")
+        self._h = handle
+        self.set_weights(weights)
+
+    # -- helpers -------------------------------------------------------------------------
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            raise RuntimeError(f"{what} failed ({rc}): {self._lib.neon_moe_last_error(self._h).decode()}")
+
+    @staticmethod
+    def _np_ptr(a):
+        return None if a is None else ctypes.c_void_p(a.ctypes.data)
+
+    def set_weights(self, w: MoeWeights) -> None:
+        arrs = [np.ascontiguousarray(a) for a in (w.router_w, w.router_b, w.gate_up_blocks, w.gate_up_scales,
+                                                  w.gate_up_bias, w.down_blocks, w.down_scales, w.down_bias)]
+        self._check(self._lib.neon_moe_set_weights(self._h, *[self._np_ptr(a) for a in arrs], 0), "neon_moe_set_weights")
+
+    # -- device path ---------------------------------------------------------------------
+    def run(self, hidden, logit_bias=None, out=None, want_routing=False, stream=None):
+        """One pass over device tensors.  ``hidden``: torch bf16 (or int16/uint16 bit view)
+        [T, H] on this layer's GPU; returns fp32 [T, H] (and idx, w when ``want_routing``)."""
+        import torch
+        T = hidden.shape[0]
+        assert hidden.is_cuda and hidden.is_contiguous() and hidden.element_size() == 2
+        dev = hidden.device
+        if out is None:
+            out = torch.empty((T, self.shape.hidden), dtype=torch.float32, device=dev)
+        idx = w = None
+        if want_routing:
+            idx = torch.empty((T, self.shape.top_k), dtype=torch.int32, device=dev)
+            w = torch.empty((T, self.shape.top_k), dtype=torch.float32, device=dev)
+        st = (stream or torch.cuda.current_stream(dev)).cuda_stream
+        rc = self._lib.neon_moe_forward(self._h, hidden.data_ptr(), T,
+                                        None if logit_bias is None else logit_bias.data_ptr(),
+                                        out.data_ptr(), None if idx is None else idx.data_ptr(),
+                                        None if w is None else w.data_ptr(), st)
+        self._check(rc, "neon_moe_forward")
+        return (out, idx, w) if want_routing else out
+
+    # -- host path -----------------------------------------------------------------------
+    def run_host(self, hidden: np.ndarray, logit_bias: np.ndarray | None = None, out: np.ndarray | None = None,
+                 want_routing: bool = False):
+        """One pass over HOST arrays (uint16 bf16 bits in, fp32 out); copies happen inside."""
+        hidden = np.ascontiguousarray(hidden, np.uint16)
+        T = hidden.shape[0]
+        if out is None:
+            out = np.empty((T, self.shape.hidden), np.float32)
+        lb = None if logit_bias is None else np.ascontiguousarray(logit_bias, np.float32)
+        idx = np.empty((T, self.shape.top_k), np.int32) if want_routing else None
+        w = np.empty((T, self.shape.top_k), np.float32) if want_routing else None
+        rc = self._lib.neon_moe_forward_host(self._h, self._np_ptr(hidden), T, self._np_ptr(lb), self._np_ptr(out),
+                                             self._np_ptr(idx), self._np_ptr(w))
+        self._check(rc, "neon_moe_forward_host")
+        return (out, idx, w) if want_routing else out
+
+    def run_host_ptr(self, hidden_ptr: int, T: int, logit_bias_ptr: int | None, out_ptr: int) -> None:
+        """Host pass on raw (e.g. pinned) addresses, no Python-side copies."""
+        self._check(self._lib.neon_moe_forward_host(self._h, hidden_ptr, T, logit_bias_ptr, out_ptr, None, None),
+                    "neon_moe_forward_host")
+
+    def read_dispatch(self):
+        n = ctypes.c_int(0)
+        self._check(self._lib.neon_moe_read_dispatch(self._h, None, None, None, None, ctypes.byref(n)), "read_dispatch")
+        el = self.shape.n_experts // self.ep_size
+        count = np.zeros(el, np.int32)
+        offset = np.zeros(el + 1, np.int32)
+        perm = np.zeros(n.value, np.int32)
+        inv = np.zeros(n.value, np.int32)
+        self._check(self._lib.neon_moe_read_dispatch(self._h, self._np_ptr(count), self._np_ptr(offset),
+                                                     self._np_ptr(perm), self._np_ptr(inv), ctypes.byref(n)),
+                    "read_dispatch")
+        return count, offset, perm, inv
+
+    def profile(self, enable: bool) -> None:
+        self._check(self._lib.neon_moe_profile(self._h, int(enable)), "neon_moe_profile")
+
+    def read_profile(self):
+        """Summed stage times in ms since the last read: dict + number of forwards."""
+        ms = (ctypes.c_double * 4)()
+        n = ctypes.c_int(0)
+        self._check(self._lib.neon_moe_read_profile(self._h, ms, ctypes.byref(n)), "neon_moe_read_profile")
+        return dict(zip(("route_dispatch", "gate_up", "down", "combine"), list(ms))), n.value
+
+    def status(self) -> int:
+        word = ctypes.c_int(0)
+        self._lib.neon_moe_status(self._h, ctypes.byref(word))
+        return word.value
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.neon_moe_launch_count(self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.neon_moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

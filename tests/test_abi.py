@@ -1,0 +1,67 @@
+"""CPU tests of the C-ABI library: it loads, exports every declared symbol, and refuses
+to compute without a GPU (no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from neonengine_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.load()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "neon_moe.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(neon_moe_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_exports_every_declared_symbol(lib):
+    names = declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in neon_moe.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "python binding table out of sync with the header"
+
+
+def test_version(lib):
+    assert b"sm_100a" in lib.neon_moe_version()
+
+
+def test_create_rejects_bad_config(lib):
+    h = ctypes.c_void_p()
+    cfg = _lib.NeonMoeConfig(100, 64, 8, 4, 7.0, 1.702, 4, 0, 1, 0)  # hidden not a multiple of 64
+    assert lib.neon_moe_create(ctypes.byref(cfg), ctypes.byref(h)) == 1
+    assert b"multiples of 64" in lib.neon_moe_last_error(None)
+    cfg = _lib.NeonMoeConfig(64, 64, 8, 9, 7.0, 1.702, 4, 0, 1, 0)   # top_k too large
+    assert lib.neon_moe_create(ctypes.byref(cfg), ctypes.byref(h)) == 1
+    cfg = _lib.NeonMoeConfig(64, 64, 8, 4, 7.0, 1.702, 4, 3, 2, 0)   # rank >= size
+    assert lib.neon_moe_create(ctypes.byref(cfg), ctypes.byref(h)) == 1
+
+
+def test_no_cpu_fallback(lib):
+    """Without a GPU a valid create must fail with the CUDA error code, not compute on the host."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    h = ctypes.c_void_p()
+    cfg = _lib.NeonMoeConfig(64, 64, 8, 4, 7.0, 1.702, 4, 0, 1, 0)
+    assert lib.neon_moe_create(ctypes.byref(cfg), ctypes.byref(h)) == 2
+    assert not h.value
+
+
+def test_product_does_not_import_oracle():
+    pkg = os.path.join(ROOT, "neonengine_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"(import\s+oracle|from\s+oracle|moe_oracle|oracle/)", text), \
+                    f"{f} reaches into the oracle"

@@ -1,0 +1,159 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on
+the same seeded inputs.  Routing and dispatch are integer work and must be bit-exact;
+outputs must meet the contract tolerance (max-abs <= 2e-2 and mean-rel <= 5e-3)."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import assert_close, load_golden
+from neonengine_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return torch
+
+
+def make_layer(shape, W, max_tokens):
+    from neonengine_b200.moe_layer_system import MoeLayerSystem
+    return MoeLayerSystem(shape, W, max_tokens=max_tokens, device=0)
+
+
+def run_device(layer, hidden, logit_bias=None):
+    torch = torch_cuda()
+    h = torch.from_numpy(hidden.view(np.int16)).cuda()
+    lb = None if logit_bias is None else torch.from_numpy(np.asarray(logit_bias, np.float32)).cuda()
+    out, idx, w = layer.run(h, logit_bias=lb, want_routing=True)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), idx.cpu().numpy(), w.cpu().numpy()
+
+
+def check_against_oracle(layer, W, hidden, logit_bias=None, tokens=None, what=""):
+    out, idx, w = run_device(layer, hidden, logit_bias)
+    ridx, rw = oracle.route(hidden, W.router_w, W.router_b, W.shape.top_k, logit_bias)
+    np.testing.assert_array_equal(idx, ridx, err_msg=f"{what}: routing indices differ")
+    np.testing.assert_allclose(w, rw, rtol=0, atol=2e-6, err_msg=f"{what}: routing weights")
+    ref = oracle.experts(hidden, ridx, rw, W, tokens=tokens)
+    got = out if tokens is None else out[tokens]
+    err = assert_close(got, ref, what)
+    # dispatch arrays: bit-exact with the oracle's stable counting sort
+    count, offset, perm, inv = layer.read_dispatch()
+    rc, ro, rp, ri = oracle.dispatch(ridx, W.shape.n_experts)
+    np.testing.assert_array_equal(count, rc)
+    np.testing.assert_array_equal(offset, ro)
+    np.testing.assert_array_equal(perm, rp)
+    np.testing.assert_array_equal(inv, ri)
+    assert layer.status() == 0
+    return out, err
+
+
+@pytest.mark.parametrize("name", ["small_seeded", "small_seeded_zipf", "integer_kat", "clamp_negative", "all_ties"])
+def test_golden_vectors(name):
+    shape, W, hidden, lb, z = load_golden(name)
+    layer = make_layer(shape, W, max_tokens=16)
+    out, idx, w = run_device(layer, hidden, lb)
+    np.testing.assert_array_equal(idx, z["idx"])
+    np.testing.assert_allclose(w, z["w"], rtol=0, atol=2e-6)
+    ref = z["out"]
+    if name == "integer_kat" or name == "all_ties":   # |out| ~ 3584: compare relatively
+        np.testing.assert_allclose(out, ref, rtol=2e-6)
+    else:
+        assert_close(out, ref, name)
+    # the host-buffer entry point gives the same bits
+    out_h, idx_h, w_h = layer.run_host(hidden, lb, want_routing=True)
+    np.testing.assert_array_equal(out_h, out)
+    np.testing.assert_array_equal(idx_h, idx)
+    layer.close()
+
+
+@pytest.fixture(scope="module")
+def full20b():
+    """gpt-oss-20b-shaped layer: H=I=2880, E=32, k=4, benchmark distributions, seed 0."""
+    shape = synth.MoeShape()
+    W = synth.make_weights(shape, 0)
+    layer = make_layer(shape, W, max_tokens=512)
+    yield shape, W, layer
+    layer.close()
+
+
+def test_config0_decode_single_token(full20b):
+    shape, W, layer = full20b
+    for stream in range(3):
+        hidden = synth.make_hidden(1, W, 0, stream=stream)
+        check_against_oracle(layer, W, hidden, what=f"config0 stream {stream}")
+
+
+def test_config1_batched_decode_zipf(full20b):
+    shape, W, layer = full20b
+    lb = synth.zipf_logit_bias(shape.n_experts)
+    hidden = synth.make_hidden(64, W, 0, logit_bias=lb)
+    out, err = check_against_oracle(layer, W, hidden, logit_bias=lb, what="config1")
+    count = layer.read_dispatch()[0]
+    assert count.sum() == 256 and count.max() > 3 * count[count > 0].min()  # loads are skewed
+
+
+@pytest.mark.parametrize("T", [2, 3, 5, 9, 17, 33, 100])
+def test_ragged_token_counts(full20b, T):
+    shape, W, layer = full20b
+    hidden = synth.make_hidden(T, W, 1, stream=T)
+    toks = None if T <= 33 else np.arange(0, T, 7, dtype=np.int32)
+    check_against_oracle(layer, W, hidden, tokens=toks, what=f"T={T}")
+
+
+def test_all_tokens_on_the_same_experts(full20b):
+    """A large bias on four experts sends every token to them: 28 experts stay empty and
+    four experts get all 40 tokens (more than one 8-token MMA tile)."""
+    shape, W, layer = full20b
+    lb = np.zeros(shape.n_experts, np.float32)
+    lb[[3, 7, 20, 31]] = 50.0
+    hidden = synth.make_hidden(40, W, 2, logit_bias=lb)
+    out, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, what="same experts")
+    count = layer.read_dispatch()[0]
+    assert sorted(np.nonzero(count)[0].tolist()) == [3, 7, 20, 31] and set(count[count > 0]) == {40}
+
+
+def test_empty_batch_and_bad_sizes(full20b):
+    shape, W, layer = full20b
+    out = layer.run_host(np.zeros((0, shape.hidden), np.uint16))
+    assert out.shape == (0, shape.hidden)
+    with pytest.raises(RuntimeError, match="max_tokens"):
+        layer.run_host(np.zeros((513, shape.hidden), np.uint16))
+
+
+def test_deterministic_and_token_order_invariant(full20b):
+    """Two runs give identical bits, and permuting the tokens permutes the output rows
+    bit-exactly (each token's reductions do not depend on its position in the batch)."""
+    shape, W, layer = full20b
+    lb = synth.zipf_logit_bias(shape.n_experts)
+    hidden = synth.make_hidden(64, W, 3, logit_bias=lb)
+    a = run_device(layer, hidden, lb)[0]
+    b = run_device(layer, hidden, lb)[0]
+    np.testing.assert_array_equal(a, b)
+    perm = np.random.default_rng(0).permutation(64)
+    c = run_device(layer, np.ascontiguousarray(hidden[perm]), lb)[0]
+    np.testing.assert_array_equal(c, a[perm])
+
+
+def test_prefill_sized_batch_properties(full20b):
+    """T=512 (uniform routing): oracle on a token sample, routing exact for all tokens,
+    routing weights sum to one, counts add up."""
+    shape, W, layer = full20b
+    hidden = synth.make_hidden(512, W, 4)
+    toks = np.arange(3, 512, 37, dtype=np.int32)
+    out, _ = check_against_oracle(layer, W, hidden, tokens=toks, what="T=512")
+    _, idx, w = run_device(layer, hidden)
+    np.testing.assert_allclose(w.sum(axis=1), 1.0, atol=1e-6)
+    assert layer.read_dispatch()[0].sum() == 512 * 4
+    assert np.isfinite(out).all()
+
+
+def test_scale_out_of_range_is_rejected():
+    shape, W, hidden, lb, z = load_golden("small_seeded")
+    bad = synth.MoeWeights(shape, W.router_w, W.router_b, W.gate_up_blocks, W.gate_up_scales.copy(),
+                           W.gate_up_bias, W.down_blocks, W.down_scales, W.down_bias)
+    bad.gate_up_scales[0, 0, 0] = 200
+    with pytest.raises(RuntimeError, match="scale"):
+        make_layer(shape, bad, 4)

@@ -92,6 +92,35 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden_bf16, int T, const f
 int neon_moe_forward_host(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
                           float* out_f32, int32_t* topk_idx, float* topk_w);
 
+/* The layer pass for callers that must not allocate device memory.  It has no counterpart
+ * in the reference engine.
+ *
+ * Who needs it: code that is handed a finished layer (weights already on the GPU, set up by
+ * some other component at start-up) but runs where cudaMalloc is off limits - a plugin that
+ * lives inside a host application's fixed memory budget, a latency-critical decode loop that
+ * may not take the allocator's lock or its implicit device synchronisation, or a second
+ * thread that wants a pass while the handle's own workspaces are busy on another stream.
+ * neon_moe_forward keeps its intermediates in workspaces that neon_moe_create took from
+ * cudaMalloc; this variant keeps them in a 2 MiB array built into the library image (each
+ * GPU that loads the library holds those 2 MiB until the process exits) and calls neither
+ * cudaMalloc/cudaFree nor any allocating library routine.  `h` is only read: it supplies
+ * the weights and the layer description.
+ *
+ * Arguments are those of neon_moe_forward (all device pointers, stream-ordered).  Limit: the
+ * intermediates of T tokens must fit the array - T*top_k*(4*inter + 4*hidden + 16) bytes plus
+ * small tables, i.e. T <= 22 at hidden = inter = 2880, top_k = 4.  Larger T is rejected
+ * with NEON_MOE_EINVAL and a message naming both sizes; nothing is launched then.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ * make that first call before starting any stream capture.  All calls on a GPU share the
+ * one array and it keeps the previous call's contents: every pass rewrites each table
+ * entry it later reads, so nothing has to start at zero, but two calls whose kernels can
+ * overlap on the GPU (different streams, no ordering between them) race on it - order them.
+ * Errors are reported through neon_moe_last_error(NULL). */
+int neon_moe_forward_static(const neon_moe_handle* h, const void* hidden_bf16, int T,
+                            const float* logit_bias, float* out_f32, int32_t* topk_idx, float* topk_w,
+                            void* cuda_stream);
+
 /* Host copies of the dispatch arrays of the most recent forward on this handle
  * (synchronises the handle's last stream): count[E_local], offset[E_local+1],
  * perm[n] (sorted position -> entry t*k+s) and inv[n], n = *n_entries.  NULLs skipped.
@@ -115,7 +144,8 @@ int neon_moe_read_profile(neon_moe_handle* h, double* ms, int* n_forwards);
 /* Number of kernel launches the handle has issued since creation (for launch accounting). */
 int64_t neon_moe_launch_count(const neon_moe_handle* h);
 
-/* Text of the last error on this handle (or of the last failed create when h == NULL).
+/* Text of the last error on this handle (h == NULL: of this thread's last failed
+ * neon_moe_create or neon_moe_forward_static).
  * Owned by the library; valid until the next call on the handle. */
 const char* neon_moe_last_error(const neon_moe_handle* h);
 

@@ -28,6 +28,7 @@ SIGNATURES = {
     "neon_moe_create": (c_int, [ctypes.POINTER(NeonMoeConfig), ctypes.POINTER(c_void_p)]),
     "neon_moe_set_weights": (c_int, [c_void_p] * 9 + [c_int]),
     "neon_moe_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "neon_moe_forward_static": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_forward_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_read_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int)]),
     "neon_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_int)]),

@@ -367,3 +367,115 @@ int neon_moe_status(neon_moe_handle* h, int* word) {
 }
 
 }  // extern "C"
+
+// =======================================================================================
+// Allocation-free variant of the layer pass.
+//
+// neon_moe_forward keeps its intermediates (routing, dispatch arrays, the SwiGLU
+// activations and the per-slot down rows) in workspaces that neon_moe_create obtained from
+// cudaMalloc, sized by max_tokens.  The variant below keeps the same intermediates in one
+// fixed array that is part of the loaded library image, so a pass needs no allocation that
+// belongs to the calling thread or handle.
+// =======================================================================================
+namespace {
+
+constexpr size_t kStaticScratchBytes = 2u << 20;  // 2 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace
+
+extern "C" int neon_moe_forward_static(const neon_moe_handle* h, const void* hidden, int T,
+                                       const float* logit_bias, float* out, int32_t* topk_idx, float* topk_w,
+                                       void* cuda_stream) {
+    if (!h) return fail(nullptr, NEON_MOE_EINVAL, "null handle");
+    if (!h->has_weights) return fail(nullptr, NEON_MOE_ESTATE, "forward_static before set_weights");
+    if (h->cfg.ep_size != 1) return fail(nullptr, NEON_MOE_ESTATE, "forward_static needs ep_size == 1");
+    if (T < 0) return fail(nullptr, NEON_MOE_EINVAL, "negative T");
+    if (T == 0) return NEON_MOE_OK;
+    if (!hidden || !out) return fail(nullptr, NEON_MOE_EINVAL, "null hidden/out");
+    const int H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts, k = h->cfg.top_k;
+    const size_t n = (size_t)T * k;
+    // carve the scratch: every piece starts on a 256-byte boundary
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align256(off + bytes); return o; };
+    const size_t o_idx = take(n * 4), o_rw = take(n * 4), o_count = take((size_t)E * 4),
+                 o_offset = take((size_t)(E + 1) * 4), o_perm = take(n * 4), o_inv = take(n * 4),
+                 o_ahi = take(n * I * 2), o_alo = take(n * I * 2), o_y = take(n * H * 4);
+    if (off > kStaticScratchBytes)
+        return fail(nullptr, NEON_MOE_EINVAL,
+                    "forward_static: T=%d needs %zu bytes of scratch, the built-in array holds %zu; "
+                    "use neon_moe_forward for larger batches", T, off, kStaticScratchBytes);
+    const int dev = h->cfg.device;
+    if (dev < 0 || dev >= kMaxDevices) return fail(nullptr, NEON_MOE_EINVAL, "device ordinal beyond %d", kMaxDevices);
+    cudaError_t ce = cudaSetDevice(dev);
+    if (ce != cudaSuccess) return fail(nullptr, NEON_MOE_ECUDA, "cudaSetDevice failed: %s", cudaGetErrorString(ce));
+    if (!g_static_scratch_addr[dev]) {
+        // The array's name is only a host-side stand-in; kernels need its device address,
+        // looked up once per device with that device current.
+        void* p = nullptr;
+        ce = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (ce != cudaSuccess || !p)
+            return fail(nullptr, NEON_MOE_ECUDA, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(ce));
+        g_static_scratch_addr[dev] = p;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_static_scratch_addr[dev]);
+    int32_t* s_idx = reinterpret_cast<int32_t*>(base + o_idx);
+    float* s_rw = reinterpret_cast<float*>(base + o_rw);
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+
+    router_topk_kernel<256><<<T, 256, (H + E) * sizeof(float), st>>>(
+        static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, s_idx, s_rw);
+    DispatchArrays d{reinterpret_cast<int32_t*>(base + o_count), reinterpret_cast<int32_t*>(base + o_offset),
+                     reinterpret_cast<int32_t*>(base + o_perm), reinterpret_cast<int32_t*>(base + o_inv)};
+    dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(s_idx, (int)n, 0, E, d);
+
+    ExpertParams p{};
+    p.offset = d.offset;
+    p.perm = d.perm;
+    p.top_k = k;
+    p.x = static_cast<const uint16_t*>(hidden);
+    p.a_hi = reinterpret_cast<uint16_t*>(base + o_ahi);
+    p.a_lo = reinterpret_cast<uint16_t*>(base + o_alo);
+    p.limit = h->cfg.swiglu_limit;
+    p.alpha = h->cfg.swiglu_alpha;
+    p.route_w = s_rw;
+    p.y = reinterpret_cast<float*>(base + o_y);
+    constexpr int WARPS = 4;
+    const dim3 block(32 * WARPS);
+    p.wq = h->gu_wq; p.sq = h->gu_sq; p.bias = h->gu_bias;
+    p.rows = 2 * I; p.K = H; p.tiles = 2 * I / 16; p.nbp = H / 64;
+    {
+        dim3 grid((p.tiles + WARPS - 1) / WARPS, E);
+        if (T <= 8) expert_mma_kernel<1, true, WARPS><<<grid, block, 0, st>>>(p);
+        else if (T <= 16) expert_mma_kernel<2, true, WARPS><<<grid, block, 0, st>>>(p);
+        else if (T <= 32) expert_mma_kernel<4, true, WARPS><<<grid, block, 0, st>>>(p);
+        else expert_mma_kernel<8, true, WARPS><<<grid, block, 0, st>>>(p);
+    }
+    p.wq = h->dn_wq; p.sq = h->dn_sq; p.bias = h->dn_bias;
+    p.rows = H; p.K = I; p.tiles = H / 16; p.nbp = I / 64;
+    {
+        dim3 grid((p.tiles + WARPS - 1) / WARPS, E);
+        if (T <= 8) expert_mma_kernel<1, false, WARPS><<<grid, block, 0, st>>>(p);
+        else if (T <= 16) expert_mma_kernel<2, false, WARPS><<<grid, block, 0, st>>>(p);
+        else if (T <= 32) expert_mma_kernel<4, false, WARPS><<<grid, block, 0, st>>>(p);
+        else expert_mma_kernel<8, false, WARPS><<<grid, block, 0, st>>>(p);
+    }
+    dim3 cgrid((H / 4 + 127) / 128, T);
+    combine_kernel<<<cgrid, 128, 0, st>>>(p.y, d.inv, T, H, k, out);
+    if (topk_idx) {
+        ce = cudaMemcpyAsync(topk_idx, s_idx, n * 4, cudaMemcpyDeviceToDevice, st);
+        if (ce != cudaSuccess) return fail(nullptr, NEON_MOE_ECUDA, "copy of topk_idx failed: %s", cudaGetErrorString(ce));
+    }
+    if (topk_w) {
+        ce = cudaMemcpyAsync(topk_w, s_rw, n * 4, cudaMemcpyDeviceToDevice, st);
+        if (ce != cudaSuccess) return fail(nullptr, NEON_MOE_ECUDA, "copy of topk_w failed: %s", cudaGetErrorString(ce));
+    }
+    ce = cudaGetLastError();
+    if (ce != cudaSuccess) return fail(nullptr, NEON_MOE_ECUDA, "launch failed: %s", cudaGetErrorString(ce));
+    return NEON_MOE_OK;
+}

@@ -70,6 +70,31 @@ class MoeLayerSystem:
         self._check(rc, "neon_moe_forward")
         return (out, idx, w) if want_routing else out
 
+    def run_static(self, hidden, logit_bias=None, out=None, want_routing=False, stream=None):
+        """Same pass as ``run`` through ``neon_moe_forward_static``: the intermediates live
+        in the library's built-in 2 MiB device array instead of this handle's workspaces, so
+        the call allocates nothing (``out`` and the routing tensors are the caller's; pass
+        them in to avoid even torch's allocator).  Small batches only (T <= 22 at the
+        gpt-oss shapes); calls that can overlap on one GPU must be ordered by the caller."""
+        import torch
+        T = hidden.shape[0]
+        assert hidden.is_cuda and hidden.is_contiguous() and hidden.element_size() == 2
+        dev = hidden.device
+        if out is None:
+            out = torch.empty((T, self.shape.hidden), dtype=torch.float32, device=dev)
+        idx = w = None
+        if want_routing:
+            idx = torch.empty((T, self.shape.top_k), dtype=torch.int32, device=dev)
+            w = torch.empty((T, self.shape.top_k), dtype=torch.float32, device=dev)
+        st = (stream or torch.cuda.current_stream(dev)).cuda_stream
+        rc = self._lib.neon_moe_forward_static(self._h, hidden.data_ptr(), T,
+                                               None if logit_bias is None else logit_bias.data_ptr(),
+                                               out.data_ptr(), None if idx is None else idx.data_ptr(),
+                                               None if w is None else w.data_ptr(), st)
+        if rc != 0:
+            raise RuntimeError(f"neon_moe_forward_static failed ({rc}): {self._lib.neon_moe_last_error(None).decode()}")
+        return (out, idx, w) if want_routing else out
+
     # -- host path -----------------------------------------------------------------------
     def run_host(self, hidden: np.ndarray, logit_bias: np.ndarray | None = None, out: np.ndarray | None = None,
                  want_routing: bool = False):

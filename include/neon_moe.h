@@ -132,6 +132,13 @@ int neon_moe_read_dispatch(neon_moe_handle* h, int32_t* count, int32_t* offset, 
  * wait.  Synchronises the handle's last stream. */
 int neon_moe_status(neon_moe_handle* h, int* device_status_word);
 
+/* Tuning / test switches.  "path": 2 (default on sm_100) = TMA + tcgen05 block-scaled
+ * grouped GEMM, 1 = the mma.sync kernels.  "a_tx_bytes": bytes a 128x128 4-bit TMA box
+ * reports to its mbarrier (default 8192).
+ * Follows: the literal knobs the engine's apps set before running a system,
+ * NeonEngine/src/raytracing_app.cpp:605-631. */
+int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value);
+
 /* Per-stage device timing.  enable != 0 makes every following forward record CUDA events
  * around its stages on the caller's stream; neon_moe_read_profile synchronises, adds the
  * elapsed times of all forwards since the last read into ms[4] = {router+dispatch, gate_up,

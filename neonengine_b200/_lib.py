@@ -32,6 +32,7 @@ SIGNATURES = {
     "neon_moe_forward_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_read_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int)]),
     "neon_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    "neon_moe_set_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.c_int64]),
     "neon_moe_profile": (c_int, [c_void_p, c_int]),
     "neon_moe_read_profile": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
     "neon_moe_launch_count": (ctypes.c_int64, [c_void_p]),

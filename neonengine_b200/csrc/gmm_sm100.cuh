@@ -1,0 +1,378 @@
+// Grouped block-scaled expert GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma with
+// TMEM accumulators, plus the weight re-tiling, token-tile list and activation splitting
+// kernels around it.
+//
+// Orientation ("swap-AB"): the 128 weight rows of an item are the M operand (one TMEM lane
+// per row), the item's tokens are the N operand (16..128 columns).  Weights stay MXFP4 in HBM
+// (4 bits + one E8M0 byte per 32); TMA expands the nibbles into the 8-bit containers that
+// tcgen05.mma.kind::mxf8f6f4 reads, and the tensor core applies the E8M0 block scales, so no
+// CUDA-core instruction touches a weight.  Activations are split into TERMS e4m3 terms with
+// their own E8M0 block scales (bf16 = 2 terms exactly, fp32 SwiGLU output = 4 terms, error
+// <= 2^-16 relative); each term is one more accumulating MMA.
+#pragma once
+#include <cuda_fp8.h>
+
+#include "moe_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace neon {
+
+constexpr int kChunkK = 128;  // K elements per pipeline stage (one 128-byte swizzle row)
+
+__host__ __device__ inline int round_up_int(int v, int m) { return (v + m - 1) / m * m; }
+
+// ---------------------------------------------------------------------------------------
+// "tc" weight format.  Nibbles: [E][rows][Kp/2] bytes, Kp = K rounded up to 128, pad = 0.
+// gate_up rows are permuted so that TMEM lane quarter q of tile m holds 16 gate rows (lanes
+// 0..15: channels 64m+16q+l) followed by their 16 linear rows (lanes 16..31): SwiGLU is then
+// one warp shuffle away.  Scales: [E][m_tiles][n_chunks][512 B] atoms, byte
+// (r%32)*16 + (r/32)*4 + kb for tile row r and k-block kb of the chunk - the layout that
+// tcgen05.cp.32x128b.warpx4 turns into the TMEM scale-factor format.  Pads hold 127 (1.0).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ int tc_source_row(int r, int gate_up) {
+    if (!gate_up) return r;
+    int m = r >> 7, q = (r >> 5) & 3, l = r & 31;
+    int ch = 64 * m + 16 * q + (l & 15);
+    return 2 * ch + (l >> 4);
+}
+
+__global__ void repack_tc_kernel(const uint8_t* __restrict__ blocks, const uint8_t* __restrict__ scales, int n_experts,
+                                 int rows, int K, int gate_up, uint8_t* __restrict__ wt, uint8_t* __restrict__ sfa) {
+    const int Kp = round_up_int(K, kChunkK), pitch16 = Kp / 32;  // 16-byte units per output row
+    const long long total = (long long)n_experts * rows * pitch16;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        int u = (int)(i % pitch16);
+        long long rr = i / pitch16;
+        int r = (int)(rr % rows), e = (int)(rr / rows);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (u * 16 < K / 2)
+            v = *reinterpret_cast<const uint4*>(blocks + ((size_t)e * rows + tc_source_row(r, gate_up)) * (K / 2) + u * 16);
+        *reinterpret_cast<uint4*>(wt + ((size_t)e * rows + r) * (Kp / 2) + u * 16) = v;
+    }
+    const int m_tiles = (rows + 127) / 128, n_chunks = Kp / kChunkK;
+    const long long total_sf = (long long)n_experts * m_tiles * n_chunks * 128;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_sf;
+         i += (long long)gridDim.x * blockDim.x) {
+        int r = (int)(i % 128);
+        long long rr = i / 128;
+        int c = (int)(rr % n_chunks);
+        rr /= n_chunks;
+        int m = (int)(rr % m_tiles), e = (int)(rr / m_tiles);
+        int row = 128 * m + r;
+        uint32_t word = 0;
+        for (int kb = 0; kb < 4; ++kb) {
+            int blk = 4 * c + kb;
+            uint32_t byte = 127;
+            if (row < rows && blk < K / 32) byte = scales[((size_t)e * rows + tc_source_row(row, gate_up)) * (K / 32) + blk];
+            word |= byte << (8 * kb);
+        }
+        *reinterpret_cast<uint32_t*>(sfa + (((size_t)e * m_tiles + m) * n_chunks + c) * 512 + (r & 31) * 16 + (r >> 5) * 4) = word;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Token tiles: each expert's run of sorted rows is cut into tiles of at most `tile_tokens`
+// rows.  One CTA; writes the tile list, *n_tiles and the tile of every sorted row.
+// ---------------------------------------------------------------------------------------
+struct TileList {
+    int32_t* expert;    // [cap]
+    int32_t* row0;      // [cap] first sorted row
+    int32_t* rows;      // [cap] rows in the tile (1..tile_tokens)
+    int32_t* n_tiles;   // [1]
+    int32_t* row_tile;  // [n] tile of each sorted row
+};
+
+__global__ void __launch_bounds__(1024) build_tiles_kernel(const int32_t* __restrict__ offset, int n_local,
+                                                           int tile_tokens, TileList tl) {
+    __shared__ int s_first[kMaxExperts + 1];  // first tile index of each expert
+    if (threadIdx.x == 0) {
+        int nt = 0;
+        for (int e = 0; e < n_local; ++e) {
+            s_first[e] = nt;
+            int lo = offset[e], hi = offset[e + 1];
+            for (int r = lo; r < hi; r += tile_tokens) {
+                tl.expert[nt] = e;
+                tl.row0[nt] = r;
+                tl.rows[nt] = min(tile_tokens, hi - r);
+                ++nt;
+            }
+        }
+        s_first[n_local] = nt;
+        *tl.n_tiles = nt;
+    }
+    __syncthreads();
+    for (int e = 0; e < n_local; ++e) {
+        int lo = offset[e], hi = offset[e + 1];
+        for (int r = lo + threadIdx.x; r < hi; r += blockDim.x) tl.row_tile[r] = s_first[e] + (r - lo) / tile_tokens;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Activation splitting.  One warp per (sorted row p, 128-wide K chunk); lane l owns 4
+// elements.  Term t: per 32-block scale 2^(floor(log2 amax) - 7) (E8M0), value rounded to
+// e4m3, remainder carried to the next term.  Output planes q[t][p][Kp] (bytes) and scale
+// atoms sfb[t][tile][chunk][512] indexed by the row's position inside its token tile.
+// FROM_BF16: source rows are bf16 hidden states gathered through perm (token = perm[p]/k);
+// otherwise fp32 rows [p][K].
+// ---------------------------------------------------------------------------------------
+template <int TERMS, bool FROM_BF16>
+__global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm,
+                                                         int top_k, int K, int n_rows, const int32_t* __restrict__ row_tile,
+                                                         const int32_t* __restrict__ tile_row0, uint8_t* __restrict__ q,
+                                                         size_t q_plane, uint8_t* __restrict__ sfb, size_t sfb_plane) {
+    const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows * n_chunks) return;
+    const int p = warp / n_chunks, c = warp % n_chunks;
+    const int k0 = c * kChunkK + 4 * lane;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k0 < K) {
+        if (FROM_BF16) {
+            const uint16_t* row = static_cast<const uint16_t*>(src) + (size_t)(perm[p] / top_k) * K;
+            uint2 raw = *reinterpret_cast<const uint2*>(row + k0);
+            v[0] = __uint_as_float(raw.x << 16);
+            v[1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[2] = __uint_as_float(raw.y << 16);
+            v[3] = __uint_as_float(raw.y & 0xffff0000u);
+        } else {
+            float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)p * K + k0);
+            v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+        }
+    }
+    const int tile = row_tile[p], j = p - tile_row0[tile];
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+        int sb = amax > 0.f ? max(ef - 7, 0) : 127;           // E8M0 byte: amax / scale in [128, 256)
+        float inv = __uint_as_float((uint32_t)(254 - sb) << 23);
+        float scale = sb > 0 ? __uint_as_float((uint32_t)sb << 23) : __uint_as_float(0x00400000u);
+        __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
+        __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+        *reinterpret_cast<uint32_t*>(q + t * q_plane + (size_t)p * Kp + k0) = (uint32_t)lo | ((uint32_t)hi << 16);
+        if (t + 1 < TERMS) {
+            __half2_raw blo = __nv_cvt_fp8x2_to_halfraw2(lo, __NV_E4M3), bhi = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
+            float2 flo = __half22float2(*reinterpret_cast<__half2*>(&blo)), fhi = __half22float2(*reinterpret_cast<__half2*>(&bhi));
+            v[0] -= flo.x * scale; v[1] -= flo.y * scale; v[2] -= fhi.x * scale; v[3] -= fhi.y * scale;
+        }
+        uint32_t w = (uint32_t)sb;
+        w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 8) << 8;
+        w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 16) << 16;
+        w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 24) << 24;
+        if (lane == 0)
+            *reinterpret_cast<uint32_t*>(sfb + t * sfb_plane + ((size_t)tile * n_chunks + c) * 512 + (j & 31) * 16 + (j >> 5) * 4) = w;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// The GEMM.  Persistent CTAs (one per SM) walk items = (token tile, 128-row weight tile),
+// item index = blockIdx.x + i*gridDim.x, weight tile fastest so that concurrent CTAs share
+// a token tile's activations in L2.  Six warps: 0 = TMA producer, 1 = MMA issuer,
+// 2..5 = epilogue (TMEM lane quarter = warp % 4).  Per K chunk one stage holds the A tile
+// (128 x 128 containers, 16 KB), TERMS activation planes (BN_MAX x 128 bytes each) and their
+// scale atoms.  Accumulators are double-buffered in TMEM so the epilogue of item i overlaps
+// the MMAs of item i+1.  Every wait is bounded: on a timeout the CTA records a code in
+// *status, all roles leave their loops, in-flight copies get time to land, TMEM is freed.
+// ---------------------------------------------------------------------------------------
+struct GmmParams {
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    size_t sfb_plane;
+    const int32_t *tile_expert, *tile_row0, *tile_rows, *n_tiles;
+    int m_tiles, n_chunks, rows_total;
+    uint32_t a_tx_bytes;
+    const uint16_t* bias;  // [E][rows_total], original row order
+    // gate_up epilogue
+    float* a_out;          // [n][inter] fp32
+    int inter;
+    float limit, alpha;
+    // down epilogue
+    const int32_t* perm;
+    const float* route_w;
+    float* y;              // [n][hidden] fp32, sorted order
+    int hidden;
+    int* status;
+};
+
+template <int BN_MAX, int TERMS>
+struct GmmSmem {
+    static constexpr int kBPlane = BN_MAX * 128;
+    static constexpr int kStage = (16384 + TERMS * kBPlane + 512 * (1 + TERMS) + 1023) / 1024 * 1024;
+    static constexpr int kTail = 1024;
+    static constexpr int kBudget = 225 * 1024;
+    static constexpr int kStagesFit = (kBudget - kTail - 1024) / kStage;
+    static constexpr int kStagesTmem = 256 / (4 * (1 + TERMS));
+    static constexpr int kStages = kStagesFit < kStagesTmem ? kStagesFit : kStagesTmem;
+    static constexpr int kBytes = kStages * kStage + kTail + 1024;
+};
+
+constexpr long long kWaitLimitCycles = 400000000ll;  // ~0.2 s at 2 GHz
+
+template <int BN_MAX, int TERMS, bool GATE_UP>
+__global__ void __launch_bounds__(192, 1)
+gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GmmParams p) {
+    using namespace sm100;
+    using L = GmmSmem<BN_MAX, TERMS>;
+    constexpr int STAGES = L::kStages;
+    constexpr int SF_COLS = 4 * (1 + TERMS);
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStage);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 2) tmem_alloc(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int n_items = *p.n_tiles * p.m_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+                const int tile = item / p.m_tiles, m = item % p.m_tiles;
+                const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
+                const int nboxes = (rows + 7) >> 3;
+                const uint32_t tx = p.a_tx_bytes + 512 + TERMS * (nboxes * 1024 + 512);
+                for (int c = 0; c < p.n_chunks; ++c, ++it) {
+                    const int s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles)) goto done;
+                    uint8_t* st = smem + s * L::kStage;
+                    mbar_expect_tx(&full[s], tx);
+                    tma_load_3d(st, &tmA, &full[s], c * kChunkK, m * 128, e);
+                    bulk_load(st + 16384 + TERMS * L::kBPlane,
+                              p.sfa + (((size_t)e * p.m_tiles + m) * p.n_chunks + c) * 512, 512, &full[s]);
+#pragma unroll
+                    for (int t = 0; t < TERMS; ++t) {
+                        for (int b = 0; b < nboxes; ++b)
+                            tma_load_3d(st + 16384 + t * L::kBPlane + b * 1024, &tmB, &full[s], c * kChunkK, row0 + 8 * b, t);
+                        bulk_load(st + 16384 + TERMS * L::kBPlane + 512 * (1 + t),
+                                  p.sfb + t * p.sfb_plane + ((size_t)tile * p.n_chunks + c) * 512, 512, &full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, iter = 0;
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
+                const int tile = item / p.m_tiles;
+                const int rows = p.tile_rows[tile];
+                const uint32_t n_mma = (uint32_t)max(16, round_up_int(rows, 16));
+                const int b = iter & 1, aph = (iter >> 1) & 1;
+                if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles)) goto done;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + b * BN_MAX;
+                for (int c = 0; c < p.n_chunks; ++c, ++it) {
+                    const int s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles)) goto done;
+                    tc_fence_after();
+                    uint8_t* st = smem + s * L::kStage;
+                    const uint32_t sf_tmem = tmem_base + 256 + s * SF_COLS;
+                    const uint32_t sf_smem = smem_u32(st + 16384 + TERMS * L::kBPlane);
+                    tc_copy_sf(sf_tmem, make_sf_desc(sf_smem));
+#pragma unroll
+                    for (int t = 0; t < TERMS; ++t) tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(sf_smem + 512 * (1 + t)));
+                    const uint64_t a_desc = make_sw128_desc(smem_u32(st));
+#pragma unroll
+                    for (int t = 0; t < TERMS; ++t) {
+                        const uint64_t b_desc = make_sw128_desc(smem_u32(st + 16384 + t * L::kBPlane));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, make_idesc_bs(5, 0, n_mma, j, j), sf_tmem,
+                                         sf_tmem + 4 * (1 + t), (uint32_t)(c | t | j));
+                    }
+                    tc_commit(&empty[s]);
+                }
+                tc_commit(&acc_full[b]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int iter = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
+            const int tile = item / p.m_tiles, m = item % p.m_tiles;
+            const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
+            const int b = iter & 1, aph = (iter >> 1) & 1;
+            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN_MAX;
+            const int ncol = max(16, round_up_int(rows, 16));
+            if (GATE_UP) {
+                // lanes 0..15: gate rows of channels ch0 + lane; lanes 16..31: their linear rows
+                const int ch = 64 * m + 16 * q + (lane & 15);
+                const float bias = bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + 2 * ch + (lane >> 4)]);
+                for (int c16 = 0; c16 < ncol; c16 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c16, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float mine = v[i] + bias;
+                        float lin = __shfl_down_sync(0xffffffffu, mine, 16);
+                        if (lane < 16 && c16 + i < rows) {
+                            float g = fminf(mine, p.limit);
+                            float l = fminf(fmaxf(lin, -p.limit), p.limit);
+                            p.a_out[(size_t)(row0 + c16 + i) * p.inter + ch] = g / (1.f + expf(-p.alpha * g)) * (l + 1.f);
+                        }
+                    }
+                }
+            } else {
+                const int row = 128 * m + 32 * q + lane;
+                const bool valid = row < p.rows_total;
+                const float bias = valid ? bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + row]) : 0.f;
+                for (int c16 = 0; c16 < ncol; c16 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c16, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (valid && c16 + i < rows) {
+                            const int pos = row0 + c16 + i;
+                            p.y[(size_t)pos * p.hidden + row] = p.route_w[p.perm[pos]] * (v[i] + bias);
+                        }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);
+        }
+    }
+done:
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // leave time for copies that were already issued to land before the CTA retires
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000ll) {}
+    }
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace neon

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "moe_kernels.cuh"
+#include "gmm_sm100.cuh"
 
 using namespace neon;
 
@@ -32,6 +33,7 @@ struct neon_moe_handle {
     cudaStream_t last_stream = nullptr;
     cudaStream_t own_stream = nullptr;
     int last_n = 0;
+    int n_sms = 148;
     // weights
     uint16_t *router_w = nullptr, *router_b = nullptr, *gu_bias = nullptr, *dn_bias = nullptr;
     uint4 *gu_wq = nullptr, *dn_wq = nullptr;
@@ -41,6 +43,15 @@ struct neon_moe_handle {
     float *route_w = nullptr, *y = nullptr;
     uint16_t *a_hi = nullptr, *a_lo = nullptr;
     int* status = nullptr;
+    // tensor-core path: "tc" weights, tensor maps, activation-term planes, token tiles
+    int path = 2;                 // 1 = mma.sync kernels, 2 = TMA + tcgen05 block-scaled GEMM
+    uint32_t a_tx_bytes = 8192;   // bytes one 128x128 4-bit box adds to its mbarrier
+    uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
+    uint8_t *xq = nullptr, *x_sfb = nullptr, *aq = nullptr, *a_sfb = nullptr;
+    float* a_f32 = nullptr;
+    int32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_tiles = nullptr, *row_tile = nullptr;
+    int tile_cap = 0, kp_h = 0, kp_i = 0;
+    CUtensorMap tm_gu{}, tm_dn{}, tm_x{}, tm_a{};
     // per-stage profiling: 5 events per forward
     bool profiling = false;
     std::vector<cudaEvent_t> events;
@@ -78,7 +89,9 @@ int dev_alloc(neon_moe_handle* h, T** p, size_t count) {
 void free_all(neon_moe_handle* h) {
     void* ptrs[] = {h->router_w, h->router_b, h->gu_bias, h->dn_bias, h->gu_wq, h->dn_wq, h->gu_sq, h->dn_sq,
                     h->idx, h->count, h->offset, h->perm, h->inv, h->route_w, h->y, h->a_hi, h->a_lo,
-                    h->status, h->st_hidden, h->st_out, h->st_bias};
+                    h->status, h->st_hidden, h->st_out, h->st_bias, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
+                    h->xq, h->x_sfb, h->aq, h->a_sfb, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
+                    h->n_tiles, h->row_tile};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);
@@ -86,6 +99,7 @@ void free_all(neon_moe_handle* h) {
 }
 
 constexpr size_t kMaxProfiledForwards = 4096;
+constexpr int kMaxDevicesAttr = 64;
 
 // Records the next profiling event on `st` (no-op unless profiling is on and room is left).
 void mark(neon_moe_handle* h, cudaStream_t st, bool active) {
@@ -140,6 +154,95 @@ int copy_in(neon_moe_handle* h, uint16_t** dst, const void* src, size_t count, i
     }
     CU(h, cudaMemcpy(*dst, src, count * 2, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
     return NEON_MOE_OK;
+}
+
+
+// ---- tensor-core path helpers -----------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// 3-D map over [dim2][dim1][dim0] with a (128, box_rows, 1) box and 128-byte swizzle.
+int make_map(neon_moe_handle* h, CUtensorMap* map, CUtensorMapDataType type, void* base, uint64_t dim0, uint64_t dim1,
+             uint64_t dim2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {dim0, dim1, dim2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {128, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, type, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return NEON_MOE_OK;
+}
+
+// Upload (when needed) and re-tile one MXFP4 matrix set into the "tc" format.
+int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* scales, int rows, int K, int gate_up,
+                   int on_device, uint8_t** wt, uint8_t** sfa, CUtensorMap* map) {
+    const int E = h->n_local;
+    const size_t nb = (size_t)E * rows * (K / 2), ns = (size_t)E * rows * (K / 32);
+    const uint8_t *d_blocks = blocks, *d_scales = scales;
+    uint8_t *tmp_b = nullptr, *tmp_s = nullptr;
+    if (!on_device) {
+        CU(h, cudaMalloc(&tmp_b, nb));
+        CU(h, cudaMalloc(&tmp_s, ns));
+        CU(h, cudaMemcpy(tmp_b, blocks, nb, cudaMemcpyHostToDevice));
+        CU(h, cudaMemcpy(tmp_s, scales, ns, cudaMemcpyHostToDevice));
+        d_blocks = tmp_b;
+        d_scales = tmp_s;
+    }
+    const int Kp = round_up_int(K, kChunkK), m_tiles = (rows + 127) / 128, n_chunks = Kp / kChunkK;
+    if (!*wt) {
+        int rc = dev_alloc(h, wt, (size_t)E * rows * (Kp / 2) + 256);
+        if (rc) return rc;
+        rc = dev_alloc(h, sfa, (size_t)E * m_tiles * n_chunks * 512);
+        if (rc) return rc;
+    }
+    repack_tc_kernel<<<148 * 8, 256>>>(d_blocks, d_scales, E, rows, K, gate_up, *wt, *sfa);
+    h->launches++;
+    CU(h, cudaGetLastError());
+    CU(h, cudaDeviceSynchronize());
+    if (tmp_b) cudaFree(tmp_b);
+    if (tmp_s) cudaFree(tmp_s);
+    return make_map(h, map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, *wt, (uint64_t)Kp, (uint64_t)rows, (uint64_t)E,
+                    (uint64_t)Kp / 2, (uint64_t)rows * (Kp / 2), 128);
+}
+
+int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 64 ? 64 : 128); }
+
+template <int BN, int TERMS, bool GATE_UP>
+int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tmA, const CUtensorMap& tmB, const GmmParams& p, cudaStream_t st) {
+    using L = GmmSmem<BN, TERMS>;
+    static bool configured[kMaxDevicesAttr] = {};
+    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP>;
+    if (!configured[h->cfg.device]) {
+        CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+        configured[h->cfg.device] = true;
+    }
+    kern<<<h->n_sms, 192, L::kBytes, st>>>(tmA, tmB, p);
+    h->launches++;
+    return NEON_MOE_OK;
+}
+
+template <int TERMS, bool GATE_UP>
+int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tmA, const CUtensorMap& tmB, const GmmParams& p,
+               cudaStream_t st) {
+    if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP>(h, tmA, tmB, p, st);
+    if (tile_tokens == 64) return launch_gmm_one<64, TERMS, GATE_UP>(h, tmA, tmB, p, st);
+    return launch_gmm_one<128, TERMS, GATE_UP>(h, tmA, tmB, p, st);
 }
 
 template <bool GATE_UP>
@@ -202,6 +305,28 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         (rc = dev_alloc(h, &h->st_out, (size_t)cfg->max_tokens * cfg->hidden)) ||
         (rc = dev_alloc(h, &h->st_bias, (size_t)cfg->n_experts)))
         return bail(rc);
+    {
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, cfg->device) != cudaSuccess)
+            return bail(fail(h, NEON_MOE_ECUDA, "cudaGetDeviceProperties failed"));
+        h->n_sms = prop.multiProcessorCount;
+        if (prop.major != 10) h->path = 1;  // tcgen05 needs sm_100
+    }
+    h->kp_h = round_up_int(cfg->hidden, kChunkK);
+    h->kp_i = round_up_int(cfg->inter, kChunkK);
+    h->tile_cap = h->n_local + (int)(n / 16) + 2;
+    const size_t nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
+    if ((rc = dev_alloc(h, &h->xq, 2 * n * h->kp_h)) || (rc = dev_alloc(h, &h->x_sfb, 2 * (size_t)h->tile_cap * nch_h * 512)) ||
+        (rc = dev_alloc(h, &h->aq, 4 * n * h->kp_i)) || (rc = dev_alloc(h, &h->a_sfb, 4 * (size_t)h->tile_cap * nch_i * 512)) ||
+        (rc = dev_alloc(h, &h->a_f32, n * cfg->inter)) || (rc = dev_alloc(h, &h->tile_expert, (size_t)h->tile_cap)) ||
+        (rc = dev_alloc(h, &h->tile_row0, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile_rows, (size_t)h->tile_cap)) ||
+        (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
+        return bail(rc);
+    if ((rc = make_map(h, &h->tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, h->xq, (uint64_t)h->kp_h, (uint64_t)n, 2, (uint64_t)h->kp_h,
+                       (uint64_t)n * h->kp_h, 8)) ||
+        (rc = make_map(h, &h->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, h->aq, (uint64_t)h->kp_i, (uint64_t)n, 4, (uint64_t)h->kp_i,
+                       (uint64_t)n * h->kp_i, 8)))
+        return bail(rc);
     if (cudaMemset(h->status, 0, 16) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
     if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(fail(h, NEON_MOE_ECUDA, "cudaStreamCreate failed"));
@@ -235,6 +360,8 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
     if ((rc = copy_in(h, &h->dn_bias, dn_bias, (size_t)EL * H, on_device))) return rc;
     if ((rc = load_matrix(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wq, &h->gu_sq))) return rc;
     if ((rc = load_matrix(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wq, &h->dn_sq))) return rc;
+    if ((rc = load_matrix_tc(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wt, &h->gu_sfa, &h->tm_gu))) return rc;
+    if ((rc = load_matrix_tc(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wt, &h->dn_sfa, &h->tm_dn))) return rc;
     CU(h, cudaDeviceSynchronize());
     h->has_weights = true;
     return NEON_MOE_OK;
@@ -262,28 +389,62 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float*
     dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->idx, n, 0, E, d);
     h->launches++;
 
-    ExpertParams p{};
-    p.offset = h->offset;
-    p.perm = h->perm;
-    p.top_k = k;
-    p.x = static_cast<const uint16_t*>(hidden);
-    p.a_hi = h->a_hi;
-    p.a_lo = h->a_lo;
-    p.limit = h->cfg.swiglu_limit;
-    p.alpha = h->cfg.swiglu_alpha;
-    p.route_w = h->route_w;
-    p.y = h->y;
-    // gate_up: rows 2I, K = H
-    p.wq = h->gu_wq; p.sq = h->gu_sq; p.bias = h->gu_bias;
-    p.rows = 2 * I; p.K = H; p.tiles = 2 * I / 16; p.nbp = H / 64;
-    mark(h, st, prof);
-    launch_expert<true>(h, p, T, st);
-    mark(h, st, prof);
-    // down: rows H, K = I
-    p.wq = h->dn_wq; p.sq = h->dn_sq; p.bias = h->dn_bias;
-    p.rows = H; p.K = I; p.tiles = H / 16; p.nbp = I / 64;
-    launch_expert<false>(h, p, T, st);
-    mark(h, st, prof);
+    if (h->path == 2) {
+        const int tt = tile_tokens_for(T);
+        TileList tl{h->tile_expert, h->tile_row0, h->tile_rows, h->n_tiles, h->row_tile};
+        build_tiles_kernel<<<1, 1024, 0, st>>>(h->offset, h->n_local, tt, tl);
+        h->launches++;
+        const int nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
+        const size_t x_plane = (size_t)h->cfg.max_tokens * k * h->kp_h, a_plane = (size_t)h->cfg.max_tokens * k * h->kp_i;
+        const size_t xs_plane = (size_t)h->tile_cap * nch_h * 512, as_plane = (size_t)h->tile_cap * nch_i * 512;
+        split_rows_kernel<2, true><<<(n * nch_h + 7) / 8, 256, 0, st>>>(hidden, h->perm, k, H, n, h->row_tile, h->tile_row0,
+                                                                        h->xq, x_plane, h->x_sfb, xs_plane);
+        h->launches++;
+        GmmParams g{};
+        g.tile_expert = h->tile_expert; g.tile_row0 = h->tile_row0; g.tile_rows = h->tile_rows; g.n_tiles = h->n_tiles;
+        g.a_tx_bytes = h->a_tx_bytes;
+        g.a_out = h->a_f32; g.inter = I; g.limit = h->cfg.swiglu_limit; g.alpha = h->cfg.swiglu_alpha;
+        g.perm = h->perm; g.route_w = h->route_w; g.y = h->y; g.hidden = H; g.status = h->status;
+        // gate_up: rows 2I, K = H
+        g.sfa = h->gu_sfa; g.sfb = h->x_sfb; g.sfb_plane = xs_plane; g.bias = h->gu_bias;
+        g.m_tiles = 2 * I / 128; g.n_chunks = nch_h; g.rows_total = 2 * I;
+        mark(h, st, prof);
+        int rc = launch_gmm<2, true>(h, tt, h->tm_gu, h->tm_x, g, st);
+        if (rc) return rc;
+        mark(h, st, prof);
+        split_rows_kernel<4, false><<<(n * nch_i + 7) / 8, 256, 0, st>>>(h->a_f32, nullptr, k, I, n, h->row_tile, h->tile_row0,
+                                                                         h->aq, a_plane, h->a_sfb, as_plane);
+        h->launches++;
+        // down: rows H, K = I
+        g.sfa = h->dn_sfa; g.sfb = h->a_sfb; g.sfb_plane = as_plane; g.bias = h->dn_bias;
+        g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
+        rc = launch_gmm<4, false>(h, tt, h->tm_dn, h->tm_a, g, st);
+        if (rc) return rc;
+        mark(h, st, prof);
+    } else {
+        ExpertParams p{};
+        p.offset = h->offset;
+        p.perm = h->perm;
+        p.top_k = k;
+        p.x = static_cast<const uint16_t*>(hidden);
+        p.a_hi = h->a_hi;
+        p.a_lo = h->a_lo;
+        p.limit = h->cfg.swiglu_limit;
+        p.alpha = h->cfg.swiglu_alpha;
+        p.route_w = h->route_w;
+        p.y = h->y;
+        // gate_up: rows 2I, K = H
+        p.wq = h->gu_wq; p.sq = h->gu_sq; p.bias = h->gu_bias;
+        p.rows = 2 * I; p.K = H; p.tiles = 2 * I / 16; p.nbp = H / 64;
+        mark(h, st, prof);
+        launch_expert<true>(h, p, T, st);
+        mark(h, st, prof);
+        // down: rows H, K = I
+        p.wq = h->dn_wq; p.sq = h->dn_sq; p.bias = h->dn_bias;
+        p.rows = H; p.K = I; p.tiles = H / 16; p.nbp = I / 64;
+        launch_expert<false>(h, p, T, st);
+        mark(h, st, prof);
+    }
 
     dim3 cgrid((H / 4 + 127) / 128, T);
     combine_kernel<<<cgrid, 128, 0, st>>>(h->y, h->inv, T, H, k, out);
@@ -331,6 +492,19 @@ int neon_moe_read_dispatch(neon_moe_handle* h, int32_t* count, int32_t* offset, 
     if (offset) CU(h, cudaMemcpy(offset, h->offset, (size_t)(EL + 1) * 4, cudaMemcpyDeviceToHost));
     if (perm) CU(h, cudaMemcpy(perm, h->perm, (size_t)n * 4, cudaMemcpyDeviceToHost));
     if (inv) CU(h, cudaMemcpy(inv, h->inv, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return NEON_MOE_OK;
+}
+
+int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
+    if (!h || !name) return NEON_MOE_EINVAL;
+    if (!strcmp(name, "path")) {
+        if (value != 1 && value != 2) return fail(h, NEON_MOE_EINVAL, "path must be 1 (mma.sync) or 2 (tcgen05)");
+        h->path = (int)value;
+    } else if (!strcmp(name, "a_tx_bytes")) {
+        h->a_tx_bytes = (uint32_t)value;
+    } else {
+        return fail(h, NEON_MOE_EINVAL, "unknown option '%s'", name);
+    }
     return NEON_MOE_OK;
 }
 

@@ -129,6 +129,9 @@ class MoeLayerSystem:
                     "read_dispatch")
         return count, offset, perm, inv
 
+    def set_option(self, name: str, value: int) -> None:
+        self._check(self._lib.neon_moe_set_option(self._h, name.encode(), int(value)), "neon_moe_set_option")
+
     def profile(self, enable: bool) -> None:
         self._check(self._lib.neon_moe_profile(self._h, int(enable)), "neon_moe_profile")
 

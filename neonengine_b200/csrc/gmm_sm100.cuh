@@ -22,7 +22,9 @@ constexpr int kChunkK = 128;  // K elements per pipeline stage (one 128-byte swi
 __host__ __device__ inline int round_up_int(int v, int m) { return (v + m - 1) / m * m; }
 
 // ---------------------------------------------------------------------------------------
-// "tc" weight format.  Nibbles: [E][rows][Kp/2] bytes, Kp = K rounded up to 128, pad = 0.
+// "tc" weight format.  Nibbles are stored box by box: [E][m_tiles][n_chunks][128 rows][64 B],
+// so the 128-row x 128-column box one TMA operation fetches is 8 KB of contiguous HBM.
+// Kp = K rounded up to 128 and rows rounded up to 128 are padded with zero nibbles.
 // gate_up rows are permuted so that TMEM lane quarter q of tile m holds 16 gate rows (lanes
 // 0..15: channels 64m+16q+l) followed by their 16 linear rows (lanes 16..31): SwiGLU is then
 // one warp shuffle away.  Scales: [E][m_tiles][n_chunks][512 B] atoms, byte
@@ -38,19 +40,23 @@ __device__ __forceinline__ int tc_source_row(int r, int gate_up) {
 
 __global__ void repack_tc_kernel(const uint8_t* __restrict__ blocks, const uint8_t* __restrict__ scales, int n_experts,
                                  int rows, int K, int gate_up, uint8_t* __restrict__ wt, uint8_t* __restrict__ sfa) {
-    const int Kp = round_up_int(K, kChunkK), pitch16 = Kp / 32;  // 16-byte units per output row
-    const long long total = (long long)n_experts * rows * pitch16;
+    const int Kp = round_up_int(K, kChunkK);
+    const int m_tiles = (rows + 127) / 128, n_chunks = Kp / kChunkK;
+    const long long total = (long long)n_experts * m_tiles * n_chunks * 128 * 4;  // 16-byte units
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
-        int u = (int)(i % pitch16);
-        long long rr = i / pitch16;
-        int r = (int)(rr % rows), e = (int)(rr / rows);
+        int u = (int)(i & 3);
+        int r = (int)((i >> 2) & 127);
+        long long rr = i >> 9;
+        int c = (int)(rr % n_chunks);
+        rr /= n_chunks;
+        int m = (int)(rr % m_tiles), e = (int)(rr / m_tiles);
+        int row = 128 * m + r, byte0 = c * 64 + u * 16;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (u * 16 < K / 2)
-            v = *reinterpret_cast<const uint4*>(blocks + ((size_t)e * rows + tc_source_row(r, gate_up)) * (K / 2) + u * 16);
-        *reinterpret_cast<uint4*>(wt + ((size_t)e * rows + r) * (Kp / 2) + u * 16) = v;
+        if (row < rows && byte0 < K / 2)
+            v = *reinterpret_cast<const uint4*>(blocks + ((size_t)e * rows + tc_source_row(row, gate_up)) * (K / 2) + byte0);
+        reinterpret_cast<uint4*>(wt)[i] = v;
     }
-    const int m_tiles = (rows + 127) / 128, n_chunks = Kp / kChunkK;
     const long long total_sf = (long long)n_experts * m_tiles * n_chunks * 128;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_sf;
          i += (long long)gridDim.x * blockDim.x) {
@@ -111,16 +117,31 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const int32_t* __rest
 // ---------------------------------------------------------------------------------------
 // Activation splitting.  One warp per (sorted row p, 128-wide K chunk); lane l owns 4
 // elements.  Term t: per 32-block scale 2^(floor(log2 amax) - 7) (E8M0), value rounded to
-// e4m3, remainder carried to the next term.  Output planes q[t][p][Kp] (bytes) and scale
-// atoms sfb[t][tile][chunk][512] indexed by the row's position inside its token tile.
+// e4m3, remainder carried to the next term.
+//
+// Output: one block per (token tile, chunk), written as the exact shared-memory image the
+// GEMM stage wants, so a single bulk copy brings in all terms and their scales:
+//   [TERMS x 512 B scale atoms][row group 0: term 0 | term 1 | ...][row group 1: ...] ...
+// A row group is 8 rows x 128 B of one term in the 128-byte-swizzled K-major layout (the
+// 16-byte unit u of row r sits at unit u ^ (r % 8)).  Block stride = act_block_bytes().
 // FROM_BF16: source rows are bf16 hidden states gathered through perm (token = perm[p]/k);
 // otherwise fp32 rows [p][K].
 // ---------------------------------------------------------------------------------------
-template <int TERMS, bool FROM_BF16>
+// Two block layouts.  Sequential (prefill, tile_tokens = 128): as above, one MMA per term.
+// Stacked (decode, tile_tokens <= 32): the terms are stacked along N - B row t*npad + j is
+// term t of tile row j, npad = rows rounded up to 8 - so one MMA covers all terms and reads
+// the weight tile once; the block is [512 B scale atom][512 B pad][TERMS*npad rows x 128 B].
+__host__ __device__ inline size_t act_block_bytes(int terms, int tile_tokens, bool stacked) {
+    if (stacked) return 1024 + (size_t)terms * tile_tokens * 128;
+    return (size_t)terms * 512 + (size_t)(tile_tokens / 8) * terms * 1024;
+}
+
+template <int TERMS, bool FROM_BF16, bool STACK>
 __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm,
                                                          int top_k, int K, int n_rows, const int32_t* __restrict__ row_tile,
-                                                         const int32_t* __restrict__ tile_row0, uint8_t* __restrict__ q,
-                                                         size_t q_plane, uint8_t* __restrict__ sfb, size_t sfb_plane) {
+                                                         const int32_t* __restrict__ tile_row0,
+                                                         const int32_t* __restrict__ tile_rows, int tile_tokens,
+                                                         uint8_t* __restrict__ act) {
     const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_rows * n_chunks) return;
@@ -141,6 +162,8 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
         }
     }
     const int tile = row_tile[p], j = p - tile_row0[tile];
+    const int npad = (tile_rows[tile] + 7) & ~7;
+    uint8_t* blk = act + ((size_t)tile * n_chunks + c) * act_block_bytes(TERMS, tile_tokens, STACK);
 #pragma unroll
     for (int t = 0; t < TERMS; ++t) {
         float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
@@ -153,7 +176,12 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
         float scale = sb > 0 ? __uint_as_float((uint32_t)sb << 23) : __uint_as_float(0x00400000u);
         __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
         __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
-        *reinterpret_cast<uint32_t*>(q + t * q_plane + (size_t)p * Kp + k0) = (uint32_t)lo | ((uint32_t)hi << 16);
+        // row of this term inside the block and the place of its scale word
+        const int n = STACK ? t * npad + j : j;
+        uint8_t* row_ptr = STACK ? blk + 1024 + (size_t)(n >> 3) * 1024
+                                 : blk + TERMS * 512 + ((size_t)(n >> 3) * TERMS + t) * 1024;
+        *reinterpret_cast<uint32_t*>(row_ptr + (n & 7) * 128 + (((lane >> 2) ^ (n & 7)) << 4) + ((lane & 3) << 2)) =
+            (uint32_t)lo | ((uint32_t)hi << 16);
         if (t + 1 < TERMS) {
             __half2_raw blo = __nv_cvt_fp8x2_to_halfraw2(lo, __NV_E4M3), bhi = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
             float2 flo = __half22float2(*reinterpret_cast<__half2*>(&blo)), fhi = __half22float2(*reinterpret_cast<__half2*>(&bhi));
@@ -163,28 +191,34 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
         w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 8) << 8;
         w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 16) << 16;
         w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 24) << 24;
-        if (lane == 0)
-            *reinterpret_cast<uint32_t*>(sfb + t * sfb_plane + ((size_t)tile * n_chunks + c) * 512 + (j & 31) * 16 + (j >> 5) * 4) = w;
+        if (lane == 0) *reinterpret_cast<uint32_t*>(blk + (STACK ? 0 : t * 512) + (n & 31) * 16 + (n >> 5) * 4) = w;
     }
 }
 
 // ---------------------------------------------------------------------------------------
-// The GEMM.  Persistent CTAs (one per SM) walk items = (token tile, 128-row weight tile),
-// item index = blockIdx.x + i*gridDim.x, weight tile fastest so that concurrent CTAs share
-// a token tile's activations in L2.  Six warps: 0 = TMA producer, 1 = MMA issuer,
-// 2..5 = epilogue (TMEM lane quarter = warp % 4).  Per K chunk one stage holds the A tile
-// (128 x 128 containers, 16 KB), TERMS activation planes (BN_MAX x 128 bytes each) and their
-// scale atoms.  Accumulators are double-buffered in TMEM so the epilogue of item i overlaps
-// the MMAs of item i+1.  Every wait is bounded: on a timeout the CTA records a code in
-// *status, all roles leave their loops, in-flight copies get time to land, TMEM is freed.
+// The GEMM.  Persistent CTAs walk items = (token tile, 128-row weight tile), item index =
+// blockIdx.x + i*gridDim.x, weight tile fastest so that concurrent CTAs share a token tile's
+// activations in L2.  Six warps: 0 = TMA producer, 1 = MMA issuer, 2..5 = epilogue (TMEM
+// lane quarter = warp % 4).
+//
+// A pipeline stage holds KC consecutive K chunks: KC weight boxes (one TMA operation; the
+// boxes of an item are contiguous rows of the 2-D weight tensor), KC activation blocks (one
+// bulk copy, they are contiguous too) and KC weight scale atoms (one bulk copy).  Each
+// mbarrier round trip and each copy / tcgen05 issue costs a few hundred cycles of a single
+// thread, so the per-stage fixed cost is spread over 2 x 8 KB of weights.
+// Accumulators are double-buffered in TMEM so the epilogue of item i overlaps the MMAs of
+// item i+1.  Every wait is bounded: on a timeout the CTA records a code in *status, all
+// roles leave their loops, in-flight copies get time to land, TMEM is freed.
 // ---------------------------------------------------------------------------------------
 struct GmmParams {
-    const uint8_t* sfa;
-    const uint8_t* sfb;
-    size_t sfb_plane;
+    const uint8_t* sfa;    // [E][m_tiles][n_chunks][512]
+    const uint8_t* act;    // [tile][n_chunks][act_block_bytes]
     const int32_t *tile_expert, *tile_row0, *tile_rows, *n_tiles;
     int m_tiles, n_chunks, rows_total;
-    uint32_t a_tx_bytes;
+    uint32_t a_tx_bytes;   // bytes one 128 x 128 4-bit box reports to its mbarrier
+    int tmem_cols;         // TMEM columns to allocate (power of two)
+    int stages;            // pipeline stages in use (<= GmmSmem::kStages)
+    long long* trace;      // optional [2 roles][512 stages][2] clock stamps of CTA 0
     const uint16_t* bias;  // [E][rows_total], original row order
     // gate_up epilogue
     float* a_out;          // [n][inter] fp32
@@ -198,32 +232,44 @@ struct GmmParams {
     int* status;
 };
 
-template <int BN_MAX, int TERMS>
+template <int BN_MAX, int TERMS, bool STACK, int KC>
 struct GmmSmem {
-    static constexpr int kBPlane = BN_MAX * 128;
-    static constexpr int kStage = (16384 + TERMS * kBPlane + 512 * (1 + TERMS) + 1023) / 1024 * 1024;
+    static constexpr int kActBytes = STACK ? 1024 + TERMS * BN_MAX * 128 : TERMS * 512 + (BN_MAX / 8) * TERMS * 1024;
+    static constexpr int kStage = (KC * (16384 + kActBytes + 512) + 1023) / 1024 * 1024;
+    static constexpr int kSfCols = KC * (STACK ? 8 : 4 * (1 + TERMS));  // TMEM columns of scales per stage
+    static constexpr int kAccCols = STACK ? TERMS * BN_MAX : BN_MAX;    // TMEM columns of one accumulator buffer
     static constexpr int kTail = 1024;
     static constexpr int kBudget = 225 * 1024;
     static constexpr int kStagesFit = (kBudget - kTail - 1024) / kStage;
-    static constexpr int kStagesTmem = 256 / (4 * (1 + TERMS));
+    static constexpr int kStagesTmem = (512 - 2 * kAccCols) / kSfCols;
     static constexpr int kStages = kStagesFit < kStagesTmem ? kStagesFit : kStagesTmem;
-    static constexpr int kBytes = kStages * kStage + kTail + 1024;
+    static constexpr int smem_bytes(int stages) { return stages * kStage + kTail + 1024; }
+    static constexpr int tmem_cols(int stages) {
+        int need = 2 * kAccCols + stages * kSfCols, cols = 32;
+        while (cols < need) cols *= 2;
+        return cols;
+    }
+    static_assert(kStages >= 2, "at least two stages");
+    static_assert(KC * 16384 % 1024 == 0 && kActBytes % 1024 == 0, "alignment");
 };
 
 constexpr long long kWaitLimitCycles = 400000000ll;  // ~0.2 s at 2 GHz
 
-template <int BN_MAX, int TERMS, bool GATE_UP>
-__global__ void __launch_bounds__(192, 1)
-gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GmmParams p) {
+template <int BN_MAX, int TERMS, bool GATE_UP, bool STACK, int KC>
+__global__ void __launch_bounds__(192)
+gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA1, const GmmParams p) {
     using namespace sm100;
-    using L = GmmSmem<BN_MAX, TERMS>;
-    constexpr int STAGES = L::kStages;
-    constexpr int SF_COLS = 4 * (1 + TERMS);
+    using L = GmmSmem<BN_MAX, TERMS, STACK, KC>;
+    constexpr int STAGES_MAX = L::kStages;
+    const int STAGES = p.stages;
+    constexpr int SF_COLS = L::kSfCols;
+    constexpr int SF_BASE = 2 * L::kAccCols;
+    constexpr int ACT_OFF = KC * 16384, SFA_OFF = ACT_OFF + KC * L::kActBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStage);
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStage);  // barriers follow the stages in use
+    uint64_t* empty = full + STAGES_MAX;
+    uint64_t* acc_full = empty + STAGES_MAX;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -241,75 +287,111 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tmA);
-        prefetch_tmap(&tmB);
+        prefetch_tmap(&tmA1);
     }
-    if (warp == 2) tmem_alloc(tmem_slot, 512);
+    const uint32_t tmem_cols = (uint32_t)p.tmem_cols;
+    if (warp == 2) tmem_alloc(tmem_slot, tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int n_items = *p.n_tiles * p.m_tiles;
+    constexpr size_t act_stride = L::kActBytes;
 
     if (warp == 0) {
-        if (lane == 0) {
-            int it = 0;
-            for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-                const int tile = item / p.m_tiles, m = item % p.m_tiles;
-                const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
-                const int nboxes = (rows + 7) >> 3;
-                const uint32_t tx = p.a_tx_bytes + 512 + TERMS * (nboxes * 1024 + 512);
-                for (int c = 0; c < p.n_chunks; ++c, ++it) {
-                    const int s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles)) goto done;
-                    uint8_t* st = smem + s * L::kStage;
-                    mbar_expect_tx(&full[s], tx);
-                    tma_load_3d(st, &tmA, &full[s], c * kChunkK, m * 128, e);
-                    bulk_load(st + 16384 + TERMS * L::kBPlane,
-                              p.sfa + (((size_t)e * p.m_tiles + m) * p.n_chunks + c) * 512, 512, &full[s]);
-#pragma unroll
-                    for (int t = 0; t < TERMS; ++t) {
-                        for (int b = 0; b < nboxes; ++b)
-                            tma_load_3d(st + 16384 + t * L::kBPlane + b * 1024, &tmB, &full[s], c * kChunkK, row0 + 8 * b, t);
-                        bulk_load(st + 16384 + TERMS * L::kBPlane + 512 * (1 + t),
-                                  p.sfb + t * p.sfb_plane + ((size_t)tile * p.n_chunks + c) * 512, 512, &full[s]);
-                    }
+        // The warp stays converged (uniform operands); lane 0 polls the barrier, one elected
+        // lane issues the stage's three copies.
+        int it = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int tile = item / p.m_tiles, m = item % p.m_tiles;
+            const int e = p.tile_expert[tile], rows = p.tile_rows[tile];
+            const uint32_t act_bytes = STACK ? 1024 + TERMS * ((rows + 7) >> 3) * 1024
+                                             : TERMS * 512 + ((rows + 7) >> 3) * TERMS * 1024;
+            const size_t box = ((size_t)e * p.m_tiles + m) * p.n_chunks;
+            for (int c0 = 0; c0 < p.n_chunks; c0 += KC, ++it) {
+                const int kc = min(KC, p.n_chunks - c0);
+                const int s = it % STAGES, ph = (it / STAGES) & 1;
+                int ok = 1;
+                if (lane == 0) {
+                    ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
+                    if (ok) mbar_expect_tx(&full[s], kc * (p.a_tx_bytes + 512) + (kc - 1) * (uint32_t)act_stride + act_bytes);
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) goto done;
+                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(0 * 512 + it) * 2] = clock64();
+                uint8_t* st = smem + s * L::kStage;
+                if (elect_one()) {
+                    if (kc == KC) tma_load_2d(st, &tmA, &full[s], 0, (int)((box + c0) * 128));
+                    else tma_load_2d(st, &tmA1, &full[s], 0, (int)((box + c0) * 128));
+                    bulk_load(st + SFA_OFF, p.sfa + (box + c0) * 512, kc * 512, &full[s]);
+                    bulk_load(st + ACT_OFF, p.act + ((size_t)tile * p.n_chunks + c0) * act_stride,
+                              (kc - 1) * (uint32_t)act_stride + act_bytes, &full[s]);
+                }
+                __syncwarp();
+                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(0 * 512 + it) * 2 + 1] = clock64();
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            int it = 0, iter = 0;
-            for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
-                const int tile = item / p.m_tiles;
-                const int rows = p.tile_rows[tile];
-                const uint32_t n_mma = (uint32_t)max(16, round_up_int(rows, 16));
-                const int b = iter & 1, aph = (iter >> 1) & 1;
-                if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles)) goto done;
+        // The whole warp walks the loop so every operand stays warp-uniform; one elected lane
+        // issues the tcgen05 instructions.
+        int it = 0, iter = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
+            const int tile = item / p.m_tiles;
+            const int rows = p.tile_rows[tile];
+            const int npad = (rows + 7) & ~7;
+            const uint32_t n_mma = STACK ? (uint32_t)(TERMS * npad) : (uint32_t)max(16, round_up_int(rows, 16));
+            const int b = iter & 1, aph = (iter >> 1) & 1;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) goto done;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + b * L::kAccCols;
+            for (int c0 = 0; c0 < p.n_chunks; c0 += KC, ++it) {
+                const int kc = min(KC, p.n_chunks - c0);
+                const int s = it % STAGES, ph = (it / STAGES) & 1;
+                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(1 * 512 + it) * 2] = clock64();
+                if (lane == 0) ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
+                if (!__shfl_sync(0xffffffffu, ok, 0)) goto done;
+                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(1 * 512 + it) * 2 + 1] = clock64();
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + b * BN_MAX;
-                for (int c = 0; c < p.n_chunks; ++c, ++it) {
-                    const int s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (!mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles)) goto done;
-                    tc_fence_after();
-                    uint8_t* st = smem + s * L::kStage;
-                    const uint32_t sf_tmem = tmem_base + 256 + s * SF_COLS;
-                    const uint32_t sf_smem = smem_u32(st + 16384 + TERMS * L::kBPlane);
-                    tc_copy_sf(sf_tmem, make_sf_desc(sf_smem));
+                uint8_t* st = smem + s * L::kStage;
+                if (elect_one()) {
 #pragma unroll
-                    for (int t = 0; t < TERMS; ++t) tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(sf_smem + 512 * (1 + t)));
-                    const uint64_t a_desc = make_sw128_desc(smem_u32(st));
+                    for (int k = 0; k < KC; ++k) {
+                        if (k < kc) {
+                            const uint32_t sf_tmem = tmem_base + SF_BASE + s * SF_COLS + k * (SF_COLS / KC);
+                            const uint32_t act_smem = smem_u32(st + ACT_OFF + k * L::kActBytes);
+                            const uint64_t a_desc = make_sw128_desc(smem_u32(st + k * 16384));
+                            const uint32_t first = (uint32_t)(c0 + k);  // 0 only for the item's first chunk
+                            tc_copy_sf(sf_tmem, make_sf_desc(smem_u32(st + SFA_OFF + k * 512)));
+                            if (STACK) {
+                                tc_copy_sf(sf_tmem + 4, make_sf_desc(act_smem));
+                                const uint64_t b_desc = make_sw128_desc(act_smem + 1024);
 #pragma unroll
-                    for (int t = 0; t < TERMS; ++t) {
-                        const uint64_t b_desc = make_sw128_desc(smem_u32(st + 16384 + t * L::kBPlane));
+                                for (int j = 0; j < 4; ++j)
+                                    mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, make_idesc_bs(5, 0, n_mma, j, j),
+                                                 sf_tmem, sf_tmem + 4, first | (uint32_t)j);
+                            } else {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, make_idesc_bs(5, 0, n_mma, j, j), sf_tmem,
-                                         sf_tmem + 4 * (1 + t), (uint32_t)(c | t | j));
+                                for (int t = 0; t < TERMS; ++t)
+                                    tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(act_smem + 512 * t));
+#pragma unroll
+                                for (int t = 0; t < TERMS; ++t) {
+                                    const uint64_t b_desc = make_sw128_desc(act_smem + TERMS * 512 + t * 1024, TERMS * 1024);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+                                        mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, make_idesc_bs(5, 0, n_mma, j, j),
+                                                     sf_tmem, sf_tmem + 4 * (1 + t), first | (uint32_t)(t | j));
+                                }
+                            }
+                        }
                     }
                     tc_commit(&empty[s]);
                 }
-                tc_commit(&acc_full[b]);
+                __syncwarp();
             }
+            if (elect_one()) tc_commit(&acc_full[b]);
+            __syncwarp();
         }
     } else {
         const int q = warp & 3;
@@ -320,39 +402,41 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             const int b = iter & 1, aph = (iter >> 1) & 1;
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN_MAX;
-            const int ncol = max(16, round_up_int(rows, 16));
-            if (GATE_UP) {
-                // lanes 0..15: gate rows of channels ch0 + lane; lanes 16..31: their linear rows
-                const int ch = 64 * m + 16 * q + (lane & 15);
-                const float bias = bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + 2 * ch + (lane >> 4)]);
-                for (int c16 = 0; c16 < ncol; c16 += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + c16, v);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * L::kAccCols;
+            const int npad = (rows + 7) & ~7;
+            // GATE_UP: lanes 0..15 hold gate rows of channels ch, lanes 16..31 their linear rows
+            const int ch = 64 * m + 16 * q + (lane & 15);
+            const int row = 128 * m + 32 * q + lane;
+            const bool valid = GATE_UP ? true : row < p.rows_total;
+            float bias = 0.f;
+            if (GATE_UP) bias = bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + 2 * ch + (lane >> 4)]);
+            else if (valid) bias = bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + row]);
+            for (int j8 = 0; j8 < npad; j8 += 8) {
+                float v[8];
+                tmem_ld8(taddr + j8, v);
+                if (STACK) {  // add the columns of the other terms
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float mine = v[i] + bias;
-                        float lin = __shfl_down_sync(0xffffffffu, mine, 16);
-                        if (lane < 16 && c16 + i < rows) {
-                            float g = fminf(mine, p.limit);
-                            float l = fminf(fmaxf(lin, -p.limit), p.limit);
-                            p.a_out[(size_t)(row0 + c16 + i) * p.inter + ch] = g / (1.f + expf(-p.alpha * g)) * (l + 1.f);
-                        }
+                    for (int t = 1; t < TERMS; ++t) {
+                        float u[8];
+                        tmem_ld8(taddr + t * npad + j8, u);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] += u[i];
                     }
                 }
-            } else {
-                const int row = 128 * m + 32 * q + lane;
-                const bool valid = row < p.rows_total;
-                const float bias = valid ? bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + row]) : 0.f;
-                for (int c16 = 0; c16 < ncol; c16 += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + c16, v);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (valid && c16 + i < rows) {
-                            const int pos = row0 + c16 + i;
-                            p.y[(size_t)pos * p.hidden + row] = p.route_w[p.perm[pos]] * (v[i] + bias);
+                for (int i = 0; i < 8; ++i) {
+                    const int pos = row0 + j8 + i;
+                    const float mine = v[i] + bias;
+                    if (GATE_UP) {
+                        const float lin = __shfl_down_sync(0xffffffffu, mine, 16);
+                        if (lane < 16 && j8 + i < rows) {
+                            const float g = fminf(mine, p.limit);
+                            const float l = fminf(fmaxf(lin, -p.limit), p.limit);
+                            p.a_out[(size_t)pos * p.inter + ch] = g / (1.f + expf(-p.alpha * g)) * (l + 1.f);
                         }
+                    } else if (valid && j8 + i < rows) {
+                        p.y[(size_t)pos * p.hidden + row] = p.route_w[p.perm[pos]] * mine;
+                    }
                 }
             }
             tc_fence_before();
@@ -371,7 +455,7 @@ done:
     }
     if (warp == 2) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, tmem_cols);
     }
 }
 

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -46,12 +47,14 @@ struct neon_moe_handle {
     // tensor-core path: "tc" weights, tensor maps, activation-term planes, token tiles
     int path = 2;                 // 1 = mma.sync kernels, 2 = TMA + tcgen05 block-scaled GEMM
     uint32_t a_tx_bytes = 8192;   // bytes one 128x128 4-bit box adds to its mbarrier
+    int max_stages = 0, ctas_per_sm = 1, chunks_per_stage = 2;
+    long long* trace = nullptr;
     uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
-    uint8_t *xq = nullptr, *x_sfb = nullptr, *aq = nullptr, *a_sfb = nullptr;
+    uint8_t *x_act = nullptr, *a_act = nullptr;  // activation blocks (terms + scales) per (tile, chunk)
     float* a_f32 = nullptr;
     int32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_tiles = nullptr, *row_tile = nullptr;
     int tile_cap = 0, kp_h = 0, kp_i = 0;
-    CUtensorMap tm_gu{}, tm_dn{}, tm_x{}, tm_a{};
+    CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
     // per-stage profiling: 5 events per forward
     bool profiling = false;
     std::vector<cudaEvent_t> events;
@@ -90,7 +93,7 @@ void free_all(neon_moe_handle* h) {
     void* ptrs[] = {h->router_w, h->router_b, h->gu_bias, h->dn_bias, h->gu_wq, h->dn_wq, h->gu_sq, h->dn_sq,
                     h->idx, h->count, h->offset, h->perm, h->inv, h->route_w, h->y, h->a_hi, h->a_lo,
                     h->status, h->st_hidden, h->st_out, h->st_bias, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
-                    h->xq, h->x_sfb, h->aq, h->a_sfb, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
+                    h->x_act, h->a_act, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
                     h->n_tiles, h->row_tile};
     for (void* p : ptrs)
         if (p) cudaFree(p);
@@ -174,24 +177,25 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 3-D map over [dim2][dim1][dim0] with a (128, box_rows, 1) box and 128-byte swizzle.
-int make_map(neon_moe_handle* h, CUtensorMap* map, CUtensorMapDataType type, void* base, uint64_t dim0, uint64_t dim1,
-             uint64_t dim2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box_rows) {
+// 2-D map over packed 4-bit weight boxes: rows of 128 nibbles (64 B), box = 128 x 128, expanded
+// by TMA to one byte per nibble (16 nibbles + 8 pad bytes per 16 B) with 128-byte swizzle.
+int make_weight_map(neon_moe_handle* h, CUtensorMap* map, void* base, uint64_t n_rows, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[3] = {dim0, dim1, dim2};
-    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
-    cuuint32_t box[3] = {128, box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, type, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    cuuint64_t dims[2] = {128, n_rows};
+    cuuint64_t strides[1] = {64};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, base, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return NEON_MOE_OK;
 }
 
 // Upload (when needed) and re-tile one MXFP4 matrix set into the "tc" format.
 int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* scales, int rows, int K, int gate_up,
-                   int on_device, uint8_t** wt, uint8_t** sfa, CUtensorMap* map) {
+                   int on_device, uint8_t** wt, uint8_t** sfa, CUtensorMap* map, CUtensorMap* map2) {
     const int E = h->n_local;
     const size_t nb = (size_t)E * rows * (K / 2), ns = (size_t)E * rows * (K / 32);
     const uint8_t *d_blocks = blocks, *d_scales = scales;
@@ -206,7 +210,7 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
     }
     const int Kp = round_up_int(K, kChunkK), m_tiles = (rows + 127) / 128, n_chunks = Kp / kChunkK;
     if (!*wt) {
-        int rc = dev_alloc(h, wt, (size_t)E * rows * (Kp / 2) + 256);
+        int rc = dev_alloc(h, wt, (size_t)E * m_tiles * n_chunks * 8192);
         if (rc) return rc;
         rc = dev_alloc(h, sfa, (size_t)E * m_tiles * n_chunks * 512);
         if (rc) return rc;
@@ -217,32 +221,64 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
     CU(h, cudaDeviceSynchronize());
     if (tmp_b) cudaFree(tmp_b);
     if (tmp_s) cudaFree(tmp_s);
-    return make_map(h, map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, *wt, (uint64_t)Kp, (uint64_t)rows, (uint64_t)E,
-                    (uint64_t)Kp / 2, (uint64_t)rows * (Kp / 2), 128);
+    int rc = make_weight_map(h, map, *wt, (uint64_t)E * m_tiles * n_chunks * 128, 128);
+    if (rc) return rc;
+    return make_weight_map(h, map2, *wt, (uint64_t)E * m_tiles * n_chunks * 128, 256);
 }
 
-int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 64 ? 64 : 128); }
+// Token-tile size: decode batches use small tiles with the activation terms stacked along N
+// (one MMA per k-block reads the weight tile once); larger batches use 128-token tiles.
+int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 64 ? 32 : 128); }
 
-template <int BN, int TERMS, bool GATE_UP>
-int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tmA, const CUtensorMap& tmB, const GmmParams& p, cudaStream_t st) {
-    using L = GmmSmem<BN, TERMS>;
+template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC>
+int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap& tm2, GmmParams p, cudaStream_t st) {
+    using L = GmmSmem<BN, TERMS, STACK, KC>;
     static bool configured[kMaxDevicesAttr] = {};
-    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP>;
+    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP, STACK, KC>;
     if (!configured[h->cfg.device]) {
-        CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+        CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::smem_bytes(L::kStages)));
         configured[h->cfg.device] = true;
     }
-    kern<<<h->n_sms, 192, L::kBytes, st>>>(tmA, tmB, p);
+    int stages = L::kStages, ctas = h->n_sms;
+    if (h->ctas_per_sm == 2) {  // two half-size CTAs per SM when at least two stages fit in half the shared memory
+        const int half = (110 * 1024 - 2048) / L::kStage;
+        if (half >= 2 && L::tmem_cols(half) <= 256) {
+            stages = std::min(stages, half);
+            ctas = 2 * h->n_sms;
+        }
+    }
+    if (h->max_stages > 0) stages = std::max(2, std::min(stages, h->max_stages));
+    p.stages = stages;
+    p.tmem_cols = L::tmem_cols(stages);
+    kern<<<ctas, 192, L::smem_bytes(stages), st>>>(KC == 2 ? tm2 : tm1, tm1, p);
     h->launches++;
     return NEON_MOE_OK;
 }
 
 template <int TERMS, bool GATE_UP>
-int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tmA, const CUtensorMap& tmB, const GmmParams& p,
+int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, const CUtensorMap& tm2, const GmmParams& p,
                cudaStream_t st) {
-    if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP>(h, tmA, tmB, p, st);
-    if (tile_tokens == 64) return launch_gmm_one<64, TERMS, GATE_UP>(h, tmA, tmB, p, st);
-    return launch_gmm_one<128, TERMS, GATE_UP>(h, tmA, tmB, p, st);
+    const bool two = h->chunks_per_stage == 2;
+    if (tile_tokens == 16)
+        return two ? launch_gmm_one<16, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st)
+                   : launch_gmm_one<16, TERMS, GATE_UP, true, 1>(h, tm1, tm2, p, st);
+    if (tile_tokens == 32)
+        return two ? launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st)
+                   : launch_gmm_one<32, TERMS, GATE_UP, true, 1>(h, tm1, tm2, p, st);
+    return launch_gmm_one<128, TERMS, GATE_UP, false, 1>(h, tm1, tm2, p, st);
+}
+
+template <int TERMS, bool FROM_BF16>
+void launch_split(neon_moe_handle* h, int tile_tokens, const void* src, int K, int n, uint8_t* act, cudaStream_t st) {
+    const int n_chunks = round_up_int(K, kChunkK) / kChunkK;
+    const dim3 grid((n * n_chunks + 7) / 8);
+    if (tile_tokens <= 32)
+        split_rows_kernel<TERMS, FROM_BF16, true><<<grid, 256, 0, st>>>(src, h->perm, h->cfg.top_k, K, n, h->row_tile,
+                                                                        h->tile_row0, h->tile_rows, tile_tokens, act);
+    else
+        split_rows_kernel<TERMS, FROM_BF16, false><<<grid, 256, 0, st>>>(src, h->perm, h->cfg.top_k, K, n, h->row_tile,
+                                                                         h->tile_row0, h->tile_rows, tile_tokens, act);
+    h->launches++;
 }
 
 template <bool GATE_UP>
@@ -316,16 +352,16 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
     h->kp_i = round_up_int(cfg->inter, kChunkK);
     h->tile_cap = h->n_local + (int)(n / 16) + 2;
     const size_t nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
-    if ((rc = dev_alloc(h, &h->xq, 2 * n * h->kp_h)) || (rc = dev_alloc(h, &h->x_sfb, 2 * (size_t)h->tile_cap * nch_h * 512)) ||
-        (rc = dev_alloc(h, &h->aq, 4 * n * h->kp_i)) || (rc = dev_alloc(h, &h->a_sfb, 4 * (size_t)h->tile_cap * nch_i * 512)) ||
+    size_t x_bytes = 0, a_bytes = 0;  // worst case over the three token-tile sizes
+    for (int tt : {16, 32, 128}) {
+        const size_t tiles = (size_t)h->n_local + n / tt + 1;
+        x_bytes = std::max(x_bytes, tiles * nch_h * act_block_bytes(2, tt, tt <= 32));
+        a_bytes = std::max(a_bytes, tiles * nch_i * act_block_bytes(4, tt, tt <= 32));
+    }
+    if ((rc = dev_alloc(h, &h->x_act, x_bytes)) || (rc = dev_alloc(h, &h->a_act, a_bytes)) ||
         (rc = dev_alloc(h, &h->a_f32, n * cfg->inter)) || (rc = dev_alloc(h, &h->tile_expert, (size_t)h->tile_cap)) ||
         (rc = dev_alloc(h, &h->tile_row0, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile_rows, (size_t)h->tile_cap)) ||
         (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
-        return bail(rc);
-    if ((rc = make_map(h, &h->tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, h->xq, (uint64_t)h->kp_h, (uint64_t)n, 2, (uint64_t)h->kp_h,
-                       (uint64_t)n * h->kp_h, 8)) ||
-        (rc = make_map(h, &h->tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, h->aq, (uint64_t)h->kp_i, (uint64_t)n, 4, (uint64_t)h->kp_i,
-                       (uint64_t)n * h->kp_i, 8)))
         return bail(rc);
     if (cudaMemset(h->status, 0, 16) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
     if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
@@ -360,8 +396,8 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
     if ((rc = copy_in(h, &h->dn_bias, dn_bias, (size_t)EL * H, on_device))) return rc;
     if ((rc = load_matrix(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wq, &h->gu_sq))) return rc;
     if ((rc = load_matrix(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wq, &h->dn_sq))) return rc;
-    if ((rc = load_matrix_tc(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wt, &h->gu_sfa, &h->tm_gu))) return rc;
-    if ((rc = load_matrix_tc(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wt, &h->dn_sfa, &h->tm_dn))) return rc;
+    if ((rc = load_matrix_tc(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wt, &h->gu_sfa, &h->tm_gu, &h->tm_gu2))) return rc;
+    if ((rc = load_matrix_tc(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wt, &h->dn_sfa, &h->tm_dn, &h->tm_dn2))) return rc;
     CU(h, cudaDeviceSynchronize());
     h->has_weights = true;
     return NEON_MOE_OK;
@@ -395,30 +431,24 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float*
         build_tiles_kernel<<<1, 1024, 0, st>>>(h->offset, h->n_local, tt, tl);
         h->launches++;
         const int nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
-        const size_t x_plane = (size_t)h->cfg.max_tokens * k * h->kp_h, a_plane = (size_t)h->cfg.max_tokens * k * h->kp_i;
-        const size_t xs_plane = (size_t)h->tile_cap * nch_h * 512, as_plane = (size_t)h->tile_cap * nch_i * 512;
-        split_rows_kernel<2, true><<<(n * nch_h + 7) / 8, 256, 0, st>>>(hidden, h->perm, k, H, n, h->row_tile, h->tile_row0,
-                                                                        h->xq, x_plane, h->x_sfb, xs_plane);
-        h->launches++;
+        launch_split<2, true>(h, tt, hidden, H, n, h->x_act, st);
         GmmParams g{};
         g.tile_expert = h->tile_expert; g.tile_row0 = h->tile_row0; g.tile_rows = h->tile_rows; g.n_tiles = h->n_tiles;
-        g.a_tx_bytes = h->a_tx_bytes;
+        g.a_tx_bytes = h->a_tx_bytes; g.trace = h->trace;
         g.a_out = h->a_f32; g.inter = I; g.limit = h->cfg.swiglu_limit; g.alpha = h->cfg.swiglu_alpha;
         g.perm = h->perm; g.route_w = h->route_w; g.y = h->y; g.hidden = H; g.status = h->status;
         // gate_up: rows 2I, K = H
-        g.sfa = h->gu_sfa; g.sfb = h->x_sfb; g.sfb_plane = xs_plane; g.bias = h->gu_bias;
+        g.sfa = h->gu_sfa; g.act = h->x_act; g.bias = h->gu_bias;
         g.m_tiles = 2 * I / 128; g.n_chunks = nch_h; g.rows_total = 2 * I;
         mark(h, st, prof);
-        int rc = launch_gmm<2, true>(h, tt, h->tm_gu, h->tm_x, g, st);
+        int rc = launch_gmm<2, true>(h, tt, h->tm_gu, h->tm_gu2, g, st);
         if (rc) return rc;
         mark(h, st, prof);
-        split_rows_kernel<4, false><<<(n * nch_i + 7) / 8, 256, 0, st>>>(h->a_f32, nullptr, k, I, n, h->row_tile, h->tile_row0,
-                                                                         h->aq, a_plane, h->a_sfb, as_plane);
-        h->launches++;
+        launch_split<4, false>(h, tt, h->a_f32, I, n, h->a_act, st);
         // down: rows H, K = I
-        g.sfa = h->dn_sfa; g.sfb = h->a_sfb; g.sfb_plane = as_plane; g.bias = h->dn_bias;
+        g.sfa = h->dn_sfa; g.act = h->a_act; g.bias = h->dn_bias;
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
-        rc = launch_gmm<4, false>(h, tt, h->tm_dn, h->tm_a, g, st);
+        rc = launch_gmm<4, false>(h, tt, h->tm_dn, h->tm_dn2, g, st);
         if (rc) return rc;
         mark(h, st, prof);
     } else {
@@ -502,6 +532,17 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->path = (int)value;
     } else if (!strcmp(name, "a_tx_bytes")) {
         h->a_tx_bytes = (uint32_t)value;
+    } else if (!strcmp(name, "trace_ptr")) {
+        h->trace = reinterpret_cast<long long*>(value);
+    } else if (!strcmp(name, "ctas_per_sm")) {
+        h->ctas_per_sm = (int)value;
+    } else if (!strcmp(name, "n_ctas")) {
+        h->n_sms = (int)value;
+    } else if (!strcmp(name, "chunks_per_stage")) {
+        if (value != 1 && value != 2) return fail(h, NEON_MOE_EINVAL, "chunks_per_stage must be 1 or 2");
+        h->chunks_per_stage = (int)value;
+    } else if (!strcmp(name, "max_stages")) {
+        h->max_stages = (int)value;
     } else {
         return fail(h, NEON_MOE_EINVAL, "unknown option '%s'", name);
     }

@@ -11,6 +11,18 @@ namespace sm100 {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// True in exactly one lane of a fully converged warp.  Code under it stays on the warp-uniform
+// datapath, which tcgen05 operands (descriptors, TMEM addresses) must come from.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- mbarrier ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -60,6 +72,12 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
 // Plain bulk copy; dst, src 16-byte aligned, bytes a multiple of 16.
@@ -132,13 +150,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float v[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Same for 8 columns.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float v[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // ---- descriptors ----------------------------------------------------------------------------
 // K-major operand tile in the 128-byte-swizzled layout TMA writes: rows of 128 bytes, groups
-// of 8 rows (1024 B) stacked contiguously.  Fields: start address >> 4 (bits 0-13), leading
-// byte offset (unused for swizzled K-major, 1) at 16-29, stride byte offset (1024 >> 4) at
-// 32-45, descriptor version 1 at 46-47, layout type 2 (128B swizzle) at 61-63.
-__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+// of 8 rows (1024 B) `group_stride` bytes apart.  Fields: start address >> 4 (bits 0-13),
+// leading byte offset (unused for swizzled K-major, 1) at 16-29, stride byte offset
+// (group_stride >> 4) at 32-45, descriptor version 1 at 46-47, layout type 2 (128B swizzle)
+// at 61-63.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr, uint32_t group_stride = 1024) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(group_stride >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 // Unswizzled scale-factor atom: 32 rows of 16 bytes, 8-row groups 128 B apart.

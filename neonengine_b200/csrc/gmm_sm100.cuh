@@ -299,78 +299,84 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     constexpr size_t act_stride = L::kActBytes;
 
     if (warp == 0) {
-        // The warp stays converged (uniform operands); lane 0 polls the barrier, one elected
-        // lane issues the stage's three copies.
-        int it = 0;
+        // Producer.  The warp stays converged so that copy operands live on the uniform
+        // datapath; all lanes poll the barrier, one elected lane arms it and issues the
+        // stage's three copies.  Stage index, phase and global addresses are carried
+        // incrementally: every extra instruction in this loop costs ~10 cycles per stage.
+        int s = 0, ph = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int tile = item / p.m_tiles, m = item % p.m_tiles;
+            const int tile = item / p.m_tiles, m = item - tile * p.m_tiles;
             const int e = p.tile_expert[tile], rows = p.tile_rows[tile];
             const uint32_t act_bytes = STACK ? 1024 + TERMS * ((rows + 7) >> 3) * 1024
                                              : TERMS * 512 + ((rows + 7) >> 3) * TERMS * 1024;
-            const size_t box = ((size_t)e * p.m_tiles + m) * p.n_chunks;
-            for (int c0 = 0; c0 < p.n_chunks; c0 += KC, ++it) {
-                const int kc = min(KC, p.n_chunks - c0);
-                const int s = it % STAGES, ph = (it / STAGES) & 1;
-                int ok = 1;
-                if (lane == 0) {
-                    ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
-                    if (ok) mbar_expect_tx(&full[s], kc * (p.a_tx_bytes + 512) + (kc - 1) * (uint32_t)act_stride + act_bytes);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) goto done;
-                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(0 * 512 + it) * 2] = clock64();
+            const uint32_t box = (uint32_t)((e * p.m_tiles + m) * p.n_chunks);
+            int box_row = (int)(box * 128);
+            const uint8_t* sfa_src = p.sfa + (size_t)box * 512;
+            const uint8_t* act_src = p.act + (size_t)tile * p.n_chunks * act_stride;
+            const uint32_t tx_full = KC * (p.a_tx_bytes + 512) + (KC - 1) * (uint32_t)act_stride + act_bytes;
+            for (int left = p.n_chunks; left > 0; left -= KC) {
+                const bool whole = left >= KC;
+                int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
+                if (!__all_sync(0xffffffffu, ok)) goto done;
                 uint8_t* st = smem + s * L::kStage;
                 if (elect_one()) {
-                    if (kc == KC) tma_load_2d(st, &tmA, &full[s], 0, (int)((box + c0) * 128));
-                    else tma_load_2d(st, &tmA1, &full[s], 0, (int)((box + c0) * 128));
-                    bulk_load(st + SFA_OFF, p.sfa + (box + c0) * 512, kc * 512, &full[s]);
-                    bulk_load(st + ACT_OFF, p.act + ((size_t)tile * p.n_chunks + c0) * act_stride,
-                              (kc - 1) * (uint32_t)act_stride + act_bytes, &full[s]);
+                    if (whole) {
+                        mbar_expect_tx(&full[s], tx_full);
+                        tma_load_2d(st, &tmA, &full[s], 0, box_row);
+                        bulk_load(st + SFA_OFF, sfa_src, KC * 512, &full[s]);
+                        bulk_load(st + ACT_OFF, act_src, (KC - 1) * (uint32_t)act_stride + act_bytes, &full[s]);
+                    } else {  // the odd last chunk of the item (KC == 2 only)
+                        mbar_expect_tx(&full[s], p.a_tx_bytes + 512 + act_bytes);
+                        tma_load_2d(st, &tmA1, &full[s], 0, box_row);
+                        bulk_load(st + SFA_OFF, sfa_src, 512, &full[s]);
+                        bulk_load(st + ACT_OFF, act_src, act_bytes, &full[s]);
+                    }
                 }
                 __syncwarp();
-                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(0 * 512 + it) * 2 + 1] = clock64();
+                box_row += KC * 128;
+                sfa_src += KC * 512;
+                act_src += KC * act_stride;
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
     } else if (warp == 1) {
-        // The whole warp walks the loop so every operand stays warp-uniform; one elected lane
-        // issues the tcgen05 instructions.
-        int it = 0, iter = 0;
+        // MMA issuer.  Same shape: converged warp, all lanes poll, one elected lane issues.
+        int s = 0, ph = 0, iter = 0;
+        const uint32_t smem_base = smem_u32(smem);
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
             const int tile = item / p.m_tiles;
             const int rows = p.tile_rows[tile];
             const int npad = (rows + 7) & ~7;
             const uint32_t n_mma = STACK ? (uint32_t)(TERMS * npad) : (uint32_t)max(16, round_up_int(rows, 16));
+            const uint32_t idesc0 = make_idesc_bs(5, 0, n_mma, 0, 0);
+            constexpr uint32_t kIdescStep = (1u << 4) | (1u << 29);  // next scale id for A and B
             const int b = iter & 1, aph = (iter >> 1) & 1;
-            int ok = 1;
-            if (lane == 0) ok = mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles);
-            if (!__shfl_sync(0xffffffffu, ok, 0)) goto done;
+            int ok = mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles);
+            if (!__all_sync(0xffffffffu, ok)) goto done;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + b * L::kAccCols;
-            for (int c0 = 0; c0 < p.n_chunks; c0 += KC, ++it) {
-                const int kc = min(KC, p.n_chunks - c0);
-                const int s = it % STAGES, ph = (it / STAGES) & 1;
-                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(1 * 512 + it) * 2] = clock64();
-                if (lane == 0) ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
-                if (!__shfl_sync(0xffffffffu, ok, 0)) goto done;
-                if (p.trace && blockIdx.x == 0 && lane == 0 && it < 512) p.trace[(1 * 512 + it) * 2 + 1] = clock64();
+            uint32_t first = 0;  // becomes non-zero after the item's first MMA
+            for (int left = p.n_chunks; left > 0; left -= KC) {
+                ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
+                if (!__all_sync(0xffffffffu, ok)) goto done;
                 tc_fence_after();
-                uint8_t* st = smem + s * L::kStage;
+                const uint32_t st = smem_base + s * L::kStage;
+                const uint32_t sf_stage = tmem_base + SF_BASE + s * SF_COLS;
                 if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < KC; ++k) {
-                        if (k < kc) {
-                            const uint32_t sf_tmem = tmem_base + SF_BASE + s * SF_COLS + k * (SF_COLS / KC);
-                            const uint32_t act_smem = smem_u32(st + ACT_OFF + k * L::kActBytes);
-                            const uint64_t a_desc = make_sw128_desc(smem_u32(st + k * 16384));
-                            const uint32_t first = (uint32_t)(c0 + k);  // 0 only for the item's first chunk
-                            tc_copy_sf(sf_tmem, make_sf_desc(smem_u32(st + SFA_OFF + k * 512)));
+                        if (k < left) {
+                            const uint32_t sf_tmem = sf_stage + k * (SF_COLS / KC);
+                            const uint32_t act_smem = st + ACT_OFF + k * L::kActBytes;
+                            const uint64_t a_desc = make_sw128_desc(st + k * 16384);
+                            tc_copy_sf(sf_tmem, make_sf_desc(st + SFA_OFF + k * 512));
                             if (STACK) {
                                 tc_copy_sf(sf_tmem + 4, make_sf_desc(act_smem));
                                 const uint64_t b_desc = make_sw128_desc(act_smem + 1024);
 #pragma unroll
                                 for (int j = 0; j < 4; ++j)
-                                    mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, make_idesc_bs(5, 0, n_mma, j, j),
-                                                 sf_tmem, sf_tmem + 4, first | (uint32_t)j);
+                                    mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,
+                                                 sf_tmem + 4, first | (uint32_t)(k | j));
                             } else {
 #pragma unroll
                                 for (int t = 0; t < TERMS; ++t)
@@ -380,8 +386,8 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                                     const uint64_t b_desc = make_sw128_desc(act_smem + TERMS * 512 + t * 1024, TERMS * 1024);
 #pragma unroll
                                     for (int j = 0; j < 4; ++j)
-                                        mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, make_idesc_bs(5, 0, n_mma, j, j),
-                                                     sf_tmem, sf_tmem + 4 * (1 + t), first | (uint32_t)(t | j));
+                                        mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,
+                                                     sf_tmem + 4 * (1 + t), first | (uint32_t)(k | t | j));
                                 }
                             }
                         }
@@ -389,6 +395,8 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     tc_commit(&empty[s]);
                 }
                 __syncwarp();
+                first = 1;
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             if (elect_one()) tc_commit(&acc_full[b]);
             __syncwarp();

@@ -1,12 +1,14 @@
 #!/usr/bin/env python
 """Benchmark of the gpt-oss-shaped MoE layer (tokens/s) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2|cfg4] [--impl reference]
 
 A step is one pass of the MoE layer over one batch of seeded synthetic hidden states.
 Default workload at one GPU is the batched-decode configuration (T=64 tokens, Zipf-skewed
 routing, gpt-oss-20b shapes); batches rotate and the 424 MB of expert weights exceed the
-126 MB L2, so every step streams its weights from HBM.
+126 MB L2, so every step streams its weights from HBM.  With N > 1 GPUs (torchrun) the default
+is the 128-expert configuration, expert-parallel: experts sharded over the ranks, token rows
+exchanged by all-to-all over NVLink (NCCL), 8192 tokens per GPU (weak scaling).
 
 One JSON line is printed by rank 0:
   value     tokens/s with inputs resident in HBM (CUDA events on the launching stream)
@@ -42,6 +44,8 @@ WORKLOADS = {
     "cfg0": (1, 32, False, "gpt-oss-20b MoE layer, decode T=1"),
     "cfg1": (64, 32, True, "gpt-oss-20b MoE layer, batched decode T=64, Zipf(1.1) router bias"),
     "cfg2": (4096, 32, False, "gpt-oss-20b MoE layer, prefill T=4096, uniform routing"),
+    "cfg4": (8192, 128, False, "gpt-oss-120b-shaped MoE layer, 128 experts, T=8192 tokens per GPU, uniform routing, "
+                               "experts sharded over the GPUs (expert parallel) when more than one"),
 }
 
 
@@ -161,7 +165,7 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -171,7 +175,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload is None:
-        args.workload = "cfg1"
+        args.workload = "cfg1" if max(world, args.gpus) == 1 else "cfg4"
+    if args.steps is None:
+        args.steps = 2000 if WORKLOADS[args.workload][0] <= 64 else 50
     if args.impl == "reference":
         if args.steps > 64:
             args.steps = 8
@@ -190,19 +196,36 @@ def main():
 
     T, E, zipf, desc = WORKLOADS[args.workload]
     shape = synth.MoeShape(n_experts=E)
-    W = synth.make_weights(shape, 0)
-    n_batches = 8 if T <= 64 else 2
+    ep = world > 1
+    if ep and E % world:
+        raise SystemExit(f"{E} experts cannot be sharded over {world} ranks")
+    nl = E // world
+    W = synth.make_weights(shape, 0, experts=(rank * nl, (rank + 1) * nl) if ep else None)
+    decode = T <= 64
+    n_batches = 8 if decode else 2
     batches, lb = make_batches(T, W, zipf, n_batches, base_stream=100 * rank)
-    layer = MoeLayerSystem(shape, W, max_tokens=T, device=local_rank)
     dev = torch.device("cuda", local_rank)
+    layer = MoeLayerSystem(shape, W, max_tokens=T, device=local_rank, ep_rank=rank, ep_size=world)
+    if ep:
+        ids = [MoeLayerSystem.ep_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        layer.ep_init(ids[0])
     d_batches = [torch.from_numpy(b.view(np.int16)).to(dev) for b in batches]
     d_lb = None if lb is None else torch.from_numpy(lb).to(dev)
     d_out = torch.empty((T, shape.hidden), dtype=torch.float32, device=dev)
+    H, I, k = shape.hidden, shape.inter, shape.top_k
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world > 1:
+            t = torch.tensor([v], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
 
     def timed(fn, steps):
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -212,24 +235,28 @@ def main():
             fn(i)
         ev1.record()
         barrier()
-        ms = ev0.elapsed_time(ev1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return max_over_ranks(ev0.elapsed_time(ev1))
+
+    run = layer.run_ep if ep else layer.run
 
     def step_device(i):
-        layer.run(d_batches[i % n_batches], logit_bias=d_lb, out=d_out)
+        run(d_batches[i % n_batches], logit_bias=d_lb, out=d_out)
 
     # pinned host buffers for the end-to-end arm
     h_in = [torch.from_numpy(b.view(np.int16)).pin_memory() for b in batches]
     h_out = torch.empty((T, shape.hidden), dtype=torch.float32).pin_memory()
     h_lb = None if lb is None else torch.from_numpy(lb).pin_memory()
+    d_stage = torch.empty((T, shape.hidden), dtype=torch.int16, device=dev)
 
     def step_host(i):
-        layer.run_host_ptr(h_in[i % n_batches].data_ptr(), T, None if h_lb is None else h_lb.data_ptr(),
-                           h_out.data_ptr())
+        if ep:   # host -> device, expert-parallel pass, device -> host
+            d_stage.copy_(h_in[i % n_batches], non_blocking=True)
+            layer.run_ep(d_stage, logit_bias=d_lb, out=d_out)
+            h_out.copy_(d_out, non_blocking=True)
+            torch.cuda.synchronize()
+        else:
+            layer.run_host_ptr(h_in[i % n_batches].data_ptr(), T, None if h_lb is None else h_lb.data_ptr(),
+                               h_out.data_ptr())
 
     with ClockSampler(local_rank) as clocks:
         for i in range(max(args.warmup, 3)):
@@ -238,66 +265,99 @@ def main():
         ms = timed(step_device, args.steps)
         launches = layer.launch_count - l0
         # per-kernel durations over the same steps (CUDA events recorded inside the library)
-        layer.profile(True)
-        prof_steps = min(args.steps, 4000)
-        timed(step_device, prof_steps)
-        stage_ms, n_prof = layer.read_profile()
-        layer.profile(False)
+        stage_ms, n_prof, ep_ms, ep_rows = None, 0, None, 0
+        if ep:
+            acc = {}
+            for i in range(min(args.steps, 20)):
+                step_device(i)
+                tms, rows = layer.ep_times()
+                ep_rows += rows
+                for kk, v in tms.items():
+                    acc[kk] = acc.get(kk, 0.0) + v
+                n_prof += 1
+            ep_ms = {kk: max_over_ranks(v / n_prof) for kk, v in acc.items()}
+            ep_rows /= n_prof
+        else:
+            layer.profile(True)
+            timed(step_device, min(args.steps, 4000))
+            stage_ms, n_prof = layer.read_profile()
+            layer.profile(False)
         # end to end through host buffers
         e2e_steps = max(3, min(args.steps, 500))
         for i in range(3):
             step_host(i)
-        t0 = time.perf_counter()
         barrier()
+        t0 = time.perf_counter()
         for i in range(e2e_steps):
             step_host(i)
         barrier()
-        e2e_s = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([e2e_s], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_s = float(t.item())
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
     assert layer.status() == 0
 
     tokens_per_step = T * world
-    value = tokens_per_step * args.steps / (ms * 1e-3)
+    step_s = ms / args.steps * 1e-3
+    value = tokens_per_step / step_s
     e2e_value = tokens_per_step * e2e_steps / e2e_s
-
-    # roofline of the dominant kernel: the gate_up expert product streams, per touched
-    # expert, its nibbles + scales + bias once; plus the hidden rows in and the activation out
-    touched = []
-    for b in d_batches:
-        layer.run(b, logit_bias=d_lb, out=d_out)
-        touched.append(int((layer.read_dispatch()[0] > 0).sum()))
-    mean_touched = sum(touched) / len(touched)
-    H, I = shape.hidden, shape.inter
-    gu_expert_bytes = 2 * I * H // 2 + 2 * I * H // 32 + 2 * I * 2
-    gu_bytes = mean_touched * gu_expert_bytes + T * H * 2 + T * shape.top_k * I * 4
-    layer_bytes = mean_touched * shape.expert_bytes + shape.router_bytes + T * H * 2 + T * H * 4
     peaks, peak_kind = measured_peaks()
-    gu_ms = stage_ms["gate_up"] / max(n_prof, 1)
-    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else None
-    roofline = {"bound": "hbm", "kernel": "expert_mma_kernel<gate_up>", "achieved": achieved,
-                "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": None if achieved is None else achieved / peaks["hbm_gbs"],
-                "traffic": None, "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gu_ms,
-                "stage_ms_per_step": {k: v / max(n_prof, 1) for k, v in stage_ms.items()},
-                "layer_bytes_per_step": layer_bytes,
-                "layer_gbs": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
-                "layer_frac_of_peak": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                "layer_frac_of_8000": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / 8000.0,
-                "experts_touched_mean": mean_touched}
+    gu_expert_bytes = 2 * I * H // 2 + 2 * I * H // 32 + 2 * I * 2
+    gu_flops_per_pair = 2 * 2 * I * H
 
+    if ep:
+        # dominant unit: the local expert pass (both grouped GEMMs) over the rows this rank received
+        ex_ms = ep_ms["experts"]
+        achieved = ep_rows * shape.flops_per_pair / (ex_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "gmm_bs_kernel (gate_up + down, local experts)", "achieved": achieved,
+                    "peak": peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")), "peak_kind": peak_kind + " bf16 sustained",
+                    "unit": "TFLOP/s", "traffic": None, "ms_per_launch": ex_ms,
+                    "algorithmic_flops_per_launch": ep_rows * shape.flops_per_pair,
+                    "ep_stage_ms_per_step_max_over_ranks": ep_ms, "rows_received_rank0": ep_rows,
+                    "all_to_all_exposed_ms": ep_ms["dispatch_a2a"] + ep_ms["combine_a2a"]}
+        roofline["frac"] = achieved / roofline["peak"]
+    else:
+        touched = []
+        for bt in d_batches:
+            layer.run(bt, logit_bias=d_lb, out=d_out)
+            touched.append(int((layer.read_dispatch()[0] > 0).sum()))
+        mean_touched = sum(touched) / len(touched)
+        per_step = {kk: v / max(n_prof, 1) for kk, v in stage_ms.items()}
+        gu_ms = per_step["gate_up"]
+        layer_bytes = mean_touched * shape.expert_bytes + shape.router_bytes + T * H * 2 + T * H * 4
+        if decode:
+            # the gate_up product streams each touched expert's nibbles + scales + bias once,
+            # plus the hidden rows in and the fp32 activation out
+            gu_bytes = mean_touched * gu_expert_bytes + T * H * 2 + T * k * I * 4
+            achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved,
+                        "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+                        "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                        "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gu_ms}
+        else:
+            gu_flops = T * k * gu_flops_per_pair
+            achieved = gu_flops / (gu_ms * 1e-3) / 1e12
+            peak = peaks.get("bf16_tflops", 1590.0)
+            roofline = {"bound": "tensor", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peak,
+                        "peak_kind": peak_kind + " bf16 burst", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                        "algorithmic_flops_per_launch": gu_flops, "ms_per_launch": gu_ms,
+                        "layer_tflops": T * k * shape.flops_per_pair / step_s / 1e12,
+                        "layer_frac_of_mxfp4_nominal_9000": T * k * shape.flops_per_pair / step_s / 1e12 / 9000.0}
+        roofline.update({"stage_ms_per_step": per_step, "layer_bytes_per_step": layer_bytes,
+                         "layer_gbs": layer_bytes / step_s / 1e9,
+                         "layer_frac_of_peak": layer_bytes / step_s / 1e9 / peaks["hbm_gbs"],
+                         "layer_frac_of_8000": layer_bytes / step_s / 1e9 / 8000.0,
+                         "experts_touched_mean": mean_touched})
+
+    weights_mb = shape.expert_bytes * nl / 1e6
     line = {"metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": args.workload, "description": desc, "tokens_per_step_per_gpu": T,
-                       "hidden": H, "inter": I, "n_experts": E, "top_k": shape.top_k,
-                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
-                       "l2_policy": f"{n_batches} rotating batches; {shape.expert_bytes * E / 1e6:.0f} MB of expert "
-                                    "weights per pass exceed the 126 MB L2"},
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2 + (E * 4 if lb is not None else 0),
+                       "hidden": H, "inter": I, "n_experts": E, "top_k": k,
+                       "parallelism": "single GPU" if world == 1 else f"ep{world} (experts sharded, all-to-all over NCCL)",
+                       "l2_policy": f"{n_batches} rotating batches; {weights_mb:.0f} MB of expert weights per GPU "
+                                    "exceed the 126 MB L2"},
+            "e2e": {"value": e2e_value, "unit": "tokens/s",
+                    "h2d_bytes_per_step": T * H * 2 + (E * 4 if (lb is not None and not ep) else 0),
                     "d2h_bytes_per_step": T * H * 4, "steps": e2e_steps},
             "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks.summary()}
 

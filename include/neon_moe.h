@@ -92,6 +92,38 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden_bf16, int T, const f
 int neon_moe_forward_host(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
                           float* out_f32, int32_t* topk_idx, float* topk_w);
 
+/* ---- Expert parallelism (n_experts sharded evenly over ep_size GPUs of one node) -----------
+ * The engine is single-GPU (NeonEngine/src/lve_device.cpp:125-148 picks one device), so these
+ * have no engine counterpart; they follow the same conventions as neon_moe_forward.
+ *
+ * neon_moe_ep_unique_id: rank 0 obtains a 128-byte NCCL id and hands it to the other ranks by
+ * any host channel.  neon_moe_ep_init: every rank joins the communicator (collective call);
+ * NCCL is loaded with dlopen at this point, single-GPU users never need it. */
+int neon_moe_ep_unique_id(void* id128);
+int neon_moe_ep_init(neon_moe_handle* h, const void* id128);
+
+/* One pass over this rank's T tokens (collective: every rank calls it, T may differ per rank).
+ * Router on own tokens, all-to-all-v of token rows (bf16) to the experts' owners over NVLink,
+ * local grouped expert products, all-to-all-v of the outputs (fp32) back, routing-weighted
+ * combine.  Arguments as neon_moe_forward.  The call synchronises the stream once in the
+ * middle (the exchange sizes are needed on the host) and returns with the rest enqueued.
+ * A rank may receive at most 2*max_tokens*top_k rows per pass (twice the average); beyond
+ * that the call fails with NEON_MOE_EINVAL before any exchange is posted. */
+int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
+                        float* out_f32, int32_t* topk_idx, float* topk_w, void* cuda_stream);
+
+/* Device times of the last expert-parallel pass, ms[5] = {route+dispatch+pack, counts +
+ * dispatch all-to-all, local experts, combine all-to-all, combine}; rows received by this
+ * rank in *rows_received (may be NULL).  Synchronises. */
+int neon_moe_ep_times(neon_moe_handle* h, double* ms5, int* rows_received);
+
+/* Host-only exchange plan from the gathered histograms all_counts[ep_size][n_experts]: rows this
+ * rank sends to / receives from every peer with their offsets, and the local expert of each
+ * received row (row_expert may be NULL).  Needs no GPU; used by neon_moe_forward_ep. */
+int neon_moe_ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int rank, int32_t* send_rows,
+                     int32_t* send_off, int32_t* recv_rows, int32_t* recv_off, int32_t* row_expert,
+                     int row_expert_cap, int* n_recv);
+
 /* The layer pass for callers that must not allocate device memory.  It has no counterpart
  * in the reference engine.
  *

@@ -29,6 +29,12 @@ SIGNATURES = {
     "neon_moe_set_weights": (c_int, [c_void_p] * 9 + [c_int]),
     "neon_moe_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_forward_static": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "neon_moe_ep_unique_id": (c_int, [c_void_p]),
+    "neon_moe_ep_init": (c_int, [c_void_p, c_void_p]),
+    "neon_moe_forward_ep": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "neon_moe_ep_times": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
+    "neon_moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 ctypes.POINTER(c_int)]),
     "neon_moe_forward_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_read_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int)]),
     "neon_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_int)]),

@@ -1,0 +1,120 @@
+// Expert parallelism: experts are sharded evenly over the ranks of one node, the router is
+// replicated, every rank routes its own tokens.  Two exchanges per pass, both all-to-all-v
+// built from grouped ncclSend/ncclRecv over NVLink: token rows (bf16) to the ranks that own
+// their experts, and the experts' outputs (fp32) back.  NCCL is loaded with dlopen so the
+// single-GPU library has no link-time dependency on it.  Kernels never touch peer memory:
+// rows land in this GPU's own receive buffer first.
+#pragma once
+#include <dlfcn.h>
+#include <nccl.h>
+
+namespace neon {
+
+struct NcclApi {
+    void* lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+
+inline NcclApi& nccl_api() {
+    static NcclApi api;
+    if (api.lib) return api;
+    // RTLD_NOLOAD first: reuse the copy a host framework has already loaded, if any
+    api.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+    if (!api.lib) api.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!api.lib) api.lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!api.lib) return api;
+    bool all = true;
+    auto sym = [&](const char* name) {
+        void* p = dlsym(api.lib, name);
+        if (!p) all = false;
+        return p;
+    };
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+    api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+    api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+    api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+    api.ok = all;
+    return api;
+}
+
+// Exchange plan of one rank from the gathered histograms all_counts[ep_size][n_experts]
+// (all_counts[r][e] = entries rank r routes to global expert e).  Rows travel grouped by
+// destination rank and, inside a rank's segment, by ascending expert, so the receiver can
+// rebuild each row's expert from the counts alone.
+//   send_rows[r], send_off[r]: rows this rank sends to r and their start in its sorted order
+//   recv_rows[r], recv_off[r]: rows it receives from r and their start in its receive buffer
+//   row_expert[i]: LOCAL expert id (0..n_local-1) of received row i (at most cap entries)
+// Returns the number of received rows, or -1 when it exceeds cap.
+inline int ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int rank, int32_t* send_rows,
+                   int32_t* send_off, int32_t* recv_rows, int32_t* recv_off, int32_t* row_expert, int cap) {
+    const int nl = n_experts / ep_size, e_lo = rank * nl;
+    int so = 0, ro = 0;
+    for (int r = 0; r < ep_size; ++r) {
+        int s = 0, v = 0;
+        for (int e = 0; e < nl; ++e) {
+            s += all_counts[(size_t)rank * n_experts + r * nl + e];
+            v += all_counts[(size_t)r * n_experts + e_lo + e];
+        }
+        send_rows[r] = s;
+        send_off[r] = so;
+        recv_rows[r] = v;
+        recv_off[r] = ro;
+        so += s;
+        if (ro + v > cap) return -1;
+        if (row_expert) {
+            int i = ro;
+            for (int e = 0; e < nl; ++e)
+                for (int c = all_counts[(size_t)r * n_experts + e_lo + e]; c > 0; --c) row_expert[i++] = e;
+        }
+        ro += v;
+    }
+    return ro;
+}
+
+// xsend[p, :] = hidden[perm[p] / k, :] for the n sorted entries (16-byte vectors).
+__global__ void pack_rows_kernel(const uint16_t* __restrict__ hidden, const int32_t* __restrict__ perm, int k, int H, int n,
+                                 uint16_t* __restrict__ xsend) {
+    const int p = blockIdx.x;
+    if (p >= n) return;
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)(perm[p] / k) * H);
+    uint4* dst = reinterpret_cast<uint4*>(xsend + (size_t)p * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// out[t, c] = sum over slots s (in order) of w[t*k+s] * y[inv[t*k+s], c].
+__global__ void combine_weighted_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv,
+                                        const float* __restrict__ w, int T, int H, int k, float* __restrict__ out) {
+    const int t = blockIdx.y;
+    const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c4 * 4 >= H) return;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sl = 0; sl < k; ++sl) {
+        const int pos = inv[t * k + sl];
+        if (pos < 0) continue;
+        const float ws = w[t * k + sl];
+        const float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * H + 4 * c4);
+        s.x += ws * v.x; s.y += ws * v.y; s.z += ws * v.z; s.w += ws * v.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * H + 4 * c4) = s;
+}
+
+__global__ void fill_ones_kernel(float* p, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = 1.f;
+}
+
+}  // namespace neon

@@ -13,6 +13,7 @@
 #include <cuda_fp8.h>
 
 #include "moe_common.cuh"
+#include "moe_kernels.cuh"
 #include "sm100_ptx.cuh"
 
 namespace neon {
@@ -111,6 +112,43 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const int32_t* __rest
     for (int e = 0; e < n_local; ++e) {
         int lo = offset[e], hi = offset[e + 1];
         for (int r = lo + threadIdx.x; r < hi; r += blockDim.x) tl.row_tile[r] = s_first[e] + (r - lo) / tile_tokens;
+    }
+}
+
+// Dispatch and token tiles in one launch (one CTA of 1024 threads): the stable counting sort
+// of dispatch_block, then the tile list built by one thread per expert.
+__global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
+                                                              DispatchArrays d, int tile_tokens, TileList tl) {
+    extern __shared__ int dsmem[];
+    __shared__ int s_first[kMaxExperts + 1];
+    dispatch_block(idx, n, e_lo, n_local, d, dsmem);
+    __syncthreads();  // offsets and counts are in global memory, written by this CTA
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        int nt = 0;
+        for (int e = 0; e < n_local; ++e) {
+            s_first[e] = nt;
+            nt += (d.count[e] + tile_tokens - 1) / tile_tokens;
+        }
+        s_first[n_local] = nt;
+        *tl.n_tiles = nt;
+    }
+    __syncthreads();
+    for (int e = tid; e < n_local; e += blockDim.x) {
+        const int lo = d.offset[e], cnt = d.count[e];
+        int t = s_first[e];
+        for (int r = 0; r < cnt; r += tile_tokens, ++t) {
+            tl.expert[t] = e;
+            tl.row0[t] = lo + r;
+            tl.rows[t] = min(tile_tokens, cnt - r);
+        }
+    }
+    for (int i = tid; i < n; i += blockDim.x) {
+        const int pos = d.inv[i];
+        if (pos >= 0) {
+            const int e = idx[i] - e_lo;
+            tl.row_tile[pos] = s_first[e] + (pos - d.offset[e]) / tile_tokens;
+        }
     }
 }
 

@@ -227,6 +227,103 @@ router_topk_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------
+// Router for the main path: one CTA of 1024 threads per token, 16-byte loads, all loads of
+// a dot product issued before the first use.  Same arithmetic contract as above: fp32
+// accumulation in a fixed order that is identical for every expert, ties to the lower id.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+router_topk_wide_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
+                        const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H, int E,
+                        int k, int32_t* __restrict__ idx, float* __restrict__ w) {
+    extern __shared__ __align__(16) unsigned char rsmem[];
+    uint4* xs = reinterpret_cast<uint4*>(rsmem);            // [H/8] bf16 x 8
+    float* lg = reinterpret_cast<float*>(rsmem + H * 2);    // [E]
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nvec = H / 8;
+    const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+    for (int i = tid; i < nvec; i += 1024) xs[i] = xrow[i];
+    __syncthreads();
+    for (int e = warp; e < E; e += 32) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(wr + (size_t)e * H);
+        float acc = 0.f;
+        constexpr int UNROLL = 12;  // 12 * 32 lanes * 8 = 3072 >= 2880 columns in one batch of loads
+        for (int base = 0; base < nvec; base += 32 * UNROLL) {
+            uint4 wv[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int i = base + u * 32 + lane;
+                wv[u] = i < nvec ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int i = base + u * 32 + lane;
+                if (i < nvec) {
+                    uint4 xv = xs[i];
+                    const uint32_t xa[4] = {xv.x, xv.y, xv.z, xv.w}, wa[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc = fmaf(__uint_as_float(xa[j] << 16), __uint_as_float(wa[j] << 16), acc);
+                        acc = fmaf(__uint_as_float(xa[j] & 0xffff0000u), __uint_as_float(wa[j] & 0xffff0000u), acc);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            float v = acc + bf16_bits_to_float(br[e]);
+            if (logit_bias) v += logit_bias[e];
+            lg[e] = v;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long keys[kMaxExperts / 32];
+#pragma unroll
+        for (int j = 0; j < kMaxExperts / 32; ++j) {
+            int e = lane + 32 * j;
+            keys[j] = (e < E) ? logit_key(lg[e], e) : 0ull;
+        }
+        float sel[kMaxTopK];
+        int seli[kMaxTopK];
+#pragma unroll
+        for (int s = 0; s < kMaxTopK; ++s) {
+            if (s < k) {
+                unsigned long long best = 0ull;
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j) best = keys[j] > best ? keys[j] : best;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                    best = other > best ? other : best;
+                }
+                int e = 0x7fffffff - (int)(uint32_t)(best & 0xffffffffull);
+                seli[s] = e;
+                sel[s] = lg[e];
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j)
+                    if (lane + 32 * j == e) keys[j] = 0ull;
+            }
+        }
+        if (lane == 0) {
+            float m = sel[0], den = 0.f, pr[kMaxTopK];
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    pr[s] = expf(sel[s] - m);
+                    den += pr[s];
+                }
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    idx[t * k + s] = seli[s];
+                    w[t * k + s] = pr[s] / den;
+                }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Grouped MXFP4 expert product on mma.m16n8k16 (weights = the 16-row M operand, tokens =
 // the N operand, 8 per n-tile).  Each warp owns one 16-row tile of one expert and walks
 // the whole K; the expert's weights are read once per chunk of 8*NT tokens (once in total

@@ -13,6 +13,7 @@
 
 #include "moe_kernels.cuh"
 #include "gmm_sm100.cuh"
+#include "ep.cuh"
 
 using namespace neon;
 
@@ -55,6 +56,16 @@ struct neon_moe_handle {
     int32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_tiles = nullptr, *row_tile = nullptr;
     int tile_cap = 0, kp_h = 0, kp_i = 0;
     CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
+    // expert parallelism: source-side routing/dispatch over all experts, exchange buffers
+    ncclComm_t comm = nullptr;
+    int n_src = 0, n_cap = 0;     // entries this rank routes (max) / entries it can receive
+    int32_t *s_idx = nullptr, *s_count = nullptr, *s_offset = nullptr, *s_perm = nullptr, *s_inv = nullptr;
+    int32_t *all_counts_d = nullptr, *row_expert = nullptr, *host_pinned = nullptr;
+    float *s_w = nullptr, *yrecv = nullptr, *yback = nullptr, *ones = nullptr;
+    uint16_t *xsend = nullptr, *xrecv = nullptr;
+    cudaEvent_t ep_ev[6] = {};
+    bool ep_timed = false;
+    int ep_last_recv = 0;
     // per-stage profiling: 5 events per forward
     bool profiling = false;
     std::vector<cudaEvent_t> events;
@@ -94,9 +105,14 @@ void free_all(neon_moe_handle* h) {
                     h->idx, h->count, h->offset, h->perm, h->inv, h->route_w, h->y, h->a_hi, h->a_lo,
                     h->status, h->st_hidden, h->st_out, h->st_bias, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
                     h->x_act, h->a_act, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
-                    h->n_tiles, h->row_tile};
+                    h->n_tiles, h->row_tile, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
+                    h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    if (h->host_pinned) cudaFreeHost(h->host_pinned);
+    for (cudaEvent_t ev : h->ep_ev)
+        if (ev) cudaEventDestroy(ev);
+    if (h->comm && nccl_api().ok) nccl_api().CommDestroy(h->comm);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);
     for (cudaEvent_t ev : h->events) cudaEventDestroy(ev);
 }
@@ -269,14 +285,15 @@ int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, cons
 }
 
 template <int TERMS, bool FROM_BF16>
-void launch_split(neon_moe_handle* h, int tile_tokens, const void* src, int K, int n, uint8_t* act, cudaStream_t st) {
+void launch_split(neon_moe_handle* h, int tile_tokens, const void* src, int K, int n, int top_k, uint8_t* act,
+                  cudaStream_t st) {
     const int n_chunks = round_up_int(K, kChunkK) / kChunkK;
     const dim3 grid((n * n_chunks + 7) / 8);
     if (tile_tokens <= 32)
-        split_rows_kernel<TERMS, FROM_BF16, true><<<grid, 256, 0, st>>>(src, h->perm, h->cfg.top_k, K, n, h->row_tile,
+        split_rows_kernel<TERMS, FROM_BF16, true><<<grid, 256, 0, st>>>(src, h->perm, top_k, K, n, h->row_tile,
                                                                         h->tile_row0, h->tile_rows, tile_tokens, act);
     else
-        split_rows_kernel<TERMS, FROM_BF16, false><<<grid, 256, 0, st>>>(src, h->perm, h->cfg.top_k, K, n, h->row_tile,
+        split_rows_kernel<TERMS, FROM_BF16, false><<<grid, 256, 0, st>>>(src, h->perm, top_k, K, n, h->row_tile,
                                                                          h->tile_row0, h->tile_rows, tile_tokens, act);
     h->launches++;
 }
@@ -330,7 +347,11 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         return rc;
     };
     if (cudaSetDevice(cfg->device) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaSetDevice failed"));
-    const size_t n = (size_t)cfg->max_tokens * cfg->top_k;
+    // entries the local expert pass may see: this rank's own when alone; with expert parallelism
+    // up to twice the per-rank average (all ranks route max_tokens tokens), beyond which a pass fails
+    h->n_src = cfg->max_tokens * cfg->top_k;
+    h->n_cap = cfg->ep_size > 1 ? 2 * h->n_src : h->n_src;
+    const size_t n = (size_t)h->n_cap;
     int rc = 0;
     if ((rc = dev_alloc(h, &h->idx, n)) || (rc = dev_alloc(h, &h->route_w, n)) ||
         (rc = dev_alloc(h, &h->count, (size_t)h->n_local)) || (rc = dev_alloc(h, &h->offset, (size_t)h->n_local + 1)) ||
@@ -363,6 +384,21 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         (rc = dev_alloc(h, &h->tile_row0, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile_rows, (size_t)h->tile_cap)) ||
         (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
         return bail(rc);
+    if (cfg->ep_size > 1) {
+        const size_t ns = (size_t)h->n_src, E = (size_t)cfg->n_experts, Hh = (size_t)cfg->hidden;
+        if ((rc = dev_alloc(h, &h->s_idx, ns)) || (rc = dev_alloc(h, &h->s_w, ns)) || (rc = dev_alloc(h, &h->s_count, E)) ||
+            (rc = dev_alloc(h, &h->s_offset, E + 1)) || (rc = dev_alloc(h, &h->s_perm, ns)) ||
+            (rc = dev_alloc(h, &h->s_inv, ns)) || (rc = dev_alloc(h, &h->all_counts_d, E * cfg->ep_size)) ||
+            (rc = dev_alloc(h, &h->row_expert, n)) || (rc = dev_alloc(h, &h->ones, n)) ||
+            (rc = dev_alloc(h, &h->xsend, ns * Hh)) || (rc = dev_alloc(h, &h->xrecv, n * Hh)) ||
+            (rc = dev_alloc(h, &h->yrecv, ns * Hh)) || (rc = dev_alloc(h, &h->yback, n * Hh)))
+            return bail(rc);
+        if (cudaMallocHost(&h->host_pinned, (E * cfg->ep_size + n) * sizeof(int32_t)) != cudaSuccess)
+            return bail(fail(h, NEON_MOE_ECUDA, "cudaMallocHost failed"));
+        fill_ones_kernel<<<(unsigned)((n + 255) / 256), 256>>>(h->ones, (int)n);
+        for (cudaEvent_t& ev : h->ep_ev)
+            if (cudaEventCreate(&ev) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaEventCreate failed"));
+    }
     if (cudaMemset(h->status, 0, 16) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
     if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(fail(h, NEON_MOE_ECUDA, "cudaStreamCreate failed"));
@@ -403,40 +439,28 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
     return NEON_MOE_OK;
 }
 
-int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
-                     int32_t* topk_idx, float* topk_w, void* cuda_stream) {
-    if (!h) return NEON_MOE_EINVAL;
-    if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "forward before set_weights");
-    if (h->cfg.ep_size != 1) return fail(h, NEON_MOE_ESTATE, "forward needs ep_size == 1; use the expert-parallel entry points");
-    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
-    if (T == 0) { h->last_n = 0; return NEON_MOE_OK; }
-    if (!hidden || !out) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
-    CU(h, cudaSetDevice(h->cfg.device));
-    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-    const int H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts, k = h->cfg.top_k;
-    const int n = T * k;
-    const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
-
-    mark(h, st, prof);
-    router_topk_kernel<256><<<T, 256, (H + E) * sizeof(float), st>>>(
-        static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, h->idx, h->route_w);
-    h->launches++;
+// Dispatch + expert products + combine for n = rows * k_eff entries: entry i uses activation
+// row i / k_eff of `hidden` and expert idx[i] - e_lo; `weighted_out` gets, per row, the sum of
+// its k_eff slots' down outputs, each multiplied by route_w[i].  Used by the single-GPU pass
+// (rows = tokens, k_eff = top_k) and by the expert-parallel local pass (rows = received
+// rows, k_eff = 1, route_w = 1).
+static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_eff, const int32_t* idx, int e_lo,
+                        const float* route_w, float* out, cudaStream_t st, bool prof) {
+    const int H = h->cfg.hidden, I = h->cfg.inter, EL = h->n_local;
+    const int n = rows * k_eff;
     DispatchArrays d{h->count, h->offset, h->perm, h->inv};
-    dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->idx, n, 0, E, d);
-    h->launches++;
-
     if (h->path == 2) {
-        const int tt = tile_tokens_for(T);
+        const int tt = tile_tokens_for(rows);
         TileList tl{h->tile_expert, h->tile_row0, h->tile_rows, h->n_tiles, h->row_tile};
-        build_tiles_kernel<<<1, 1024, 0, st>>>(h->offset, h->n_local, tt, tl);
+        dispatch_tiles_kernel<<<1, 1024, (size_t)(33 * EL) * sizeof(int), st>>>(idx, n, e_lo, EL, d, tt, tl);
         h->launches++;
         const int nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
-        launch_split<2, true>(h, tt, hidden, H, n, h->x_act, st);
+        launch_split<2, true>(h, tt, hidden, H, n, k_eff, h->x_act, st);
         GmmParams g{};
         g.tile_expert = h->tile_expert; g.tile_row0 = h->tile_row0; g.tile_rows = h->tile_rows; g.n_tiles = h->n_tiles;
         g.a_tx_bytes = h->a_tx_bytes; g.trace = h->trace;
         g.a_out = h->a_f32; g.inter = I; g.limit = h->cfg.swiglu_limit; g.alpha = h->cfg.swiglu_alpha;
-        g.perm = h->perm; g.route_w = h->route_w; g.y = h->y; g.hidden = H; g.status = h->status;
+        g.perm = h->perm; g.route_w = route_w; g.y = h->y; g.hidden = H; g.status = h->status;
         // gate_up: rows 2I, K = H
         g.sfa = h->gu_sfa; g.act = h->x_act; g.bias = h->gu_bias;
         g.m_tiles = 2 * I / 128; g.n_chunks = nch_h; g.rows_total = 2 * I;
@@ -444,7 +468,7 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float*
         int rc = launch_gmm<2, true>(h, tt, h->tm_gu, h->tm_gu2, g, st);
         if (rc) return rc;
         mark(h, st, prof);
-        launch_split<4, false>(h, tt, h->a_f32, I, n, h->a_act, st);
+        launch_split<4, false>(h, tt, h->a_f32, I, n, k_eff, h->a_act, st);
         // down: rows H, K = I
         g.sfa = h->dn_sfa; g.act = h->a_act; g.bias = h->dn_bias;
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
@@ -452,39 +476,196 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float*
         if (rc) return rc;
         mark(h, st, prof);
     } else {
+        dispatch_kernel<<<1, 1024, (size_t)(33 * EL) * sizeof(int), st>>>(idx, n, e_lo, EL, d);
+        h->launches++;
         ExpertParams p{};
         p.offset = h->offset;
         p.perm = h->perm;
-        p.top_k = k;
+        p.top_k = k_eff;
         p.x = static_cast<const uint16_t*>(hidden);
         p.a_hi = h->a_hi;
         p.a_lo = h->a_lo;
         p.limit = h->cfg.swiglu_limit;
         p.alpha = h->cfg.swiglu_alpha;
-        p.route_w = h->route_w;
+        p.route_w = route_w;
         p.y = h->y;
         // gate_up: rows 2I, K = H
         p.wq = h->gu_wq; p.sq = h->gu_sq; p.bias = h->gu_bias;
         p.rows = 2 * I; p.K = H; p.tiles = 2 * I / 16; p.nbp = H / 64;
         mark(h, st, prof);
-        launch_expert<true>(h, p, T, st);
+        launch_expert<true>(h, p, rows, st);
         mark(h, st, prof);
         // down: rows H, K = I
         p.wq = h->dn_wq; p.sq = h->dn_sq; p.bias = h->dn_bias;
         p.rows = H; p.K = I; p.tiles = H / 16; p.nbp = I / 64;
-        launch_expert<false>(h, p, T, st);
+        launch_expert<false>(h, p, rows, st);
         mark(h, st, prof);
     }
-
-    dim3 cgrid((H / 4 + 127) / 128, T);
-    combine_kernel<<<cgrid, 128, 0, st>>>(h->y, h->inv, T, H, k, out);
+    dim3 cgrid((H / 4 + 127) / 128, rows);
+    combine_kernel<<<cgrid, 128, 0, st>>>(h->y, h->inv, rows, H, k_eff, out);
     h->launches++;
     mark(h, st, prof);
+    return NEON_MOE_OK;
+}
+
+static void launch_router(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, int32_t* idx, float* w,
+                          cudaStream_t st) {
+    const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k;
+    if (h->path == 2)
+        router_topk_wide_kernel<<<T, 1024, H * 2 + E * sizeof(float), st>>>(
+            static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, idx, w);
+    else
+        router_topk_kernel<256><<<T, 256, (H + E) * sizeof(float), st>>>(
+            static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, idx, w);
+    h->launches++;
+}
+
+int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
+                     int32_t* topk_idx, float* topk_w, void* cuda_stream) {
+    if (!h) return NEON_MOE_EINVAL;
+    if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "forward before set_weights");
+    if (h->cfg.ep_size != 1) return fail(h, NEON_MOE_ESTATE, "forward needs ep_size == 1; use neon_moe_forward_ep");
+    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
+    if (T == 0) { h->last_n = 0; return NEON_MOE_OK; }
+    if (!hidden || !out) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
+    CU(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const int k = h->cfg.top_k, n = T * k;
+    const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
+    mark(h, st, prof);
+    launch_router(h, hidden, T, logit_bias, h->idx, h->route_w, st);
+    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, out, st, prof);
+    if (rc) return rc;
     if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
     if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
     CU(h, cudaGetLastError());
     h->last_stream = st;
     h->last_n = n;
+    return NEON_MOE_OK;
+}
+
+// ---- expert parallelism --------------------------------------------------------------------
+#define NC(h, call)                                                                                  \
+    do {                                                                                             \
+        ncclResult_t r_ = (call);                                                                    \
+        if (r_ != ncclSuccess)                                                                       \
+            return fail(h, NEON_MOE_ENCCL, "%s failed: %s", #call, nccl_api().GetErrorString(r_)); \
+    } while (0)
+
+int neon_moe_ep_unique_id(void* id128) {
+    if (!id128) return NEON_MOE_EINVAL;
+    if (!nccl_api().ok) return fail(nullptr, NEON_MOE_ENCCL, "libnccl.so.2 could not be loaded");
+    ncclUniqueId id;
+    NC(nullptr, nccl_api().GetUniqueId(&id));
+    memcpy(id128, id.internal, NCCL_UNIQUE_ID_BYTES);
+    return NEON_MOE_OK;
+}
+
+int neon_moe_ep_init(neon_moe_handle* h, const void* id128) {
+    if (!h || !id128) return NEON_MOE_EINVAL;
+    if (h->cfg.ep_size < 2) return fail(h, NEON_MOE_ESTATE, "ep_init needs ep_size >= 2");
+    if (!nccl_api().ok) return fail(h, NEON_MOE_ENCCL, "libnccl.so.2 could not be loaded");
+    CU(h, cudaSetDevice(h->cfg.device));
+    ncclUniqueId id;
+    memcpy(id.internal, id128, NCCL_UNIQUE_ID_BYTES);
+    NC(h, nccl_api().CommInitRank(&h->comm, h->cfg.ep_size, id, h->cfg.ep_rank));
+    return NEON_MOE_OK;
+}
+
+int neon_moe_ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int rank, int32_t* send_rows,
+                     int32_t* send_off, int32_t* recv_rows, int32_t* recv_off, int32_t* row_expert, int row_expert_cap,
+                     int* n_recv) {
+    if (!all_counts || !send_rows || !send_off || !recv_rows || !recv_off || !n_recv || ep_size <= 0 || n_experts <= 0 ||
+        n_experts % ep_size || rank < 0 || rank >= ep_size)
+        return NEON_MOE_EINVAL;
+    *n_recv = ep_plan(all_counts, ep_size, n_experts, rank, send_rows, send_off, recv_rows, recv_off, row_expert, row_expert_cap);
+    return *n_recv < 0 ? NEON_MOE_EINVAL : NEON_MOE_OK;
+}
+
+int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
+                        int32_t* topk_idx, float* topk_w, void* cuda_stream) {
+    if (!h) return NEON_MOE_EINVAL;
+    if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "forward_ep before set_weights");
+    if (!h->comm) return fail(h, NEON_MOE_ESTATE, "forward_ep before ep_init");
+    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
+    if (T > 0 && (!hidden || !out)) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
+    CU(h, cudaSetDevice(h->cfg.device));
+    NcclApi& nc = nccl_api();
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k, G = h->cfg.ep_size, me = h->cfg.ep_rank;
+    const int n = T * k;
+    // 1. route own tokens, sort entries by global expert (= by destination rank, then expert), pack rows
+    CU(h, cudaEventRecord(h->ep_ev[0], st));
+    DispatchArrays sd{h->s_count, h->s_offset, h->s_perm, h->s_inv};
+    if (T > 0) launch_router(h, hidden, T, logit_bias, h->s_idx, h->s_w, st);
+    dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->s_idx, n, 0, E, sd);
+    h->launches++;
+    if (n > 0) {
+        pack_rows_kernel<<<n, 128, 0, st>>>(static_cast<const uint16_t*>(hidden), h->s_perm, k, H, n, h->xsend);
+        h->launches++;
+    }
+    CU(h, cudaEventRecord(h->ep_ev[1], st));
+    // 2. every rank learns every histogram; sizes are needed on the host to post the exchange
+    NC(h, nc.AllGather(h->s_count, h->all_counts_d, (size_t)E, ncclInt32, h->comm, st));
+    int32_t* all_counts = h->host_pinned;
+    int32_t* row_expert_h = h->host_pinned + (size_t)E * G;
+    CU(h, cudaMemcpyAsync(all_counts, h->all_counts_d, (size_t)E * G * 4, cudaMemcpyDeviceToHost, st));
+    CU(h, cudaStreamSynchronize(st));
+    int32_t send_rows[64], send_off[64], recv_rows[64], recv_off[64];
+    if (G > 64) return fail(h, NEON_MOE_EINVAL, "ep_size above 64");
+    const int R = ep_plan(all_counts, G, E, me, send_rows, send_off, recv_rows, recv_off, row_expert_h, h->n_cap);
+    if (R < 0) return fail(h, NEON_MOE_EINVAL, "this rank would receive more than %d rows (2x the per-rank average)", h->n_cap);
+    h->ep_last_recv = R;
+    if (R > 0) CU(h, cudaMemcpyAsync(h->row_expert, row_expert_h, (size_t)R * 4, cudaMemcpyHostToDevice, st));
+    // 3. token rows to the owners of their experts
+    NC(h, nc.GroupStart());
+    for (int r = 0; r < G; ++r) {
+        if (send_rows[r]) NC(h, nc.Send(h->xsend + (size_t)send_off[r] * H, (size_t)send_rows[r] * H, ncclBfloat16, r, h->comm, st));
+        if (recv_rows[r]) NC(h, nc.Recv(h->xrecv + (size_t)recv_off[r] * H, (size_t)recv_rows[r] * H, ncclBfloat16, r, h->comm, st));
+    }
+    NC(h, nc.GroupEnd());
+    CU(h, cudaEventRecord(h->ep_ev[2], st));
+    // 4. local experts on the received rows (one slot per row, unit weight); yback is in receive order
+    if (R > 0) {
+        int rc = experts_core(h, h->xrecv, R, 1, h->row_expert, 0, h->ones, h->yback, st, false);
+        if (rc) return rc;
+    }
+    CU(h, cudaEventRecord(h->ep_ev[3], st));
+    // 5. outputs back to the token owners, in the order the rows were sent
+    NC(h, nc.GroupStart());
+    for (int r = 0; r < G; ++r) {
+        if (recv_rows[r]) NC(h, nc.Send(h->yback + (size_t)recv_off[r] * H, (size_t)recv_rows[r] * H, ncclFloat32, r, h->comm, st));
+        if (send_rows[r]) NC(h, nc.Recv(h->yrecv + (size_t)send_off[r] * H, (size_t)send_rows[r] * H, ncclFloat32, r, h->comm, st));
+    }
+    NC(h, nc.GroupEnd());
+    CU(h, cudaEventRecord(h->ep_ev[4], st));
+    // 6. routing-weighted sum of each token's slots, fixed slot order
+    if (T > 0) {
+        dim3 cgrid((H / 4 + 127) / 128, T);
+        combine_weighted_kernel<<<cgrid, 128, 0, st>>>(h->yrecv, h->s_inv, h->s_w, T, H, k, out);
+        h->launches++;
+    }
+    CU(h, cudaEventRecord(h->ep_ev[5], st));
+    h->ep_timed = true;
+    if (topk_idx && n) CU(h, cudaMemcpyAsync(topk_idx, h->s_idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
+    if (topk_w && n) CU(h, cudaMemcpyAsync(topk_w, h->s_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
+    CU(h, cudaGetLastError());
+    h->last_stream = st;
+    h->last_n = R;
+    return NEON_MOE_OK;
+}
+
+int neon_moe_ep_times(neon_moe_handle* h, double* ms5, int* rows_received) {
+    if (!h || !ms5) return NEON_MOE_EINVAL;
+    if (!h->ep_timed) return fail(h, NEON_MOE_ESTATE, "no expert-parallel pass has run");
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaEventSynchronize(h->ep_ev[5]));
+    for (int i = 0; i < 5; ++i) {
+        float t = 0.f;
+        CU(h, cudaEventElapsedTime(&t, h->ep_ev[i], h->ep_ev[i + 1]));
+        ms5[i] = t;
+    }
+    if (rows_received) *rows_received = h->ep_last_recv;
     return NEON_MOE_OK;
 }
 

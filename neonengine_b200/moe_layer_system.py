@@ -95,6 +95,50 @@ class MoeLayerSystem:
             raise RuntimeError(f"neon_moe_forward_static failed ({rc}): {self._lib.neon_moe_last_error(None).decode()}")
         return (out, idx, w) if want_routing else out
 
+    # -- expert parallelism --------------------------------------------------------------
+    @staticmethod
+    def ep_unique_id() -> bytes:
+        """128-byte NCCL id; rank 0 creates it and passes it to the other ranks."""
+        lib = _lib.load()
+        buf = ctypes.create_string_buffer(128)
+        rc = lib.neon_moe_ep_unique_id(buf)
+        if rc != 0:
+            raise RuntimeError(f"neon_moe_ep_unique_id failed ({rc}): {lib.neon_moe_last_error(None).decode()}")
+        return buf.raw
+
+    def ep_init(self, unique_id: bytes) -> None:
+        """Collective: every rank of the expert-parallel group calls it with the same id."""
+        assert len(unique_id) == 128
+        self._check(self._lib.neon_moe_ep_init(self._h, ctypes.c_char_p(unique_id)), "neon_moe_ep_init")
+
+    def run_ep(self, hidden, logit_bias=None, out=None, want_routing=False, stream=None):
+        """Expert-parallel pass over this rank's tokens (collective across the group)."""
+        import torch
+        T = hidden.shape[0]
+        assert hidden.is_cuda and hidden.is_contiguous() and hidden.element_size() == 2
+        dev = hidden.device
+        if out is None:
+            out = torch.empty((T, self.shape.hidden), dtype=torch.float32, device=dev)
+        idx = w = None
+        if want_routing:
+            idx = torch.empty((T, self.shape.top_k), dtype=torch.int32, device=dev)
+            w = torch.empty((T, self.shape.top_k), dtype=torch.float32, device=dev)
+        st = (stream or torch.cuda.current_stream(dev)).cuda_stream
+        rc = self._lib.neon_moe_forward_ep(self._h, hidden.data_ptr(), T,
+                                           None if logit_bias is None else logit_bias.data_ptr(),
+                                           out.data_ptr(), None if idx is None else idx.data_ptr(),
+                                           None if w is None else w.data_ptr(), st)
+        self._check(rc, "neon_moe_forward_ep")
+        return (out, idx, w) if want_routing else out
+
+    def ep_times(self):
+        """Device times (ms) of the last expert-parallel pass and the rows this rank received."""
+        ms = (ctypes.c_double * 5)()
+        rows = ctypes.c_int(0)
+        self._check(self._lib.neon_moe_ep_times(self._h, ms, ctypes.byref(rows)), "neon_moe_ep_times")
+        names = ("route_pack", "dispatch_a2a", "experts", "combine_a2a", "combine")
+        return dict(zip(names, list(ms))), rows.value
+
     # -- host path -----------------------------------------------------------------------
     def run_host(self, hidden: np.ndarray, logit_bias: np.ndarray | None = None, out: np.ndarray | None = None,
                  want_routing: bool = False):
@@ -161,3 +205,21 @@ class MoeLayerSystem:
             self.close()
         except Exception:
             pass
+
+
+def ep_plan(all_counts: np.ndarray, rank: int, cap: int | None = None):
+    """Host-side exchange plan (``neon_moe_ep_plan``): ``all_counts[ep_size, n_experts]`` ->
+    (send_rows, send_off, recv_rows, recv_off, row_expert).  Needs no GPU."""
+    lib = _lib.load()
+    all_counts = np.ascontiguousarray(all_counts, np.int32)
+    G, E = all_counts.shape
+    cap = int(all_counts.sum()) if cap is None else cap
+    outs = [np.zeros(G, np.int32) for _ in range(4)]
+    row_expert = np.zeros(max(cap, 1), np.int32)
+    n_recv = ctypes.c_int(0)
+    rc = lib.neon_moe_ep_plan(ctypes.c_void_p(all_counts.ctypes.data), G, E, rank,
+                              *[ctypes.c_void_p(o.ctypes.data) for o in outs],
+                              ctypes.c_void_p(row_expert.ctypes.data), cap, ctypes.byref(n_recv))
+    if rc != 0:
+        raise RuntimeError(f"neon_moe_ep_plan failed ({rc})")
+    return (*outs, row_expert[:n_recv.value])

@@ -116,13 +116,10 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const int32_t* __rest
 }
 
 // Dispatch and token tiles in one launch (one CTA of 1024 threads): the stable counting sort
-// of dispatch_block, then the tile list built by one thread per expert.
-__global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
-                                                              DispatchArrays d, int tile_tokens, TileList tl) {
-    extern __shared__ int dsmem[];
-    __shared__ int s_first[kMaxExperts + 1];
-    dispatch_block(idx, n, e_lo, n_local, d, dsmem);
-    __syncthreads();  // offsets and counts are in global memory, written by this CTA
+// of dispatch_block, then up to two tile lists (the gate_up and the down product may cut the
+// same sorted rows into tiles of different sizes), one thread per expert.
+__device__ void build_tile_list(const int32_t* __restrict__ idx, int n, int e_lo, int n_local, const DispatchArrays& d,
+                                int tile_tokens, const TileList& tl, int* s_first) {
     const int tid = threadIdx.x;
     if (tid == 0) {
         int nt = 0;
@@ -150,6 +147,20 @@ __global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __r
             tl.row_tile[pos] = s_first[e] + (pos - d.offset[e]) / tile_tokens;
         }
     }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
+                                                              DispatchArrays d, int tile_tokens, TileList tl,
+                                                              int tile_tokens2, TileList tl2, unsigned* zero_n) {
+    extern __shared__ int dsmem[];
+    __shared__ int s_first[kMaxExperts + 1];
+    if (zero_n)
+        for (int i = threadIdx.x; i < n; i += blockDim.x) zero_n[i] = 0u;
+    dispatch_block(idx, n, e_lo, n_local, d, dsmem);
+    __syncthreads();  // offsets and counts are in global memory, written by this CTA
+    build_tile_list(idx, n, e_lo, n_local, d, tile_tokens, tl, s_first);
+    if (tile_tokens2 > 0) build_tile_list(idx, n, e_lo, n_local, d, tile_tokens2, tl2, s_first);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -168,9 +179,12 @@ __global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __r
 // Two block layouts.  Sequential (prefill, tile_tokens = 128): as above, one MMA per term.
 // Stacked (decode, tile_tokens <= 32): the terms are stacked along N - B row t*npad + j is
 // term t of tile row j, npad = rows rounded up to 8 - so one MMA covers all terms and reads
-// the weight tile once; the block is [512 B scale atom][512 B pad][TERMS*npad rows x 128 B].
+// the weight tile once; the block is just TERMS*npad rows x 128 B.  Stacked terms use one
+// power-of-two scale per ROW (term t: row scale / 16^t) instead of per 32-block scales; it is
+// applied by the GEMM epilogue when it adds the terms' columns, so the tensor core sees unit
+// activation scales and no activation scale factor ever travels (split_rows_stacked_kernel).
 __host__ __device__ inline size_t act_block_bytes(int terms, int tile_tokens, bool stacked) {
-    if (stacked) return 1024 + (size_t)terms * tile_tokens * 128;
+    if (stacked) return (size_t)terms * tile_tokens * 128;
     return (size_t)terms * 512 + (size_t)(tile_tokens / 8) * terms * 1024;
 }
 
@@ -233,6 +247,91 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
     }
 }
 
+// Largest magnitude of every row (one warp per row, all loads issued before the reduction);
+// used when no producer kernel has already computed it.
+template <bool FROM_BF16>
+__global__ void __launch_bounds__(256) row_amax_kernel(const void* __restrict__ src, int K, int n_rows,
+                                                       float* __restrict__ amax_out) {
+    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (r >= n_rows) return;
+    float m = 0.f;
+    if (FROM_BF16) {
+        const uint2* row = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(src) + (size_t)r * K);
+        for (int i = lane; i < K / 4; i += 32) {
+            uint2 raw = row[i];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(raw.x << 16)), fabsf(__uint_as_float(raw.x & 0xffff0000u))),
+                               fmaxf(fabsf(__uint_as_float(raw.y << 16)), fabsf(__uint_as_float(raw.y & 0xffff0000u)))));
+        }
+    } else {
+        const float4* row = reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)r * K);
+        for (int i = lane; i < K / 4; i += 32) {
+            float4 v = row[i];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) amax_out[r] = m;
+}
+
+// Stacked-mode splitting: one warp per (sorted row p, 128-wide chunk), lane l owns 4 elements.
+// The row's largest magnitude comes precomputed: amax_in[perm[p]/top_k] for gathered bf16 hidden
+// rows (FROM_BF16), amax_in[p] otherwise; with amax_in == null every row uses the bound
+// amax_const (the clamped SwiGLU output is bounded by limit*(limit+1), so the down product's
+// input needs no measurement at all).  Term t is RN_e4m3(residual / (s / 16^t)) with
+// s = 2^(floor(log2 amax) - 7); row_scale[p] = s.
+template <int TERMS, bool FROM_BF16>
+__global__ void __launch_bounds__(256) split_rows_stacked_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm,
+                                                                 int top_k, int K, int n_rows,
+                                                                 const int32_t* __restrict__ row_tile,
+                                                                 const int32_t* __restrict__ tile_row0,
+                                                                 const int32_t* __restrict__ tile_rows, int tile_tokens,
+                                                                 const float* __restrict__ amax_in, float amax_const,
+                                                                 uint8_t* __restrict__ act, float* __restrict__ row_scale) {
+    const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows * n_chunks) return;
+    const int p = warp / n_chunks, c = warp - p * n_chunks;
+    const int src_row = FROM_BF16 ? perm[p] / top_k : p;
+    const int k0 = c * kChunkK + 4 * lane;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k0 < K) {
+        if (FROM_BF16) {
+            uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(src) + (size_t)src_row * K + k0);
+            v[0] = __uint_as_float(raw.x << 16);
+            v[1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[2] = __uint_as_float(raw.y << 16);
+            v[3] = __uint_as_float(raw.y & 0xffff0000u);
+        } else {
+            float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)src_row * K + k0);
+            v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+        }
+    }
+    const float amax = amax_in ? amax_in[src_row] : amax_const;
+    // exponent field of the row scale, kept where every term's scale and its inverse stay normal
+    const int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+    const int sb = amax > 0.f ? min(max(ef - 7, 4 * TERMS + 1), 250) : 127;
+    if (row_scale && lane == 0 && c == 0) row_scale[p] = __uint_as_float((uint32_t)sb << 23);
+    const int tile = row_tile[p], j = p - tile_row0[tile];
+    const int npad = (tile_rows[tile] + 7) & ~7;
+    uint8_t* blk = act + ((size_t)tile * n_chunks + c) * act_block_bytes(TERMS, tile_tokens, true);
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+        const float inv = __uint_as_float((uint32_t)(254 - (sb - 4 * t)) << 23);
+        const float scale = __uint_as_float((uint32_t)(sb - 4 * t) << 23);
+        __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
+        __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+        const int n = t * npad + j;
+        *reinterpret_cast<uint32_t*>(blk + (size_t)(n >> 3) * 1024 + (n & 7) * 128 + (((lane >> 2) ^ (n & 7)) << 4) +
+                                     ((lane & 3) << 2)) = (uint32_t)lo | ((uint32_t)hi << 16);
+        if (t + 1 < TERMS) {
+            __half2_raw blo = __nv_cvt_fp8x2_to_halfraw2(lo, __NV_E4M3), bhi = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
+            float2 flo = __half22float2(*reinterpret_cast<__half2*>(&blo)), fhi = __half22float2(*reinterpret_cast<__half2*>(&bhi));
+            v[0] -= flo.x * scale; v[1] -= flo.y * scale; v[2] -= fhi.x * scale; v[3] -= fhi.y * scale;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // The GEMM.  Persistent CTAs walk items = (token tile, 128-row weight tile), item index =
 // blockIdx.x + i*gridDim.x, weight tile fastest so that concurrent CTAs share a token tile's
@@ -251,6 +350,8 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
 struct GmmParams {
     const uint8_t* sfa;    // [E][m_tiles][n_chunks][512]
     const uint8_t* act;    // [tile][n_chunks][act_block_bytes]
+    const float* row_scale;  // stacked mode: power-of-two scale of each sorted row's first term, or null:
+    float row_scale_const;   //   then every row uses this one
     const int32_t *tile_expert, *tile_row0, *tile_rows, *n_tiles;
     int m_tiles, n_chunks, rows_total;
     uint32_t a_tx_bytes;   // bytes one 128 x 128 4-bit box reports to its mbarrier
@@ -270,20 +371,22 @@ struct GmmParams {
     int* status;
 };
 
-template <int BN_MAX, int TERMS, bool STACK, int KC>
+template <int BN_MAX, int TERMS, bool STACK, int KC, int NACC = 1>
 struct GmmSmem {
-    static constexpr int kActBytes = STACK ? 1024 + TERMS * BN_MAX * 128 : TERMS * 512 + (BN_MAX / 8) * TERMS * 1024;
+    static constexpr int kActBytes = STACK ? TERMS * BN_MAX * 128 : TERMS * 512 + (BN_MAX / 8) * TERMS * 1024;
     static constexpr int kStage = (KC * (16384 + kActBytes + 512) + 1023) / 1024 * 1024;
-    static constexpr int kSfCols = KC * (STACK ? 8 : 4 * (1 + TERMS));  // TMEM columns of scales per stage
-    static constexpr int kAccCols = STACK ? TERMS * BN_MAX : BN_MAX;    // TMEM columns of one accumulator buffer
+    static constexpr int kSfCols = KC * (STACK ? 4 : 4 * (1 + TERMS));  // TMEM columns of scales per stage
+    static constexpr int kPartCols = STACK ? TERMS * BN_MAX : BN_MAX;   // TMEM columns of one partial accumulator
+    static constexpr int kAccCols = NACC * kPartCols;                   // ... of one accumulator buffer (NACC partials)
+    static constexpr int kSfBase = 2 * kAccCols + (STACK ? 4 : 0);  // stacked: 4 columns of unit scales first
     static constexpr int kTail = 1024;
     static constexpr int kBudget = 225 * 1024;
     static constexpr int kStagesFit = (kBudget - kTail - 1024) / kStage;
-    static constexpr int kStagesTmem = (512 - 2 * kAccCols) / kSfCols;
+    static constexpr int kStagesTmem = (512 - kSfBase) / kSfCols;
     static constexpr int kStages = kStagesFit < kStagesTmem ? kStagesFit : kStagesTmem;
     static constexpr int smem_bytes(int stages) { return stages * kStage + kTail + 1024; }
     static constexpr int tmem_cols(int stages) {
-        int need = 2 * kAccCols + stages * kSfCols, cols = 32;
+        int need = kSfBase + stages * kSfCols, cols = 32;
         while (cols < need) cols *= 2;
         return cols;
     }
@@ -293,15 +396,19 @@ struct GmmSmem {
 
 constexpr long long kWaitLimitCycles = 400000000ll;  // ~0.2 s at 2 GHz
 
-template <int BN_MAX, int TERMS, bool GATE_UP, bool STACK, int KC>
-__global__ void __launch_bounds__(192)
+// NACC = 1: one MMA issuer warp (the configuration in use).  NACC = 2 lets a second warp take
+// alternate stages into its own partial accumulator; it brought no speed-up and is not launched.
+template <int BN_MAX, int TERMS, bool GATE_UP, bool STACK, int KC, int NACC>
+__global__ void __launch_bounds__(224)
 gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA1, const GmmParams p) {
     using namespace sm100;
-    using L = GmmSmem<BN_MAX, TERMS, STACK, KC>;
+    using L = GmmSmem<BN_MAX, TERMS, STACK, KC, NACC>;
+    static_assert(NACC == 1 || STACK, "partial accumulators are a stacked-mode feature");
     constexpr int STAGES_MAX = L::kStages;
     const int STAGES = p.stages;
     constexpr int SF_COLS = L::kSfCols;
-    constexpr int SF_BASE = 2 * L::kAccCols;
+    constexpr int SF_BASE = L::kSfBase;
+    constexpr int SF_UNIT = 2 * L::kAccCols;  // stacked mode: atom of unit activation scales
     constexpr int ACT_OFF = KC * 16384, SFA_OFF = ACT_OFF + KC * L::kActBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -313,19 +420,26 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // two issuer warps need at least two stages per item (each must open its own partial)
+    const int nacc = (NACC == 2 && p.n_chunks > KC) ? 2 : 1;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_full[b], nacc);  // one commit per MMA warp
             mbar_init(&acc_empty[b], 4);
         }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmA1);
+    }
+    uint32_t* unit_atom = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(full) + 512);  // 512 B of E8M0 1.0
+    if (STACK) {
+        if (threadIdx.x < 128) unit_atom[threadIdx.x] = 0x7f7f7f7fu;
+        fence_proxy_async();
     }
     const uint32_t tmem_cols = (uint32_t)p.tmem_cols;
     if (warp == 2) tmem_alloc(tmem_slot, tmem_cols);
@@ -341,11 +455,11 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         // datapath; all lanes poll the barrier, one elected lane arms it and issues the
         // stage's three copies.  Stage index, phase and global addresses are carried
         // incrementally: every extra instruction in this loop costs ~10 cycles per stage.
-        int s = 0, ph = 0;
+        int s = 0, ph = 0, tr = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int tile = item / p.m_tiles, m = item - tile * p.m_tiles;
             const int e = p.tile_expert[tile], rows = p.tile_rows[tile];
-            const uint32_t act_bytes = STACK ? 1024 + TERMS * ((rows + 7) >> 3) * 1024
+            const uint32_t act_bytes = STACK ? TERMS * ((rows + 7) >> 3) * 1024
                                              : TERMS * 512 + ((rows + 7) >> 3) * TERMS * 1024;
             const uint32_t box = (uint32_t)((e * p.m_tiles + m) * p.n_chunks);
             int box_row = (int)(box * 128);
@@ -356,6 +470,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 const bool whole = left >= KC;
                 int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
                 if (!__all_sync(0xffffffffu, ok)) goto done;
+                if (p.trace && blockIdx.x == 0 && lane == 0 && tr < 512) p.trace[(0 * 512 + tr) * 2] = clock64();
                 uint8_t* st = smem + s * L::kStage;
                 if (elect_one()) {
                     if (whole) {
@@ -371,73 +486,101 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     }
                 }
                 __syncwarp();
+                if (p.trace && blockIdx.x == 0 && lane == 0 && tr < 512) p.trace[(0 * 512 + tr) * 2 + 1] = clock64();
+                ++tr;
                 box_row += KC * 128;
                 sfa_src += KC * 512;
                 act_src += KC * act_stride;
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
-    } else if (warp == 1) {
-        // MMA issuer.  Same shape: converged warp, all lanes poll, one elected lane issues.
-        int s = 0, ph = 0, iter = 0;
-        const uint32_t smem_base = smem_u32(smem);
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
-            const int tile = item / p.m_tiles;
-            const int rows = p.tile_rows[tile];
-            const int npad = (rows + 7) & ~7;
-            const uint32_t n_mma = STACK ? (uint32_t)(TERMS * npad) : (uint32_t)max(16, round_up_int(rows, 16));
-            const uint32_t idesc0 = make_idesc_bs(5, 0, n_mma, 0, 0);
-            constexpr uint32_t kIdescStep = (1u << 4) | (1u << 29);  // next scale id for A and B
-            const int b = iter & 1, aph = (iter >> 1) & 1;
-            int ok = mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles);
+        // Tail: the MMA warps release a stage with an asynchronous arrive (tcgen05.commit) that
+        // may land after the accumulator-ready arrive the epilogue waits for.  Wait until every
+        // stage has been released, or a late arrive could hit shared memory that already
+        // belongs to the next CTA on this SM.
+        for (int i = 0; i < STAGES; ++i) {
+            int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 6, kWaitLimitCycles);
             if (!__all_sync(0xffffffffu, ok)) goto done;
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + b * L::kAccCols;
-            uint32_t first = 0;  // becomes non-zero after the item's first MMA
-            for (int left = p.n_chunks; left > 0; left -= KC) {
-                ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+    } else if (warp == 1 || warp == 6) {
+        // MMA issuers.  With NACC = 2, warp 1 takes the even stages and warp 6 the odd ones, so
+        // one of them is already past its barrier wait when the other finishes issuing and the
+        // tensor pipe is not left idle for the ~130-cycle barrier round trip of every stage.
+        // Same shape as the producer: converged warp, all lanes poll, one elected lane issues.
+        const int mw = warp == 6 ? 1 : 0;
+        if (mw < nacc) {
+            int s = 0, ph = 0, iter = 0, tr = 0, it = 0;
+            const uint32_t smem_base = smem_u32(smem);
+            if (STACK && mw == 0) {
+                if (elect_one()) tc_copy_sf(tmem_base + SF_UNIT, make_sf_desc(smem_u32(unit_atom)));
+                __syncwarp();
+            }
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
+                const int tile = item / p.m_tiles;
+                const int rows = p.tile_rows[tile];
+                const int npad = (rows + 7) & ~7;
+                const uint32_t n_mma = STACK ? (uint32_t)(TERMS * npad) : (uint32_t)max(16, round_up_int(rows, 16));
+                const uint32_t idesc0 = make_idesc_bs(5, 0, n_mma, 0, 0);
+                constexpr uint32_t kIdescStep = (1u << 4) | (1u << 29);  // next scale id for A and B
+                const int b = iter & 1, aph = (iter >> 1) & 1;
+                int ok = mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles);
                 if (!__all_sync(0xffffffffu, ok)) goto done;
                 tc_fence_after();
-                const uint32_t st = smem_base + s * L::kStage;
-                const uint32_t sf_stage = tmem_base + SF_BASE + s * SF_COLS;
-                if (elect_one()) {
+                const uint32_t d_tmem = tmem_base + b * L::kAccCols + mw * L::kPartCols;
+                uint32_t first = 0;  // becomes non-zero after this warp's first stage of the item
+                for (int left = p.n_chunks; left > 0; left -= KC, ++it) {
+                    if (nacc == 2 && (it & 1) != mw) {  // the other warp's stage
+                        if (++s == STAGES) { s = 0; ph ^= 1; }
+                        continue;
+                    }
+                    if (p.trace && blockIdx.x == 0 && lane == 0 && mw == 0 && tr < 512) p.trace[(1 * 512 + tr) * 2] = clock64();
+                    ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
+                    if (!__all_sync(0xffffffffu, ok)) goto done;
+                    if (p.trace && blockIdx.x == 0 && lane == 0 && mw == 0 && tr < 512) p.trace[(1 * 512 + tr) * 2 + 1] = clock64();
+                    ++tr;
+                    tc_fence_after();
+                    const uint32_t st = smem_base + s * L::kStage;
+                    const uint32_t sf_stage = tmem_base + SF_BASE + s * SF_COLS;
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < KC; ++k) {
-                        if (k < left) {
-                            const uint32_t sf_tmem = sf_stage + k * (SF_COLS / KC);
-                            const uint32_t act_smem = st + ACT_OFF + k * L::kActBytes;
-                            const uint64_t a_desc = make_sw128_desc(st + k * 16384);
-                            tc_copy_sf(sf_tmem, make_sf_desc(st + SFA_OFF + k * 512));
-                            if (STACK) {
-                                tc_copy_sf(sf_tmem + 4, make_sf_desc(act_smem));
-                                const uint64_t b_desc = make_sw128_desc(act_smem + 1024);
-#pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,
-                                                 sf_tmem + 4, first | (uint32_t)(k | j));
-                            } else {
-#pragma unroll
-                                for (int t = 0; t < TERMS; ++t)
-                                    tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(act_smem + 512 * t));
-#pragma unroll
-                                for (int t = 0; t < TERMS; ++t) {
-                                    const uint64_t b_desc = make_sw128_desc(act_smem + TERMS * 512 + t * 1024, TERMS * 1024);
+                        for (int k = 0; k < KC; ++k) {
+                            if (k < left) {
+                                const uint32_t sf_tmem = sf_stage + k * (SF_COLS / KC);
+                                const uint32_t act_smem = st + ACT_OFF + k * L::kActBytes;
+                                const uint64_t a_desc = make_sw128_desc(st + k * 16384);
+                                tc_copy_sf(sf_tmem, make_sf_desc(st + SFA_OFF + k * 512));
+                                if (STACK) {
+                                    // activation scales are all 1.0 (scale id 0 of the unit atom); only A's id advances
+                                    const uint64_t b_desc = make_sw128_desc(act_smem);
 #pragma unroll
                                     for (int j = 0; j < 4; ++j)
-                                        mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,
-                                                     sf_tmem + 4 * (1 + t), first | (uint32_t)(k | t | j));
+                                        mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * (1u << 29), sf_tmem,
+                                                     tmem_base + SF_UNIT, first | (uint32_t)(k | j));
+                                } else {
+#pragma unroll
+                                    for (int t = 0; t < TERMS; ++t)
+                                        tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(act_smem + 512 * t));
+#pragma unroll
+                                    for (int t = 0; t < TERMS; ++t) {
+                                        const uint64_t b_desc = make_sw128_desc(act_smem + TERMS * 512 + t * 1024, TERMS * 1024);
+#pragma unroll
+                                        for (int j = 0; j < 4; ++j)
+                                            mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,
+                                                         sf_tmem + 4 * (1 + t), first | (uint32_t)(k | t | j));
+                                    }
                                 }
                             }
                         }
+                        tc_commit(&empty[s]);
                     }
-                    tc_commit(&empty[s]);
+                    __syncwarp();
+                    first = 1;
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
+                if (elect_one()) tc_commit(&acc_full[b]);
                 __syncwarp();
-                first = 1;
-                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
-            if (elect_one()) tc_commit(&acc_full[b]);
-            __syncwarp();
         }
     } else {
         const int q = warp & 3;
@@ -460,14 +603,31 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             for (int j8 = 0; j8 < npad; j8 += 8) {
                 float v[8];
                 tmem_ld8(taddr + j8, v);
-                if (STACK) {  // add the columns of the other terms
+                if (STACK) {  // add the other terms' columns (term t carries 16^-t), then the row's scale
+                    float f = 1.f;
 #pragma unroll
-                    for (int t = 1; t < TERMS; ++t) {
+                    if (nacc == 2) {  // the second issuer's partial of term 0
                         float u[8];
-                        tmem_ld8(taddr + t * npad + j8, u);
+                        tmem_ld8(taddr + L::kPartCols + j8, u);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) v[i] += u[i];
                     }
+#pragma unroll
+                    for (int t = 1; t < TERMS; ++t) {
+                        f *= 0.0625f;
+#pragma unroll
+                        for (int a = 0; a < NACC; ++a) {
+                            if (a < nacc) {
+                                float u[8];
+                                tmem_ld8(taddr + a * L::kPartCols + t * npad + j8, u);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) v[i] = fmaf(u[i], f, v[i]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        v[i] *= (j8 + i < rows) ? (p.row_scale ? p.row_scale[row0 + j8 + i] : p.row_scale_const) : 0.f;
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {

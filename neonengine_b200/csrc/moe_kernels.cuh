@@ -234,15 +234,31 @@ router_topk_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
 __global__ void __launch_bounds__(1024)
 router_topk_wide_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
                         const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H, int E,
-                        int k, int32_t* __restrict__ idx, float* __restrict__ w) {
+                        int k, int32_t* __restrict__ idx, float* __restrict__ w, float* __restrict__ tok_amax) {
     extern __shared__ __align__(16) unsigned char rsmem[];
     uint4* xs = reinterpret_cast<uint4*>(rsmem);            // [H/8] bf16 x 8
     float* lg = reinterpret_cast<float*>(rsmem + H * 2);    // [E]
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nvec = H / 8;
     const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)t * H);
-    for (int i = tid; i < nvec; i += 1024) xs[i] = xrow[i];
+    __shared__ unsigned s_amax;
+    if (tid == 0) s_amax = 0u;
     __syncthreads();
+    unsigned amax_bits = 0u;  // largest |x| of the token as bf16 magnitude bits (ordered like the values)
+    for (int i = tid; i < nvec; i += 1024) {
+        uint4 v = xrow[i];
+        xs[i] = v;
+        const uint32_t a[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) amax_bits = max(amax_bits, max(a[j] & 0x7fffu, (a[j] >> 16) & 0x7fffu));
+    }
+    if (tok_amax) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, o));
+        if (lane == 0) atomicMax(&s_amax, amax_bits);
+    }
+    __syncthreads();
+    if (tok_amax && tid == 0) tok_amax[t] = __uint_as_float(s_amax << 16);
     for (int e = warp; e < E; e += 32) {
         const uint4* wrow = reinterpret_cast<const uint4*>(wr + (size_t)e * H);
         float acc = 0.f;

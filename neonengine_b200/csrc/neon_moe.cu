@@ -48,12 +48,16 @@ struct neon_moe_handle {
     // tensor-core path: "tc" weights, tensor maps, activation-term planes, token tiles
     int path = 2;                 // 1 = mma.sync kernels, 2 = TMA + tcgen05 block-scaled GEMM
     uint32_t a_tx_bytes = 8192;   // bytes one 128x128 4-bit box adds to its mbarrier
-    int max_stages = 0, ctas_per_sm = 1, chunks_per_stage = 2;
+    int max_stages = 0, ctas_per_sm = 1, partials = 0;
+    int sync_debug = 0;           // synchronise and check after every kernel (slow; names the failing kernel)
     long long* trace = nullptr;
     uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
+    float *x_scale = nullptr, *a_scale = nullptr;  // per-row activation scales (stacked mode)
+    float *x_amax = nullptr, *a_amax = nullptr;    // largest magnitude per source row / per sorted row
     uint8_t *x_act = nullptr, *a_act = nullptr;  // activation blocks (terms + scales) per (tile, chunk)
     float* a_f32 = nullptr;
     int32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_tiles = nullptr, *row_tile = nullptr;
+    int32_t *tile2_expert = nullptr, *tile2_row0 = nullptr, *tile2_rows = nullptr, *n_tiles2 = nullptr, *row_tile2 = nullptr;
     int tile_cap = 0, kp_h = 0, kp_i = 0;
     CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
     // expert parallelism: source-side routing/dispatch over all experts, exchange buffers
@@ -94,6 +98,16 @@ int fail(neon_moe_handle* h, int code, const char* fmt, ...) {
             return fail(h, NEON_MOE_ECUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
     } while (0)
 
+// With the sync_debug option: wait for the kernel just launched and name it if it failed.
+#define DBG_SYNC(h, st, what)                                                                        \
+    do {                                                                                             \
+        if ((h)->sync_debug) {                                                                       \
+            cudaError_t e_ = cudaStreamSynchronize(st);                                              \
+            if (e_ == cudaSuccess) e_ = cudaGetLastError();                                          \
+            if (e_ != cudaSuccess) return fail(h, NEON_MOE_ECUDA, "%s: %s", what, cudaGetErrorString(e_)); \
+        }                                                                                            \
+    } while (0)
+
 template <typename T>
 int dev_alloc(neon_moe_handle* h, T** p, size_t count) {
     CU(h, cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T) + 16));
@@ -104,8 +118,8 @@ void free_all(neon_moe_handle* h) {
     void* ptrs[] = {h->router_w, h->router_b, h->gu_bias, h->dn_bias, h->gu_wq, h->dn_wq, h->gu_sq, h->dn_sq,
                     h->idx, h->count, h->offset, h->perm, h->inv, h->route_w, h->y, h->a_hi, h->a_lo,
                     h->status, h->st_hidden, h->st_out, h->st_bias, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
-                    h->x_act, h->a_act, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
-                    h->n_tiles, h->row_tile, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
+                    h->x_act, h->a_act, h->x_scale, h->a_scale, h->x_amax, h->a_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
+                    h->n_tiles, h->row_tile, h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
                     h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv};
     for (void* p : ptrs)
         if (p) cudaFree(p);
@@ -246,11 +260,11 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
 // (one MMA per k-block reads the weight tile once); larger batches use 128-token tiles.
 int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 64 ? 32 : 128); }
 
-template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC>
+template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC, int NACC = 1>
 int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap& tm2, GmmParams p, cudaStream_t st) {
-    using L = GmmSmem<BN, TERMS, STACK, KC>;
+    using L = GmmSmem<BN, TERMS, STACK, KC, NACC>;
     static bool configured[kMaxDevicesAttr] = {};
-    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP, STACK, KC>;
+    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP, STACK, KC, NACC>;
     if (!configured[h->cfg.device]) {
         CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::smem_bytes(L::kStages)));
         configured[h->cfg.device] = true;
@@ -266,7 +280,7 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
     if (h->max_stages > 0) stages = std::max(2, std::min(stages, h->max_stages));
     p.stages = stages;
     p.tmem_cols = L::tmem_cols(stages);
-    kern<<<ctas, 192, L::smem_bytes(stages), st>>>(KC == 2 ? tm2 : tm1, tm1, p);
+    kern<<<ctas, 224, L::smem_bytes(stages), st>>>(KC == 2 ? tm2 : tm1, tm1, p);
     h->launches++;
     return NEON_MOE_OK;
 }
@@ -274,27 +288,21 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
 template <int TERMS, bool GATE_UP>
 int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, const CUtensorMap& tm2, const GmmParams& p,
                cudaStream_t st) {
-    const bool two = h->chunks_per_stage == 2;
-    if (tile_tokens == 16)
-        return two ? launch_gmm_one<16, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st)
-                   : launch_gmm_one<16, TERMS, GATE_UP, true, 1>(h, tm1, tm2, p, st);
-    if (tile_tokens == 32)
-        return two ? launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st)
-                   : launch_gmm_one<32, TERMS, GATE_UP, true, 1>(h, tm1, tm2, p, st);
-    return launch_gmm_one<128, TERMS, GATE_UP, false, 1>(h, tm1, tm2, p, st);
+    if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP, true, 2, 1>(h, tm1, tm2, p, st);
+    if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2, 1>(h, tm1, tm2, p, st);
+    return launch_gmm_one<128, TERMS, GATE_UP, false, 1, 1>(h, tm1, tm2, p, st);
 }
 
 template <int TERMS, bool FROM_BF16>
-void launch_split(neon_moe_handle* h, int tile_tokens, const void* src, int K, int n, int top_k, uint8_t* act,
-                  cudaStream_t st) {
+void launch_split(neon_moe_handle* h, int tile_tokens, const TileList& tl, const void* src, int K, int n, int top_k,
+                  const float* amax, float amax_const, uint8_t* act, float* row_scale, cudaStream_t st) {
     const int n_chunks = round_up_int(K, kChunkK) / kChunkK;
-    const dim3 grid((n * n_chunks + 7) / 8);
     if (tile_tokens <= 32)
-        split_rows_kernel<TERMS, FROM_BF16, true><<<grid, 256, 0, st>>>(src, h->perm, top_k, K, n, h->row_tile,
-                                                                        h->tile_row0, h->tile_rows, tile_tokens, act);
+        split_rows_stacked_kernel<TERMS, FROM_BF16><<<(n * n_chunks + 7) / 8, 256, 0, st>>>(
+            src, h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
     else
-        split_rows_kernel<TERMS, FROM_BF16, false><<<grid, 256, 0, st>>>(src, h->perm, top_k, K, n, h->row_tile,
-                                                                         h->tile_row0, h->tile_rows, tile_tokens, act);
+        split_rows_kernel<TERMS, FROM_BF16, false><<<(n * n_chunks + 7) / 8, 256, 0, st>>>(
+            src, h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, act);
     h->launches++;
 }
 
@@ -330,6 +338,8 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
     if (cfg->ep_size <= 0 || cfg->ep_rank < 0 || cfg->ep_rank >= cfg->ep_size || cfg->n_experts % cfg->ep_size)
         return fail(nullptr, NEON_MOE_EINVAL, "bad expert-parallel rank/size");
     if (cfg->max_tokens <= 0) return fail(nullptr, NEON_MOE_EINVAL, "max_tokens must be positive");
+    if (!(cfg->swiglu_limit > 0.f) || !(cfg->swiglu_limit < 1e15f))
+        return fail(nullptr, NEON_MOE_EINVAL, "swiglu_limit must be positive and finite");
     int ndev = 0;
     cudaError_t ce = cudaGetDeviceCount(&ndev);
     if (ce != cudaSuccess || ndev == 0)
@@ -380,9 +390,14 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         a_bytes = std::max(a_bytes, tiles * nch_i * act_block_bytes(4, tt, tt <= 32));
     }
     if ((rc = dev_alloc(h, &h->x_act, x_bytes)) || (rc = dev_alloc(h, &h->a_act, a_bytes)) ||
+        (rc = dev_alloc(h, &h->x_scale, n)) || (rc = dev_alloc(h, &h->a_scale, n)) ||
+        (rc = dev_alloc(h, &h->x_amax, n)) || (rc = dev_alloc(h, &h->a_amax, n)) ||
         (rc = dev_alloc(h, &h->a_f32, n * cfg->inter)) || (rc = dev_alloc(h, &h->tile_expert, (size_t)h->tile_cap)) ||
         (rc = dev_alloc(h, &h->tile_row0, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile_rows, (size_t)h->tile_cap)) ||
-        (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
+        (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)) ||
+        (rc = dev_alloc(h, &h->tile2_expert, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile2_row0, (size_t)h->tile_cap)) ||
+        (rc = dev_alloc(h, &h->tile2_rows, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->n_tiles2, (size_t)4)) ||
+        (rc = dev_alloc(h, &h->row_tile2, n)))
         return bail(rc);
     if (cfg->ep_size > 1) {
         const size_t ns = (size_t)h->n_src, E = (size_t)cfg->n_experts, Hh = (size_t)cfg->hidden;
@@ -445,35 +460,57 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
 // (rows = tokens, k_eff = top_k) and by the expert-parallel local pass (rows = received
 // rows, k_eff = 1, route_w = 1).
 static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_eff, const int32_t* idx, int e_lo,
-                        const float* route_w, float* out, cudaStream_t st, bool prof) {
+                        const float* route_w, const float* hidden_amax, float* out, cudaStream_t st, bool prof) {
     const int H = h->cfg.hidden, I = h->cfg.inter, EL = h->n_local;
     const int n = rows * k_eff;
     DispatchArrays d{h->count, h->offset, h->perm, h->inv};
     if (h->path == 2) {
-        const int tt = tile_tokens_for(rows);
+        const int tt = tile_tokens_for(rows), tt2 = 0, tt_dn = tt;  // one tile list serves both products
         TileList tl{h->tile_expert, h->tile_row0, h->tile_rows, h->n_tiles, h->row_tile};
-        dispatch_tiles_kernel<<<1, 1024, (size_t)(33 * EL) * sizeof(int), st>>>(idx, n, e_lo, EL, d, tt, tl);
+        TileList tl2{h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2};
+        const TileList& tld = tt2 ? tl2 : tl;
+        const bool stacked = tt <= 32;
+        dispatch_tiles_kernel<<<1, 1024, (size_t)(33 * EL) * sizeof(int), st>>>(
+            idx, n, e_lo, EL, d, tt, tl, tt2, tl2, nullptr);
         h->launches++;
+        DBG_SYNC(h, st, "dispatch_tiles_kernel");
         const int nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
-        launch_split<2, true>(h, tt, hidden, H, n, k_eff, h->x_act, st);
+        if (stacked && !hidden_amax) {  // no producer kernel measured the rows: do it here
+            row_amax_kernel<true><<<(rows + 7) / 8, 256, 0, st>>>(hidden, H, rows, h->x_amax);
+            h->launches++;
+            hidden_amax = h->x_amax;
+        }
+        launch_split<2, true>(h, tt, tl, hidden, H, n, k_eff, hidden_amax, 0.f, h->x_act, h->x_scale, st);
+        DBG_SYNC(h, st, "split_rows (hidden)");
         GmmParams g{};
-        g.tile_expert = h->tile_expert; g.tile_row0 = h->tile_row0; g.tile_rows = h->tile_rows; g.n_tiles = h->n_tiles;
         g.a_tx_bytes = h->a_tx_bytes; g.trace = h->trace;
         g.a_out = h->a_f32; g.inter = I; g.limit = h->cfg.swiglu_limit; g.alpha = h->cfg.swiglu_alpha;
         g.perm = h->perm; g.route_w = route_w; g.y = h->y; g.hidden = H; g.status = h->status;
         // gate_up: rows 2I, K = H
-        g.sfa = h->gu_sfa; g.act = h->x_act; g.bias = h->gu_bias;
+        g.tile_expert = tl.expert; g.tile_row0 = tl.row0; g.tile_rows = tl.rows; g.n_tiles = tl.n_tiles;
+        g.sfa = h->gu_sfa; g.act = h->x_act; g.row_scale = h->x_scale; g.bias = h->gu_bias;
         g.m_tiles = 2 * I / 128; g.n_chunks = nch_h; g.rows_total = 2 * I;
         mark(h, st, prof);
         int rc = launch_gmm<2, true>(h, tt, h->tm_gu, h->tm_gu2, g, st);
         if (rc) return rc;
+        DBG_SYNC(h, st, "gmm_bs_kernel gate_up");
         mark(h, st, prof);
-        launch_split<4, false>(h, tt, h->a_f32, I, n, k_eff, h->a_act, st);
+        // |SwiGLU| <= limit * (limit + 1): a fixed bound replaces the row maximum
+        const float a_bound = h->cfg.swiglu_limit * (h->cfg.swiglu_limit + 1.f);
+        launch_split<4, false>(h, tt_dn, tld, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
+        DBG_SYNC(h, st, "split_rows (activation)");
         // down: rows H, K = I
-        g.sfa = h->dn_sfa; g.act = h->a_act; g.bias = h->dn_bias;
+        g.tile_expert = tld.expert; g.tile_row0 = tld.row0; g.tile_rows = tld.rows; g.n_tiles = tld.n_tiles;
+        g.sfa = h->dn_sfa; g.act = h->a_act; g.row_scale = nullptr; g.bias = h->dn_bias;
+        {   // the scale split_rows derives from the bound: 2^(floor(log2 bound) - 7), same clamps
+            uint32_t bits; memcpy(&bits, &a_bound, 4);
+            int sb = std::min(std::max((int)((bits >> 23) & 0xffu) - 7, 4 * 4 + 1), 250);
+            bits = (uint32_t)sb << 23; memcpy(&g.row_scale_const, &bits, 4);
+        }
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
-        rc = launch_gmm<4, false>(h, tt, h->tm_dn, h->tm_dn2, g, st);
+        rc = launch_gmm<4, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st);
         if (rc) return rc;
+        DBG_SYNC(h, st, "gmm_bs_kernel down");
         mark(h, st, prof);
     } else {
         dispatch_kernel<<<1, 1024, (size_t)(33 * EL) * sizeof(int), st>>>(idx, n, e_lo, EL, d);
@@ -509,11 +546,11 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
 }
 
 static void launch_router(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, int32_t* idx, float* w,
-                          cudaStream_t st) {
+                          float* tok_amax, cudaStream_t st) {
     const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k;
     if (h->path == 2)
         router_topk_wide_kernel<<<T, 1024, H * 2 + E * sizeof(float), st>>>(
-            static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, idx, w);
+            static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, idx, w, tok_amax);
     else
         router_topk_kernel<256><<<T, 256, (H + E) * sizeof(float), st>>>(
             static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, idx, w);
@@ -533,8 +570,8 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float*
     const int k = h->cfg.top_k, n = T * k;
     const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
     mark(h, st, prof);
-    launch_router(h, hidden, T, logit_bias, h->idx, h->route_w, st);
-    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, out, st, prof);
+    launch_router(h, hidden, T, logit_bias, h->idx, h->route_w, h->x_amax, st);
+    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, h->path == 2 ? h->x_amax : nullptr, out, st, prof);
     if (rc) return rc;
     if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
     if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
@@ -597,7 +634,7 @@ int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const flo
     // 1. route own tokens, sort entries by global expert (= by destination rank, then expert), pack rows
     CU(h, cudaEventRecord(h->ep_ev[0], st));
     DispatchArrays sd{h->s_count, h->s_offset, h->s_perm, h->s_inv};
-    if (T > 0) launch_router(h, hidden, T, logit_bias, h->s_idx, h->s_w, st);
+    if (T > 0) launch_router(h, hidden, T, logit_bias, h->s_idx, h->s_w, nullptr, st);
     dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->s_idx, n, 0, E, sd);
     h->launches++;
     if (n > 0) {
@@ -627,7 +664,7 @@ int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const flo
     CU(h, cudaEventRecord(h->ep_ev[2], st));
     // 4. local experts on the received rows (one slot per row, unit weight); yback is in receive order
     if (R > 0) {
-        int rc = experts_core(h, h->xrecv, R, 1, h->row_expert, 0, h->ones, h->yback, st, false);
+        int rc = experts_core(h, h->xrecv, R, 1, h->row_expert, 0, h->ones, nullptr, h->yback, st, false);
         if (rc) return rc;
     }
     CU(h, cudaEventRecord(h->ep_ev[3], st));
@@ -719,9 +756,10 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->ctas_per_sm = (int)value;
     } else if (!strcmp(name, "n_ctas")) {
         h->n_sms = (int)value;
-    } else if (!strcmp(name, "chunks_per_stage")) {
-        if (value != 1 && value != 2) return fail(h, NEON_MOE_EINVAL, "chunks_per_stage must be 1 or 2");
-        h->chunks_per_stage = (int)value;
+    } else if (!strcmp(name, "sync_debug")) {
+        h->sync_debug = (int)value;
+    } else if (!strcmp(name, "partials")) {
+        h->partials = (int)value;
     } else if (!strcmp(name, "max_stages")) {
         h->max_stages = (int)value;
     } else {

@@ -45,11 +45,26 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe of the phase (no suspend): the cheap first look before falling back to
+// try_wait, which may park the thread.
+__device__ __forceinline__ bool mbar_peek(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Gives up after `limit_cycles` SM clocks or when another thread of the CTA
 // has raised *abort_flag; on a timeout it records `code` in *status and raises the flag.
 // Returns true when the barrier phase completed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code, long long limit_cycles) {
+    if (mbar_peek(bar, parity)) return true;
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {

@@ -165,8 +165,12 @@ int neon_moe_read_dispatch(neon_moe_handle* h, int32_t* count, int32_t* offset, 
 int neon_moe_status(neon_moe_handle* h, int* device_status_word);
 
 /* Tuning / test switches.  "path": 2 (default on sm_100) = TMA + tcgen05 block-scaled
- * grouped GEMM, 1 = the mma.sync kernels.  "a_tx_bytes": bytes a 128x128 4-bit TMA box
- * reports to its mbarrier (default 8192).
+ * grouped GEMM, 1 = the mma.sync kernels.  "use_graphs" (default 1): passes of up to 64
+ * tokens are captured into a CUDA graph the second time the same arguments are seen and
+ * replayed afterwards (the analogue of the engine re-submitting a recorded command buffer).
+ * "sync_debug": synchronise after every kernel and name the one that failed.
+ * "a_tx_bytes": bytes a 128x128 4-bit TMA box reports to its mbarrier (default 8192).
+ * Others ("n_ctas", "ctas_per_sm", "max_stages", "trace_ptr") are measurement aids.
  * Follows: the literal knobs the engine's apps set before running a system,
  * NeonEngine/src/raytracing_app.cpp:605-631. */
 int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value);

@@ -70,6 +70,14 @@ struct neon_moe_handle {
     cudaEvent_t ep_ev[6] = {};
     bool ep_timed = false;
     int ep_last_recv = 0;
+    // replay cache: a forward with the same arguments is captured once into a CUDA graph
+    struct CachedGraph {
+        const void *hidden, *bias, *out, *idx, *w;
+        int T, seen, launches;
+        cudaGraphExec_t exec;
+    };
+    std::vector<CachedGraph> graphs;
+    int use_graphs = 1;
     // per-stage profiling: 5 events per forward
     bool profiling = false;
     std::vector<cudaEvent_t> events;
@@ -80,6 +88,12 @@ struct neon_moe_handle {
 };
 
 namespace {
+
+void drop_graphs(neon_moe_handle* h) {
+    for (auto& g : h->graphs)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    h->graphs.clear();
+}
 
 int fail(neon_moe_handle* h, int code, const char* fmt, ...) {
     char buf[512];
@@ -127,6 +141,8 @@ void free_all(neon_moe_handle* h) {
     for (cudaEvent_t ev : h->ep_ev)
         if (ev) cudaEventDestroy(ev);
     if (h->comm && nccl_api().ok) nccl_api().CommDestroy(h->comm);
+    for (auto& g : h->graphs)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);
     for (cudaEvent_t ev : h->events) cudaEventDestroy(ev);
 }
@@ -440,6 +456,7 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
     CU(h, cudaDeviceSynchronize());
     const int H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts, EL = h->n_local;
     h->has_weights = false;
+    drop_graphs(h);
     int rc;
     if ((rc = copy_in(h, &h->router_w, router_w, (size_t)E * H, on_device))) return rc;
     if ((rc = copy_in(h, &h->router_b, router_b, (size_t)E, on_device))) return rc;
@@ -557,16 +574,75 @@ static void launch_router(neon_moe_handle* h, const void* hidden, int T, const f
     h->launches++;
 }
 
+static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
+                         int32_t* topk_idx, float* topk_w, cudaStream_t st);
+
 int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
                      int32_t* topk_idx, float* topk_w, void* cuda_stream) {
     if (!h) return NEON_MOE_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    // Small passes are launch-bound: the second time the same arguments come in, the launch
+    // sequence is captured into a CUDA graph (on the handle's own stream) and replayed from then
+    // on.  Not while profiling or debugging, and not inside a caller's own stream capture.
+    const bool cacheable = h->use_graphs && h->has_weights && h->cfg.ep_size == 1 && T > 0 && T <= 64 && hidden && out &&
+                           !h->profiling && !h->sync_debug && !h->trace;
+    if (!cacheable) return forward_eager(h, hidden, T, logit_bias, out, topk_idx, topk_w, st);
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return forward_eager(h, hidden, T, logit_bias, out, topk_idx, topk_w, st);
+    }
+    neon_moe_handle::CachedGraph* hit = nullptr;
+    for (auto& g : h->graphs)
+        if (g.hidden == hidden && g.T == T && g.bias == logit_bias && g.out == out && g.idx == topk_idx && g.w == topk_w) {
+            hit = &g;
+            break;
+        }
+    if (!hit) {
+        if (h->graphs.size() >= 64) drop_graphs(h);
+        h->graphs.push_back({hidden, logit_bias, out, topk_idx, topk_w, T, 0, 0, nullptr});
+        hit = &h->graphs.back();
+    }
+    if (!hit->exec) {
+        if (hit->seen++ == 0) return forward_eager(h, hidden, T, logit_bias, out, topk_idx, topk_w, st);
+        CU(h, cudaSetDevice(h->cfg.device));
+        const int64_t before = h->launches;
+        CU(h, cudaStreamBeginCapture(h->own_stream, cudaStreamCaptureModeThreadLocal));
+        int rc = forward_eager(h, hidden, T, logit_bias, out, topk_idx, topk_w, h->own_stream);
+        cudaGraph_t graph = nullptr;
+        cudaError_t ce = cudaStreamEndCapture(h->own_stream, &graph);
+        hit->launches = (int)(h->launches - before);
+        h->launches = before;
+        if (rc || ce != cudaSuccess || !graph) {
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            h->use_graphs = 0;  // capture is not available here: stay eager
+            return forward_eager(h, hidden, T, logit_bias, out, topk_idx, topk_w, st);
+        }
+        ce = cudaGraphInstantiate(&hit->exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ce != cudaSuccess) {
+            hit->exec = nullptr;
+            h->use_graphs = 0;
+            return forward_eager(h, hidden, T, logit_bias, out, topk_idx, topk_w, st);
+        }
+    }
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaGraphLaunch(hit->exec, st));
+    h->launches += hit->launches;
+    h->last_stream = st;
+    h->last_n = T * h->cfg.top_k;
+    return NEON_MOE_OK;
+}
+
+static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
+                         int32_t* topk_idx, float* topk_w, cudaStream_t st) {
     if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "forward before set_weights");
     if (h->cfg.ep_size != 1) return fail(h, NEON_MOE_ESTATE, "forward needs ep_size == 1; use neon_moe_forward_ep");
     if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
     if (T == 0) { h->last_n = 0; return NEON_MOE_OK; }
     if (!hidden || !out) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
     CU(h, cudaSetDevice(h->cfg.device));
-    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     const int k = h->cfg.top_k, n = T * k;
     const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
     mark(h, st, prof);
@@ -745,6 +821,7 @@ int neon_moe_read_dispatch(neon_moe_handle* h, int32_t* count, int32_t* offset, 
 
 int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     if (!h || !name) return NEON_MOE_EINVAL;
+    drop_graphs(h);
     if (!strcmp(name, "path")) {
         if (value != 1 && value != 2) return fail(h, NEON_MOE_EINVAL, "path must be 1 (mma.sync) or 2 (tcgen05)");
         h->path = (int)value;
@@ -756,6 +833,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->ctas_per_sm = (int)value;
     } else if (!strcmp(name, "n_ctas")) {
         h->n_sms = (int)value;
+    } else if (!strcmp(name, "use_graphs")) {
+        h->use_graphs = (int)value;
     } else if (!strcmp(name, "sync_debug")) {
         h->sync_debug = (int)value;
     } else if (!strcmp(name, "partials")) {

@@ -371,13 +371,12 @@ struct GmmParams {
     int* status;
 };
 
-template <int BN_MAX, int TERMS, bool STACK, int KC, int NACC = 1>
+template <int BN_MAX, int TERMS, bool STACK, int KC>
 struct GmmSmem {
     static constexpr int kActBytes = STACK ? TERMS * BN_MAX * 128 : TERMS * 512 + (BN_MAX / 8) * TERMS * 1024;
     static constexpr int kStage = (KC * (16384 + kActBytes + 512) + 1023) / 1024 * 1024;
     static constexpr int kSfCols = KC * (STACK ? 4 : 4 * (1 + TERMS));  // TMEM columns of scales per stage
-    static constexpr int kPartCols = STACK ? TERMS * BN_MAX : BN_MAX;   // TMEM columns of one partial accumulator
-    static constexpr int kAccCols = NACC * kPartCols;                   // ... of one accumulator buffer (NACC partials)
+    static constexpr int kAccCols = STACK ? TERMS * BN_MAX : BN_MAX;    // TMEM columns of one accumulator buffer
     static constexpr int kSfBase = 2 * kAccCols + (STACK ? 4 : 0);  // stacked: 4 columns of unit scales first
     static constexpr int kTail = 1024;
     static constexpr int kBudget = 225 * 1024;
@@ -396,14 +395,11 @@ struct GmmSmem {
 
 constexpr long long kWaitLimitCycles = 400000000ll;  // ~0.2 s at 2 GHz
 
-// NACC = 1: one MMA issuer warp (the configuration in use).  NACC = 2 lets a second warp take
-// alternate stages into its own partial accumulator; it brought no speed-up and is not launched.
-template <int BN_MAX, int TERMS, bool GATE_UP, bool STACK, int KC, int NACC>
-__global__ void __launch_bounds__(224)
+template <int BN_MAX, int TERMS, bool GATE_UP, bool STACK, int KC>
+__global__ void __launch_bounds__(192)
 gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA1, const GmmParams p) {
     using namespace sm100;
-    using L = GmmSmem<BN_MAX, TERMS, STACK, KC, NACC>;
-    static_assert(NACC == 1 || STACK, "partial accumulators are a stacked-mode feature");
+    using L = GmmSmem<BN_MAX, TERMS, STACK, KC>;
     constexpr int STAGES_MAX = L::kStages;
     const int STAGES = p.stages;
     constexpr int SF_COLS = L::kSfCols;
@@ -420,15 +416,13 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // two issuer warps need at least two stages per item (each must open its own partial)
-    const int nacc = (NACC == 2 && p.n_chunks > KC) ? 2 : 1;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&acc_full[b], nacc);  // one commit per MMA warp
+            mbar_init(&acc_full[b], 1);
             mbar_init(&acc_empty[b], 4);
         }
         *abort_flag = 0;
@@ -503,16 +497,14 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             if (!__all_sync(0xffffffffu, ok)) goto done;
             if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-    } else if (warp == 1 || warp == 6) {
-        // MMA issuers.  With NACC = 2, warp 1 takes the even stages and warp 6 the odd ones, so
-        // one of them is already past its barrier wait when the other finishes issuing and the
-        // tensor pipe is not left idle for the ~130-cycle barrier round trip of every stage.
-        // Same shape as the producer: converged warp, all lanes poll, one elected lane issues.
-        const int mw = warp == 6 ? 1 : 0;
-        if (mw < nacc) {
-            int s = 0, ph = 0, iter = 0, tr = 0, it = 0;
+    } else if (warp == 1) {
+        // MMA issuer.  Same shape as the producer: converged warp, all lanes poll, one elected
+        // lane issues the tcgen05 instructions.
+        {
+            int s = 0, ph = 0, iter = 0;
+            bool ready = false;  // the current stage's barrier was already seen complete
             const uint32_t smem_base = smem_u32(smem);
-            if (STACK && mw == 0) {
+            if (STACK) {
                 if (elect_one()) tc_copy_sf(tmem_base + SF_UNIT, make_sf_desc(smem_u32(unit_atom)));
                 __syncwarp();
             }
@@ -527,51 +519,53 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 int ok = mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles);
                 if (!__all_sync(0xffffffffu, ok)) goto done;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + b * L::kAccCols + mw * L::kPartCols;
-                uint32_t first = 0;  // becomes non-zero after this warp's first stage of the item
-                for (int left = p.n_chunks; left > 0; left -= KC, ++it) {
-                    if (nacc == 2 && (it & 1) != mw) {  // the other warp's stage
-                        if (++s == STAGES) { s = 0; ph ^= 1; }
-                        continue;
+                const uint32_t d_tmem = tmem_base + b * L::kAccCols;
+                uint32_t first = 0;  // becomes non-zero after the item's first stage
+                for (int left = p.n_chunks; left > 0; left -= KC) {
+                    if (!ready) {
+                        ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
+                        if (!__all_sync(0xffffffffu, ok)) goto done;
                     }
-                    if (p.trace && blockIdx.x == 0 && lane == 0 && mw == 0 && tr < 512) p.trace[(1 * 512 + tr) * 2] = clock64();
-                    ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
-                    if (!__all_sync(0xffffffffu, ok)) goto done;
-                    if (p.trace && blockIdx.x == 0 && lane == 0 && mw == 0 && tr < 512) p.trace[(1 * 512 + tr) * 2 + 1] = clock64();
-                    ++tr;
                     tc_fence_after();
                     const uint32_t st = smem_base + s * L::kStage;
                     const uint32_t sf_stage = tmem_base + SF_BASE + s * SF_COLS;
-                    if (elect_one()) {
+                    // issues the copy of chunk k's weight scales and its MMAs (elected lane only)
+                    auto issue_chunk = [&](int k) {
+                        const uint32_t sf_tmem = sf_stage + k * (SF_COLS / KC);
+                        const uint32_t act_smem = st + ACT_OFF + k * L::kActBytes;
+                        const uint64_t a_desc = make_sw128_desc(st + k * 16384);
+                        tc_copy_sf(sf_tmem, make_sf_desc(st + SFA_OFF + k * 512));
+                        if (STACK) {
+                            // activation scales are all 1.0 (scale id 0 of the unit atom); only A's id advances
+                            const uint64_t b_desc = make_sw128_desc(act_smem);
 #pragma unroll
-                        for (int k = 0; k < KC; ++k) {
-                            if (k < left) {
-                                const uint32_t sf_tmem = sf_stage + k * (SF_COLS / KC);
-                                const uint32_t act_smem = st + ACT_OFF + k * L::kActBytes;
-                                const uint64_t a_desc = make_sw128_desc(st + k * 16384);
-                                tc_copy_sf(sf_tmem, make_sf_desc(st + SFA_OFF + k * 512));
-                                if (STACK) {
-                                    // activation scales are all 1.0 (scale id 0 of the unit atom); only A's id advances
-                                    const uint64_t b_desc = make_sw128_desc(act_smem);
+                            for (int j = 0; j < 4; ++j)
+                                mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * (1u << 29), sf_tmem,
+                                             tmem_base + SF_UNIT, first | (uint32_t)(k | j));
+                        } else {
 #pragma unroll
-                                    for (int j = 0; j < 4; ++j)
-                                        mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * (1u << 29), sf_tmem,
-                                                     tmem_base + SF_UNIT, first | (uint32_t)(k | j));
-                                } else {
+                            for (int t = 0; t < TERMS; ++t) tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(act_smem + 512 * t));
 #pragma unroll
-                                    for (int t = 0; t < TERMS; ++t)
-                                        tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(act_smem + 512 * t));
+                            for (int t = 0; t < TERMS; ++t) {
+                                const uint64_t b_desc = make_sw128_desc(act_smem + TERMS * 512 + t * 1024, TERMS * 1024);
 #pragma unroll
-                                    for (int t = 0; t < TERMS; ++t) {
-                                        const uint64_t b_desc = make_sw128_desc(act_smem + TERMS * 512 + t * 1024, TERMS * 1024);
-#pragma unroll
-                                        for (int j = 0; j < 4; ++j)
-                                            mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,
-                                                         sf_tmem + 4 * (1 + t), first | (uint32_t)(k | t | j));
-                                    }
-                                }
+                                for (int j = 0; j < 4; ++j)
+                                    mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,
+                                                 sf_tmem + 4 * (1 + t), first | (uint32_t)(k | t | j));
                             }
                         }
+                    };
+                    if (elect_one()) issue_chunk(0);
+                    __syncwarp();
+                    // While those MMAs run, look whether the next stage has landed: the barrier
+                    // round trip then overlaps tensor-pipe work instead of leaving the pipe idle.
+                    {
+                        const int sn = (s + 1 == STAGES) ? 0 : s + 1;
+                        const int phn = (s + 1 == STAGES) ? ph ^ 1 : ph;
+                        ready = __all_sync(0xffffffffu, (int)mbar_peek(&full[sn], phn));
+                    }
+                    if (elect_one()) {
+                        if (KC == 2 && left > 1) issue_chunk(1);
                         tc_commit(&empty[s]);
                     }
                     __syncwarp();
@@ -606,24 +600,13 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 if (STACK) {  // add the other terms' columns (term t carries 16^-t), then the row's scale
                     float f = 1.f;
 #pragma unroll
-                    if (nacc == 2) {  // the second issuer's partial of term 0
-                        float u[8];
-                        tmem_ld8(taddr + L::kPartCols + j8, u);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) v[i] += u[i];
-                    }
 #pragma unroll
                     for (int t = 1; t < TERMS; ++t) {
                         f *= 0.0625f;
+                        float u[8];
+                        tmem_ld8(taddr + t * npad + j8, u);
 #pragma unroll
-                        for (int a = 0; a < NACC; ++a) {
-                            if (a < nacc) {
-                                float u[8];
-                                tmem_ld8(taddr + a * L::kPartCols + t * npad + j8, u);
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) v[i] = fmaf(u[i], f, v[i]);
-                            }
-                        }
+                        for (int i = 0; i < 8; ++i) v[i] = fmaf(u[i], f, v[i]);
                     }
 #pragma unroll
                     for (int i = 0; i < 8; ++i)

@@ -48,7 +48,7 @@ struct neon_moe_handle {
     // tensor-core path: "tc" weights, tensor maps, activation-term planes, token tiles
     int path = 2;                 // 1 = mma.sync kernels, 2 = TMA + tcgen05 block-scaled GEMM
     uint32_t a_tx_bytes = 8192;   // bytes one 128x128 4-bit box adds to its mbarrier
-    int max_stages = 0, ctas_per_sm = 1, partials = 0;
+    int max_stages = 0, ctas_per_sm = 1;
     int sync_debug = 0;           // synchronise and check after every kernel (slow; names the failing kernel)
     long long* trace = nullptr;
     uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
@@ -276,11 +276,11 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
 // (one MMA per k-block reads the weight tile once); larger batches use 128-token tiles.
 int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 64 ? 32 : 128); }
 
-template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC, int NACC = 1>
+template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC>
 int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap& tm2, GmmParams p, cudaStream_t st) {
-    using L = GmmSmem<BN, TERMS, STACK, KC, NACC>;
+    using L = GmmSmem<BN, TERMS, STACK, KC>;
     static bool configured[kMaxDevicesAttr] = {};
-    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP, STACK, KC, NACC>;
+    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP, STACK, KC>;
     if (!configured[h->cfg.device]) {
         CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::smem_bytes(L::kStages)));
         configured[h->cfg.device] = true;
@@ -296,7 +296,7 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
     if (h->max_stages > 0) stages = std::max(2, std::min(stages, h->max_stages));
     p.stages = stages;
     p.tmem_cols = L::tmem_cols(stages);
-    kern<<<ctas, 224, L::smem_bytes(stages), st>>>(KC == 2 ? tm2 : tm1, tm1, p);
+    kern<<<ctas, 192, L::smem_bytes(stages), st>>>(KC == 2 ? tm2 : tm1, tm1, p);
     h->launches++;
     return NEON_MOE_OK;
 }
@@ -304,9 +304,9 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
 template <int TERMS, bool GATE_UP>
 int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, const CUtensorMap& tm2, const GmmParams& p,
                cudaStream_t st) {
-    if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP, true, 2, 1>(h, tm1, tm2, p, st);
-    if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2, 1>(h, tm1, tm2, p, st);
-    return launch_gmm_one<128, TERMS, GATE_UP, false, 1, 1>(h, tm1, tm2, p, st);
+    if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
+    if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
+    return launch_gmm_one<128, TERMS, GATE_UP, false, 1>(h, tm1, tm2, p, st);
 }
 
 template <int TERMS, bool FROM_BF16>
@@ -837,8 +837,6 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->use_graphs = (int)value;
     } else if (!strcmp(name, "sync_debug")) {
         h->sync_debug = (int)value;
-    } else if (!strcmp(name, "partials")) {
-        h->partials = (int)value;
     } else if (!strcmp(name, "max_stages")) {
         h->max_stages = (int)value;
     } else {

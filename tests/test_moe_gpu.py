@@ -86,8 +86,18 @@ def test_config0_decode_single_token(full20b):
         check_against_oracle(layer, W, hidden, what=f"config0 stream {stream}")
 
 
-def test_config1_batched_decode_zipf(full20b):
+@pytest.mark.parametrize("path", [2, 1])
+def test_config1_batched_decode_zipf(full20b, path):
+    """Both kernel generations: 2 = TMA + tcgen05 block-scaled GEMM (default), 1 = mma.sync."""
     shape, W, layer = full20b
+    layer.set_option("path", path)
+    try:
+        _config1(shape, W, layer)
+    finally:
+        layer.set_option("path", 2)
+
+
+def _config1(shape, W, layer):
     lb = synth.zipf_logit_bias(shape.n_experts)
     hidden = synth.make_hidden(64, W, 0, logit_bias=lb)
     out, err = check_against_oracle(layer, W, hidden, logit_bias=lb, what="config1")
@@ -157,3 +167,56 @@ def test_scale_out_of_range_is_rejected():
     bad.gate_up_scales[0, 0, 0] = 200
     with pytest.raises(RuntimeError, match="scale"):
         make_layer(shape, bad, 4)
+
+
+def test_graph_replay_matches_eager(full20b):
+    """The third call with the same device buffers replays a captured CUDA graph; it must give
+    the same bits as the eager launch sequence, also after the input buffer's contents change."""
+    torch = torch_cuda()
+    shape, W, layer = full20b
+    lb = synth.zipf_logit_bias(shape.n_experts)
+    d_lb = torch.from_numpy(lb).cuda()
+    h = torch.empty((24, shape.hidden), dtype=torch.int16, device="cuda")
+    out = torch.empty((24, shape.hidden), dtype=torch.float32, device="cuda")
+    results = []
+    for stream in (0, 0, 0, 1, 1):
+        hidden = synth.make_hidden(24, W, 9, logit_bias=lb, stream=stream)
+        h.copy_(torch.from_numpy(hidden.view(np.int16)))
+        layer.run(h, logit_bias=d_lb, out=out)
+        torch.cuda.synchronize()
+        results.append(out.cpu().numpy().copy())
+    layer.set_option("use_graphs", 0)
+    layer.run(h, logit_bias=d_lb, out=out)
+    torch.cuda.synchronize()
+    eager = out.cpu().numpy()
+    layer.set_option("use_graphs", 1)
+    np.testing.assert_array_equal(results[0], results[1])
+    np.testing.assert_array_equal(results[1], results[2])
+    np.testing.assert_array_equal(results[3], results[4])
+    np.testing.assert_array_equal(results[4], eager)
+    assert not np.array_equal(results[2], results[3])
+
+
+def test_config2_prefill_full_size(full20b):
+    """T=4096, uniform routing (the prefill configuration): routing exact for every token,
+    oracle on a token sample, finite outputs, counts add up."""
+    shape, W, _ = full20b
+    layer = make_layer(shape, W, max_tokens=4096)
+    hidden = synth.make_hidden(4096, W, 6)
+    toks = np.arange(5, 4096, 257, dtype=np.int32)
+    out, _ = check_against_oracle(layer, W, hidden, tokens=toks, what="T=4096")
+    assert np.isfinite(out).all()
+    count = layer.read_dispatch()[0]
+    assert count.sum() == 4096 * 4 and count.min() > 256
+    layer.close()
+
+
+def test_config4_shape_128_experts():
+    """The 128-expert shape on one GPU (no sharding): T=300, oracle on a token sample."""
+    shape = synth.MoeShape(n_experts=128)
+    W = synth.make_weights(shape, 2)
+    layer = make_layer(shape, W, max_tokens=300)
+    hidden = synth.make_hidden(300, W, 2)
+    toks = np.arange(0, 300, 23, dtype=np.int32)
+    check_against_oracle(layer, W, hidden, tokens=toks, what="E=128")
+    layer.close()

@@ -327,9 +327,12 @@ def main():
             # plus the hidden rows in and the fp32 activation out
             gu_bytes = mean_touched * gu_expert_bytes + T * H * 2 + T * k * I * 4
             achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
+            # DRAM read+write of one gate_up launch from the ncu capture summarised in
+            # profiles/gmm_bs_kernel_cfg1_T64.md (245.2 MB at 26 experts touched), scaled by experts touched
+            traffic = 245.2e6 * mean_touched / 26.0 if args.workload == "cfg1" else None
             roofline = {"bound": "hbm", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved,
                         "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
-                        "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                        "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
                         "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gu_ms}
         else:
             gu_flops = T * k * gu_flops_per_pair

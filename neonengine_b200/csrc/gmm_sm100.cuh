@@ -10,6 +10,7 @@
 // their own E8M0 block scales (bf16 = 2 terms exactly, fp32 SwiGLU output = 4 terms, error
 // <= 2^-16 relative); each term is one more accumulating MMA.
 #pragma once
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include "moe_common.cuh"
@@ -332,6 +333,66 @@ __global__ void __launch_bounds__(256) split_rows_stacked_kernel(const void* __r
     }
 }
 
+// Packed-4-bit flavour of the stacked split, for tcgen05.mma.kind::mxf4 (both operands e2m1,
+// weights straight from HBM without expansion).  An e2m1 term carries ~2.6 bits, so a value is
+// written as TERMS terms with scales s, s/6, s/36, ... (s = amax/6; the residual of a term is
+// at most one sixth of its scale's range); the scales are applied by the GEMM epilogue, so
+// they need not be powers of two.  Rows are 64 bytes (128 codes, low nibble = even column)
+// in the 64-byte-swizzled K-major layout: 16-byte unit u of row n sits at u ^ ((n >> 1) & 3).
+// Block per (tile, chunk): TERMS*npad rows x 64 B.  row_scale[p] = s.
+__host__ __device__ inline size_t act4_block_bytes(int terms, int tile_tokens) { return (size_t)terms * tile_tokens * 64; }
+
+template <int TERMS, bool FROM_BF16>
+__global__ void __launch_bounds__(256) split_rows_fp4_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm,
+                                                             int top_k, int K, int n_rows,
+                                                             const int32_t* __restrict__ row_tile,
+                                                             const int32_t* __restrict__ tile_row0,
+                                                             const int32_t* __restrict__ tile_rows, int tile_tokens,
+                                                             const float* __restrict__ amax_in, float amax_const,
+                                                             uint8_t* __restrict__ act, float* __restrict__ row_scale) {
+    const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows * n_chunks) return;
+    const int p = warp / n_chunks, c = warp - p * n_chunks;
+    const int src_row = FROM_BF16 ? perm[p] / top_k : p;
+    const int k0 = c * kChunkK + 4 * lane;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k0 < K) {
+        if (FROM_BF16) {
+            uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(src) + (size_t)src_row * K + k0);
+            v[0] = __uint_as_float(raw.x << 16);
+            v[1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[2] = __uint_as_float(raw.y << 16);
+            v[3] = __uint_as_float(raw.y & 0xffff0000u);
+        } else {
+            float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)src_row * K + k0);
+            v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+        }
+    }
+    const float amax = amax_in ? amax_in[src_row] : amax_const;
+    float scale = fmaxf(amax, 1e-30f) * (1.f / 6.f);
+    if (row_scale && lane == 0 && c == 0) row_scale[p] = scale;
+    const int tile = row_tile[p], j = p - tile_row0[tile];
+    const int npad = (tile_rows[tile] + 7) & ~7;
+    uint8_t* blk = act + ((size_t)tile * n_chunks + c) * act4_block_bytes(TERMS, tile_tokens);
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+        const float inv = 1.f / scale;
+        __nv_fp4x2_storage_t lo = __nv_cvt_float2_to_fp4x2(make_float2(v[0] * inv, v[1] * inv), __NV_E2M1, cudaRoundNearest);
+        __nv_fp4x2_storage_t hi = __nv_cvt_float2_to_fp4x2(make_float2(v[2] * inv, v[3] * inv), __NV_E2M1, cudaRoundNearest);
+        const int n = t * npad + j;
+        *reinterpret_cast<uint16_t*>(blk + (size_t)(n >> 3) * 512 + (n & 7) * 64 + ((((lane >> 3) ^ ((n >> 1) & 3))) << 4) +
+                                     ((lane & 7) << 1)) = (uint16_t)((uint32_t)lo | ((uint32_t)hi << 8));
+        if (t + 1 < TERMS) {
+            __half2_raw blo = __nv_cvt_fp4x2_to_halfraw2(lo, __NV_E2M1), bhi = __nv_cvt_fp4x2_to_halfraw2(hi, __NV_E2M1);
+            float2 flo = __half22float2(*reinterpret_cast<__half2*>(&blo)), fhi = __half22float2(*reinterpret_cast<__half2*>(&bhi));
+            v[0] = fmaf(-flo.x, scale, v[0]); v[1] = fmaf(-flo.y, scale, v[1]);
+            v[2] = fmaf(-fhi.x, scale, v[2]); v[3] = fmaf(-fhi.y, scale, v[3]);
+            scale *= (1.f / 6.f);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // The GEMM.  Persistent CTAs walk items = (token tile, 128-row weight tile), item index =
 // blockIdx.x + i*gridDim.x, weight tile fastest so that concurrent CTAs share a token tile's
@@ -371,13 +432,17 @@ struct GmmParams {
     int* status;
 };
 
-template <int BN_MAX, int TERMS, bool STACK, int KC>
+// MX4: packed 4-bit operands (kind::mxf4): a weight box is 8 KB in shared memory, rows are 64 B.
+template <int BN_MAX, int TERMS, bool STACK, int KC, bool MX4 = false>
 struct GmmSmem {
-    static constexpr int kActBytes = STACK ? TERMS * BN_MAX * 128 : TERMS * 512 + (BN_MAX / 8) * TERMS * 1024;
-    static constexpr int kStage = (KC * (16384 + kActBytes + 512) + 1023) / 1024 * 1024;
+    static_assert(!MX4 || STACK, "packed 4-bit operands are a stacked-mode feature");
+    static constexpr int kABytes = MX4 ? 8192 : 16384;  // one 128 x 128 weight box in shared memory
+    static constexpr int kActBytes = MX4 ? TERMS * BN_MAX * 64
+                                         : (STACK ? TERMS * BN_MAX * 128 : TERMS * 512 + (BN_MAX / 8) * TERMS * 1024);
+    static constexpr int kStage = (KC * (kABytes + kActBytes + 512) + 1023) / 1024 * 1024;
     static constexpr int kSfCols = KC * (STACK ? 4 : 4 * (1 + TERMS));  // TMEM columns of scales per stage
     static constexpr int kAccCols = STACK ? TERMS * BN_MAX : BN_MAX;    // TMEM columns of one accumulator buffer
-    static constexpr int kSfBase = 2 * kAccCols + (STACK ? 4 : 0);  // stacked: 4 columns of unit scales first
+    static constexpr int kSfBase = 2 * kAccCols + (STACK ? 8 : 0);  // stacked: two atoms (N up to 256) of unit scales first
     static constexpr int kTail = 1024;
     static constexpr int kBudget = 225 * 1024;
     static constexpr int kStagesFit = (kBudget - kTail - 1024) / kStage;
@@ -390,22 +455,22 @@ struct GmmSmem {
         return cols;
     }
     static_assert(kStages >= 2, "at least two stages");
-    static_assert(KC * 16384 % 1024 == 0 && kActBytes % 1024 == 0, "alignment");
+    static_assert(KC * kABytes % 1024 == 0 && kActBytes % 512 == 0, "alignment");
 };
 
 constexpr long long kWaitLimitCycles = 400000000ll;  // ~0.2 s at 2 GHz
 
-template <int BN_MAX, int TERMS, bool GATE_UP, bool STACK, int KC>
+template <int BN_MAX, int TERMS, bool GATE_UP, bool STACK, int KC, bool MX4>
 __global__ void __launch_bounds__(192)
 gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA1, const GmmParams p) {
     using namespace sm100;
-    using L = GmmSmem<BN_MAX, TERMS, STACK, KC>;
+    using L = GmmSmem<BN_MAX, TERMS, STACK, KC, MX4>;
     constexpr int STAGES_MAX = L::kStages;
     const int STAGES = p.stages;
     constexpr int SF_COLS = L::kSfCols;
     constexpr int SF_BASE = L::kSfBase;
     constexpr int SF_UNIT = 2 * L::kAccCols;  // stacked mode: atom of unit activation scales
-    constexpr int ACT_OFF = KC * 16384, SFA_OFF = ACT_OFF + KC * L::kActBytes;
+    constexpr int ACT_OFF = KC * L::kABytes, SFA_OFF = ACT_OFF + KC * L::kActBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStage);  // barriers follow the stages in use
@@ -453,7 +518,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int tile = item / p.m_tiles, m = item - tile * p.m_tiles;
             const int e = p.tile_expert[tile], rows = p.tile_rows[tile];
-            const uint32_t act_bytes = STACK ? TERMS * ((rows + 7) >> 3) * 1024
+            const uint32_t act_bytes = MX4 ? TERMS * ((rows + 7) >> 3) * 512 : STACK ? TERMS * ((rows + 7) >> 3) * 1024
                                              : TERMS * 512 + ((rows + 7) >> 3) * TERMS * 1024;
             const uint32_t box = (uint32_t)((e * p.m_tiles + m) * p.n_chunks);
             int box_row = (int)(box * 128);
@@ -505,7 +570,10 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             bool ready = false;  // the current stage's barrier was already seen complete
             const uint32_t smem_base = smem_u32(smem);
             if (STACK) {
-                if (elect_one()) tc_copy_sf(tmem_base + SF_UNIT, make_sf_desc(smem_u32(unit_atom)));
+                if (elect_one()) {  // rows 0..127 and 128..255 of the N operand
+                    tc_copy_sf(tmem_base + SF_UNIT, make_sf_desc(smem_u32(unit_atom)));
+                    tc_copy_sf(tmem_base + SF_UNIT + 4, make_sf_desc(smem_u32(unit_atom)));
+                }
                 __syncwarp();
             }
             for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
@@ -513,7 +581,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 const int rows = p.tile_rows[tile];
                 const int npad = (rows + 7) & ~7;
                 const uint32_t n_mma = STACK ? (uint32_t)(TERMS * npad) : (uint32_t)max(16, round_up_int(rows, 16));
-                const uint32_t idesc0 = make_idesc_bs(5, 0, n_mma, 0, 0);
+                const uint32_t idesc0 = MX4 ? make_idesc_bs(1, 1, n_mma, 0, 0) : make_idesc_bs(5, 0, n_mma, 0, 0);
                 constexpr uint32_t kIdescStep = (1u << 4) | (1u << 29);  // next scale id for A and B
                 const int b = iter & 1, aph = (iter >> 1) & 1;
                 int ok = mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 2, kWaitLimitCycles);
@@ -533,8 +601,18 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     auto issue_chunk = [&](int k) {
                         const uint32_t sf_tmem = sf_stage + k * (SF_COLS / KC);
                         const uint32_t act_smem = st + ACT_OFF + k * L::kActBytes;
-                        const uint64_t a_desc = make_sw128_desc(st + k * 16384);
                         tc_copy_sf(sf_tmem, make_sf_desc(st + SFA_OFF + k * 512));
+                        if (MX4) {
+                            // packed e2m1 x e2m1, K = 64 per instruction, two weight scales each
+                            // (scale ids 0 and 2); activation scales are the unit atom
+                            const uint64_t a4 = make_sw64_desc(st + k * L::kABytes), b4 = make_sw64_desc(act_smem);
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+                                mma_mxf4(d_tmem, a4 + 2 * j, b4 + 2 * j, idesc0 + j * (2u << 29), sf_tmem, tmem_base + SF_UNIT,
+                                         first | (uint32_t)(k | j));
+                            return;
+                        }
+                        const uint64_t a_desc = make_sw128_desc(st + k * L::kABytes);
                         if (STACK) {
                             // activation scales are all 1.0 (scale id 0 of the unit atom); only A's id advances
                             const uint64_t b_desc = make_sw128_desc(act_smem);
@@ -602,7 +680,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 #pragma unroll
 #pragma unroll
                     for (int t = 1; t < TERMS; ++t) {
-                        f *= 0.0625f;
+                        f *= MX4 ? (1.f / 6.f) : 0.0625f;
                         float u[8];
                         tmem_ld8(taddr + t * npad + j8, u);
 #pragma unroll

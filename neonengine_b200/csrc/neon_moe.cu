@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <algorithm>
@@ -60,6 +61,8 @@ struct neon_moe_handle {
     int32_t *tile2_expert = nullptr, *tile2_row0 = nullptr, *tile2_rows = nullptr, *n_tiles2 = nullptr, *row_tile2 = nullptr;
     int tile_cap = 0, kp_h = 0, kp_i = 0;
     CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
+    CUtensorMap tm4_gu{}, tm4_dn{}, tm4_gu2{}, tm4_dn2{};  // the same boxes left packed (4-bit in shared memory)
+    int mx4 = 0;                  // decode tiles: 1 = kind::mxf4 with e2m1 activation terms, 0 = kind::mxf8f6f4 with e4m3 terms
     // expert parallelism: source-side routing/dispatch over all experts, exchange buffers
     ncclComm_t comm = nullptr;
     int n_src = 0, n_cap = 0;     // entries this rank routes (max) / entries it can receive
@@ -225,15 +228,17 @@ EncodeTiledFn encode_tiled_fn() {
 
 // 2-D map over packed 4-bit weight boxes: rows of 128 nibbles (64 B), box = 128 x 128, expanded
 // by TMA to one byte per nibble (16 nibbles + 8 pad bytes per 16 B) with 128-byte swizzle.
-int make_weight_map(neon_moe_handle* h, CUtensorMap* map, void* base, uint64_t n_rows, uint32_t box_rows) {
+int make_weight_map(neon_moe_handle* h, CUtensorMap* map, void* base, uint64_t n_rows, uint32_t box_rows, bool packed) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {128, n_rows};
     cuuint64_t strides[1] = {64};
     cuuint32_t box[2] = {128, box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, base, dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    // packed: nibbles stay packed (64-byte rows, 64-byte swizzle) for kind::mxf4
+    CUresult r = fn(map, packed ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, base, dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    packed ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return NEON_MOE_OK;
@@ -241,7 +246,8 @@ int make_weight_map(neon_moe_handle* h, CUtensorMap* map, void* base, uint64_t n
 
 // Upload (when needed) and re-tile one MXFP4 matrix set into the "tc" format.
 int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* scales, int rows, int K, int gate_up,
-                   int on_device, uint8_t** wt, uint8_t** sfa, CUtensorMap* map, CUtensorMap* map2) {
+                   int on_device, uint8_t** wt, uint8_t** sfa, CUtensorMap* map, CUtensorMap* map2, CUtensorMap* map4,
+                   CUtensorMap* map4_2) {
     const int E = h->n_local;
     const size_t nb = (size_t)E * rows * (K / 2), ns = (size_t)E * rows * (K / 32);
     const uint8_t *d_blocks = blocks, *d_scales = scales;
@@ -267,20 +273,23 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
     CU(h, cudaDeviceSynchronize());
     if (tmp_b) cudaFree(tmp_b);
     if (tmp_s) cudaFree(tmp_s);
-    int rc = make_weight_map(h, map, *wt, (uint64_t)E * m_tiles * n_chunks * 128, 128);
-    if (rc) return rc;
-    return make_weight_map(h, map2, *wt, (uint64_t)E * m_tiles * n_chunks * 128, 256);
+    const uint64_t nrows = (uint64_t)E * m_tiles * n_chunks * 128;
+    int rc;
+    if ((rc = make_weight_map(h, map, *wt, nrows, 128, false)) || (rc = make_weight_map(h, map2, *wt, nrows, 256, false)) ||
+        (rc = make_weight_map(h, map4, *wt, nrows, 128, true)) || (rc = make_weight_map(h, map4_2, *wt, nrows, 256, true)))
+        return rc;
+    return NEON_MOE_OK;
 }
 
 // Token-tile size: decode batches use small tiles with the activation terms stacked along N
 // (one MMA per k-block reads the weight tile once); larger batches use 128-token tiles.
 int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 64 ? 32 : 128); }
 
-template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC>
+template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC, bool MX4 = false>
 int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap& tm2, GmmParams p, cudaStream_t st) {
-    using L = GmmSmem<BN, TERMS, STACK, KC>;
+    using L = GmmSmem<BN, TERMS, STACK, KC, MX4>;
     static bool configured[kMaxDevicesAttr] = {};
-    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP, STACK, KC>;
+    auto kern = gmm_bs_kernel<BN, TERMS, GATE_UP, STACK, KC, MX4>;
     if (!configured[h->cfg.device]) {
         CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::smem_bytes(L::kStages)));
         configured[h->cfg.device] = true;
@@ -301,9 +310,17 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
     return NEON_MOE_OK;
 }
 
+constexpr int kMx4Terms = 6;  // e2m1 terms per activation value on the packed 4-bit path
+
 template <int TERMS, bool GATE_UP>
 int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, const CUtensorMap& tm2, const GmmParams& p,
                cudaStream_t st) {
+    if (tile_tokens <= 32 && h->mx4) {  // packed 4-bit operands, kMx4Terms e2m1 terms per activation
+        const CUtensorMap& q1 = GATE_UP ? h->tm4_gu : h->tm4_dn;
+        const CUtensorMap& q2 = GATE_UP ? h->tm4_gu2 : h->tm4_dn2;
+        if (tile_tokens == 16) return launch_gmm_one<16, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
+        return launch_gmm_one<32, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
+    }
     if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
     if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
     return launch_gmm_one<128, TERMS, GATE_UP, false, 1>(h, tm1, tm2, p, st);
@@ -313,7 +330,10 @@ template <int TERMS, bool FROM_BF16>
 void launch_split(neon_moe_handle* h, int tile_tokens, const TileList& tl, const void* src, int K, int n, int top_k,
                   const float* amax, float amax_const, uint8_t* act, float* row_scale, cudaStream_t st) {
     const int n_chunks = round_up_int(K, kChunkK) / kChunkK;
-    if (tile_tokens <= 32)
+    if (tile_tokens <= 32 && h->mx4)
+        split_rows_fp4_kernel<kMx4Terms, FROM_BF16><<<(n * n_chunks + 7) / 8, 256, 0, st>>>(
+            src, h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
+    else if (tile_tokens <= 32)
         split_rows_stacked_kernel<TERMS, FROM_BF16><<<(n * n_chunks + 7) / 8, 256, 0, st>>>(
             src, h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
     else
@@ -404,6 +424,10 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         const size_t tiles = (size_t)h->n_local + n / tt + 1;
         x_bytes = std::max(x_bytes, tiles * nch_h * act_block_bytes(2, tt, tt <= 32));
         a_bytes = std::max(a_bytes, tiles * nch_i * act_block_bytes(4, tt, tt <= 32));
+        if (tt <= 32) {
+            x_bytes = std::max(x_bytes, tiles * nch_h * act4_block_bytes(kMx4Terms, tt));
+            a_bytes = std::max(a_bytes, tiles * nch_i * act4_block_bytes(kMx4Terms, tt));
+        }
     }
     if ((rc = dev_alloc(h, &h->x_act, x_bytes)) || (rc = dev_alloc(h, &h->a_act, a_bytes)) ||
         (rc = dev_alloc(h, &h->x_scale, n)) || (rc = dev_alloc(h, &h->a_scale, n)) ||
@@ -464,8 +488,8 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
     if ((rc = copy_in(h, &h->dn_bias, dn_bias, (size_t)EL * H, on_device))) return rc;
     if ((rc = load_matrix(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wq, &h->gu_sq))) return rc;
     if ((rc = load_matrix(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wq, &h->dn_sq))) return rc;
-    if ((rc = load_matrix_tc(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wt, &h->gu_sfa, &h->tm_gu, &h->tm_gu2))) return rc;
-    if ((rc = load_matrix_tc(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wt, &h->dn_sfa, &h->tm_dn, &h->tm_dn2))) return rc;
+    if ((rc = load_matrix_tc(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wt, &h->gu_sfa, &h->tm_gu, &h->tm_gu2, &h->tm4_gu, &h->tm4_gu2))) return rc;
+    if ((rc = load_matrix_tc(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wt, &h->dn_sfa, &h->tm_dn, &h->tm_dn2, &h->tm4_dn, &h->tm4_dn2))) return rc;
     CU(h, cudaDeviceSynchronize());
     h->has_weights = true;
     return NEON_MOE_OK;
@@ -515,6 +539,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         // |SwiGLU| <= limit * (limit + 1): a fixed bound replaces the row maximum
         const float a_bound = h->cfg.swiglu_limit * (h->cfg.swiglu_limit + 1.f);
         launch_split<4, false>(h, tt_dn, tld, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
+        const bool mx4_dn = tt_dn <= 32 && h->mx4;
         DBG_SYNC(h, st, "split_rows (activation)");
         // down: rows H, K = I
         g.tile_expert = tld.expert; g.tile_row0 = tld.row0; g.tile_rows = tld.rows; g.n_tiles = tld.n_tiles;
@@ -523,6 +548,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
             uint32_t bits; memcpy(&bits, &a_bound, 4);
             int sb = std::min(std::max((int)((bits >> 23) & 0xffu) - 7, 4 * 4 + 1), 250);
             bits = (uint32_t)sb << 23; memcpy(&g.row_scale_const, &bits, 4);
+            if (mx4_dn) g.row_scale_const = a_bound * (1.f / 6.f);  // split_rows_fp4_kernel's first-term scale
         }
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
         rc = launch_gmm<4, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st);
@@ -833,6 +859,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->ctas_per_sm = (int)value;
     } else if (!strcmp(name, "n_ctas")) {
         h->n_sms = (int)value;
+    } else if (!strcmp(name, "mx4")) {
+        h->mx4 = (int)value;
     } else if (!strcmp(name, "use_graphs")) {
         h->use_graphs = (int)value;
     } else if (!strcmp(name, "sync_debug")) {

@@ -187,6 +187,11 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr, uint32_t
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(group_stride >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
+// Same for the 64-byte swizzle (rows of 64 bytes, 8-row groups of 512 B): layout type 4.
+__device__ __forceinline__ uint64_t make_sw64_desc(uint32_t smem_addr, uint32_t group_stride = 512) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(group_stride >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)4 << 61);
+}
 // Unswizzled scale-factor atom: 32 rows of 16 bytes, 8-row groups 128 B apart.
 __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);

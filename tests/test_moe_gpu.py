@@ -220,3 +220,17 @@ def test_config4_shape_128_experts():
     toks = np.arange(0, 300, 23, dtype=np.int32)
     check_against_oracle(layer, W, hidden, tokens=toks, what="E=128")
     layer.close()
+
+
+def test_packed_fp4_decode_option(full20b):
+    """Option mx4=1: decode passes on tcgen05.mma.kind::mxf4 (packed 4-bit weights in shared
+    memory, six e2m1 terms per activation).  Routing stays exact; outputs meet the contract."""
+    shape, W, layer = full20b
+    layer.set_option("mx4", 1)
+    try:
+        lb = synth.zipf_logit_bias(shape.n_experts)
+        for T, seed in ((64, 12), (3, 13)):
+            hidden = synth.make_hidden(T, W, seed, logit_bias=lb)
+            check_against_oracle(layer, W, hidden, logit_bias=lb, what=f"mx4 T={T}")
+    finally:
+        layer.set_option("mx4", 0)

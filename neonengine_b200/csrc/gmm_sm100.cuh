@@ -154,6 +154,8 @@ __device__ void build_tile_list(const int32_t* __restrict__ idx, int n, int e_lo
 __global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
                                                               DispatchArrays d, int tile_tokens, TileList tl,
                                                               int tile_tokens2, TileList tl2, unsigned* zero_n) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ int dsmem[];
     __shared__ int s_first[kMaxExperts + 1];
     if (zero_n)
@@ -162,6 +164,96 @@ __global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __r
     __syncthreads();  // offsets and counts are in global memory, written by this CTA
     build_tile_list(idx, n, e_lo, n_local, d, tile_tokens, tl, s_first);
     if (tile_tokens2 > 0) build_tile_list(idx, n, e_lo, n_local, d, tile_tokens2, tl2, s_first);
+}
+
+// The same for at most 1024 entries (decode batches): one entry per thread, four barriers, all
+// scans done by warps in shared memory.  Identical results to dispatch_tiles_kernel.
+__global__ void __launch_bounds__(1024) dispatch_tiles_small_kernel(const int32_t* __restrict__ idx, int n, int e_lo,
+                                                                    int n_local, DispatchArrays d, int tile_tokens,
+                                                                    TileList tl) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int dsmem[];
+    int* wc = dsmem;                // [32][n_local] entries of each expert per warp, then their prefix
+    __shared__ int cnt[kMaxExperts], off[kMaxExperts + 1], first[kMaxExperts + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int j = tid; j < 32 * n_local; j += 1024) wc[j] = 0;
+    int e = -1;
+    if (tid < n) {
+        e = idx[tid] - e_lo;
+        if (e < 0 || e >= n_local) e = -1;
+    }
+    __syncthreads();
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) wc[warp * n_local + e] = __popc(peers);
+    __syncthreads();
+    for (int ee = tid; ee < n_local; ee += 1024) {
+        int run = 0;
+#pragma unroll 8
+        for (int w = 0; w < 32; ++w) {
+            int c = wc[w * n_local + ee];
+            wc[w * n_local + ee] = run;
+            run += c;
+        }
+        cnt[ee] = run;
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scans of the counts and of the tile counts, 8 experts per lane
+        int c[8], tsum = 0, csum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int ee = lane * 8 + j;
+            c[j] = ee < n_local ? cnt[ee] : 0;
+            csum += c[j];
+            tsum += (c[j] + tile_tokens - 1) / tile_tokens;
+        }
+        int cpre = csum, tpre = tsum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int a = __shfl_up_sync(0xffffffffu, cpre, o), b = __shfl_up_sync(0xffffffffu, tpre, o);
+            if (lane >= o) { cpre += a; tpre += b; }
+        }
+        int crun = cpre - csum, trun = tpre - tsum;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int ee = lane * 8 + j;
+            if (ee < n_local) {
+                off[ee] = crun;
+                first[ee] = trun;
+                d.count[ee] = c[j];
+                d.offset[ee] = crun;
+            }
+            crun += c[j];
+            trun += (c[j] + tile_tokens - 1) / tile_tokens;
+        }
+        if (lane == 31) {
+            off[n_local] = cpre;
+            first[n_local] = tpre;
+            d.offset[n_local] = cpre;
+            *tl.n_tiles = tpre;
+        }
+    }
+    __syncthreads();
+    if (tid < n) {
+        if (e >= 0) {
+            const int pos = off[e] + wc[warp * n_local + e] + rank;
+            d.perm[pos] = tid;
+            d.inv[tid] = pos;
+            tl.row_tile[pos] = first[e] + (pos - off[e]) / tile_tokens;
+        } else {
+            d.inv[tid] = -1;
+        }
+    }
+    for (int ee = tid; ee < n_local; ee += 1024) {
+        const int lo = off[ee], c = cnt[ee];
+        int t = first[ee];
+        for (int r = 0; r < c; r += tile_tokens, ++t) {
+            tl.expert[t] = ee;
+            tl.row0[t] = lo + r;
+            tl.rows[t] = min(tile_tokens, c - r);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -195,6 +287,8 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
                                                          const int32_t* __restrict__ tile_row0,
                                                          const int32_t* __restrict__ tile_rows, int tile_tokens,
                                                          uint8_t* __restrict__ act) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_rows * n_chunks) return;
@@ -253,6 +347,8 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
 template <bool FROM_BF16>
 __global__ void __launch_bounds__(256) row_amax_kernel(const void* __restrict__ src, int K, int n_rows,
                                                        float* __restrict__ amax_out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (r >= n_rows) return;
     float m = 0.f;
@@ -289,6 +385,8 @@ __global__ void __launch_bounds__(256) split_rows_stacked_kernel(const void* __r
                                                                  const int32_t* __restrict__ tile_rows, int tile_tokens,
                                                                  const float* __restrict__ amax_in, float amax_const,
                                                                  uint8_t* __restrict__ act, float* __restrict__ row_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_rows * n_chunks) return;
@@ -350,6 +448,8 @@ __global__ void __launch_bounds__(256) split_rows_fp4_kernel(const void* __restr
                                                              const int32_t* __restrict__ tile_rows, int tile_tokens,
                                                              const float* __restrict__ amax_in, float amax_const,
                                                              uint8_t* __restrict__ act, float* __restrict__ row_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_rows * n_chunks) return;
@@ -480,6 +580,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -506,6 +607,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();  // everything above touched only this CTA's shared memory and TMEM
     const int n_items = *p.n_tiles * p.m_tiles;
     constexpr size_t act_stride = L::kActBytes;
 

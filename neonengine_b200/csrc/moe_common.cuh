@@ -74,6 +74,13 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream is still draining; pdl_wait() blocks until the
+// predecessor has completed and its writes are visible, pdl_launch_dependents() lets the
+// successor start launching.  Both are no-ops for ordinary launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {

@@ -235,6 +235,8 @@ __global__ void __launch_bounds__(1024)
 router_topk_wide_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
                         const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H, int E,
                         int k, int32_t* __restrict__ idx, float* __restrict__ w, float* __restrict__ tok_amax) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char rsmem[];
     uint4* xs = reinterpret_cast<uint4*>(rsmem);            // [H/8] bf16 x 8
     float* lg = reinterpret_cast<float*>(rsmem + H * 2);    // [E]
@@ -475,6 +477,24 @@ __global__ void __launch_bounds__(32 * WARPS) expert_mma_kernel(ExpertParams p) 
 // (experts of another rank) are skipped.
 __global__ void combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, int T, int H,
                                int k, float* __restrict__ out) {
+    const int t = blockIdx.y;
+    const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c4 * 4 >= H) return;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sl = 0; sl < k; ++sl) {
+        int pos = inv[t * k + sl];
+        if (pos < 0) continue;
+        float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * H + 4 * c4);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * H + 4 * c4) = s;
+}
+
+// combine_kernel for the main path (programmatic dependent launch aware).
+__global__ void combine_main_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, int T, int H, int k,
+                                    float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.y;
     const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
     if (c4 * 4 >= H) return;

@@ -50,6 +50,7 @@ struct neon_moe_handle {
     int path = 2;                 // 1 = mma.sync kernels, 2 = TMA + tcgen05 block-scaled GEMM
     uint32_t a_tx_bytes = 8192;   // bytes one 128x128 4-bit box adds to its mbarrier
     int max_stages = 0, ctas_per_sm = 1;
+    int pdl = 1;                  // programmatic dependent launch between the kernels of a pass
     int sync_debug = 0;           // synchronise and check after every kernel (slow; names the failing kernel)
     long long* trace = nullptr;
     uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
@@ -124,6 +125,24 @@ int fail(neon_moe_handle* h, int code, const char* fmt, ...) {
             if (e_ != cudaSuccess) return fail(h, NEON_MOE_ECUDA, "%s: %s", what, cudaGetErrorString(e_)); \
         }                                                                                            \
     } while (0)
+
+// Kernel launch with the programmatic-dependent-launch attribute (when `pdl`): the kernel may be
+// scheduled while its predecessor in the stream drains; the kernels call pdl_wait() before they
+// touch the predecessor's output.
+template <typename... KArgs, typename... Args>
+void launch_k(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 template <typename T>
 int dev_alloc(neon_moe_handle* h, T** p, size_t count) {
@@ -305,7 +324,7 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
     if (h->max_stages > 0) stages = std::max(2, std::min(stages, h->max_stages));
     p.stages = stages;
     p.tmem_cols = L::tmem_cols(stages);
-    kern<<<ctas, 192, L::smem_bytes(stages), st>>>(KC == 2 ? tm2 : tm1, tm1, p);
+    launch_k(h->pdl != 0, kern, dim3(ctas), dim3(192), (size_t)L::smem_bytes(stages), st, KC == 2 ? tm2 : tm1, tm1, p);
     h->launches++;
     return NEON_MOE_OK;
 }
@@ -331,14 +350,14 @@ void launch_split(neon_moe_handle* h, int tile_tokens, const TileList& tl, const
                   const float* amax, float amax_const, uint8_t* act, float* row_scale, cudaStream_t st) {
     const int n_chunks = round_up_int(K, kChunkK) / kChunkK;
     if (tile_tokens <= 32 && h->mx4)
-        split_rows_fp4_kernel<kMx4Terms, FROM_BF16><<<(n * n_chunks + 7) / 8, 256, 0, st>>>(
-            src, h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
+        launch_k(h->pdl != 0, split_rows_fp4_kernel<kMx4Terms, FROM_BF16>, dim3((n * n_chunks + 7) / 8), dim3(256), 0, st, src,
+                 h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
     else if (tile_tokens <= 32)
-        split_rows_stacked_kernel<TERMS, FROM_BF16><<<(n * n_chunks + 7) / 8, 256, 0, st>>>(
-            src, h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
+        launch_k(h->pdl != 0, split_rows_stacked_kernel<TERMS, FROM_BF16>, dim3((n * n_chunks + 7) / 8), dim3(256), 0, st, src,
+                 h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
     else
-        split_rows_kernel<TERMS, FROM_BF16, false><<<(n * n_chunks + 7) / 8, 256, 0, st>>>(
-            src, h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, act);
+        launch_k(h->pdl != 0, split_rows_kernel<TERMS, FROM_BF16, false>, dim3((n * n_chunks + 7) / 8), dim3(256), 0, st, src,
+                 h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, act);
     h->launches++;
 }
 
@@ -511,13 +530,17 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         TileList tl2{h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2};
         const TileList& tld = tt2 ? tl2 : tl;
         const bool stacked = tt <= 32;
-        dispatch_tiles_kernel<<<1, 1024, (size_t)(33 * EL) * sizeof(int), st>>>(
-            idx, n, e_lo, EL, d, tt, tl, tt2, tl2, nullptr);
+        if (n <= 1024)
+            launch_k(h->pdl != 0, dispatch_tiles_small_kernel, dim3(1), dim3(1024), (size_t)(32 * EL) * sizeof(int), st, idx, n,
+                     e_lo, EL, d, tt, tl);
+        else
+            launch_k(h->pdl != 0, dispatch_tiles_kernel, dim3(1), dim3(1024), (size_t)(33 * EL) * sizeof(int), st, idx, n, e_lo,
+                     EL, d, tt, tl, tt2, tl2, (unsigned*)nullptr);
         h->launches++;
         DBG_SYNC(h, st, "dispatch_tiles_kernel");
         const int nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
         if (stacked && !hidden_amax) {  // no producer kernel measured the rows: do it here
-            row_amax_kernel<true><<<(rows + 7) / 8, 256, 0, st>>>(hidden, H, rows, h->x_amax);
+            launch_k(h->pdl != 0, row_amax_kernel<true>, dim3((rows + 7) / 8), dim3(256), 0, st, hidden, H, rows, h->x_amax);
             h->launches++;
             hidden_amax = h->x_amax;
         }
@@ -582,7 +605,11 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         mark(h, st, prof);
     }
     dim3 cgrid((H / 4 + 127) / 128, rows);
-    combine_kernel<<<cgrid, 128, 0, st>>>(h->y, h->inv, rows, H, k_eff, out);
+    if (h->path == 2)
+        launch_k(h->pdl != 0, combine_main_kernel, cgrid, dim3(128), 0, st, (const float*)h->y, (const int32_t*)h->inv, rows, H,
+                 k_eff, out);
+    else
+        combine_kernel<<<cgrid, 128, 0, st>>>(h->y, h->inv, rows, H, k_eff, out);
     h->launches++;
     mark(h, st, prof);
     return NEON_MOE_OK;
@@ -592,8 +619,9 @@ static void launch_router(neon_moe_handle* h, const void* hidden, int T, const f
                           float* tok_amax, cudaStream_t st) {
     const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k;
     if (h->path == 2)
-        router_topk_wide_kernel<<<T, 1024, H * 2 + E * sizeof(float), st>>>(
-            static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, idx, w, tok_amax);
+        launch_k(h->pdl != 0, router_topk_wide_kernel, dim3(T), dim3(1024), H * 2 + E * sizeof(float), st,
+                 static_cast<const uint16_t*>(hidden), (const uint16_t*)h->router_w, (const uint16_t*)h->router_b, logit_bias, T, H,
+                 E, k, idx, w, tok_amax);
     else
         router_topk_kernel<256><<<T, 256, (H + E) * sizeof(float), st>>>(
             static_cast<const uint16_t*>(hidden), h->router_w, h->router_b, logit_bias, T, H, E, k, idx, w);
@@ -859,6 +887,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->ctas_per_sm = (int)value;
     } else if (!strcmp(name, "n_ctas")) {
         h->n_sms = (int)value;
+    } else if (!strcmp(name, "pdl")) {
+        h->pdl = (int)value;
     } else if (!strcmp(name, "mx4")) {
         h->mx4 = (int)value;
     } else if (!strcmp(name, "use_graphs")) {

@@ -490,6 +490,119 @@ __global__ void combine_kernel(const float* __restrict__ y, const int32_t* __res
     *reinterpret_cast<float4*>(out + (size_t)t * H + 4 * c4) = s;
 }
 
+// Router for large batches: one CTA per 8 tokens, so each expert row is read from L2 once per
+// 8 tokens.  Per (token, expert) the arithmetic and its order are exactly those of
+// router_topk_wide_kernel (same lane striding, same shuffle tree), so routing does not depend on
+// which of the two kernels ran.
+__global__ void __launch_bounds__(1024)
+router_topk_block8_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
+                          const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H, int E,
+                          int k, int32_t* __restrict__ idx, float* __restrict__ w) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int TOK = 8;
+    extern __shared__ __align__(16) unsigned char rsmem[];
+    uint4* xs = reinterpret_cast<uint4*>(rsmem);                       // [TOK][H/8]
+    float* lg = reinterpret_cast<float*>(rsmem + (size_t)TOK * H * 2);  // [TOK][E]
+    const int t0 = blockIdx.x * TOK, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nvec = H / 8, ntok = min(TOK, T - t0);
+    for (int i = tid; i < TOK * nvec; i += 1024) {
+        const int tt = i / nvec;
+        xs[i] = tt < ntok ? reinterpret_cast<const uint4*>(x + (size_t)(t0 + tt) * H)[i - tt * nvec] : make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += 32) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(wr + (size_t)e * H);
+        float acc[TOK];
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) acc[tt] = 0.f;
+        constexpr int UNROLL = 6;
+        for (int base = 0; base < nvec; base += 32 * UNROLL) {
+            uint4 wv[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int i = base + u * 32 + lane;
+                wv[u] = i < nvec ? __ldg(wrow + i) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int i = base + u * 32 + lane;
+                if (i < nvec) {
+                    const uint32_t wa[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+#pragma unroll
+                    for (int tt = 0; tt < TOK; ++tt) {
+                        uint4 xv = xs[tt * nvec + i];
+                        const uint32_t xa[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[tt] = fmaf(__uint_as_float(xa[j] << 16), __uint_as_float(wa[j] << 16), acc[tt]);
+                            acc[tt] = fmaf(__uint_as_float(xa[j] & 0xffff0000u), __uint_as_float(wa[j] & 0xffff0000u), acc[tt]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) {
+            float a = acc[tt];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            if (lane == 0) {
+                float v = a + bf16_bits_to_float(br[e]);
+                if (logit_bias) v += logit_bias[e];
+                lg[tt * E + e] = v;
+            }
+        }
+    }
+    __syncthreads();
+    if (warp < ntok) {  // warp tt selects for token t0 + tt
+        const float* lgt = lg + warp * E;
+        const int t = t0 + warp;
+        unsigned long long keys[kMaxExperts / 32];
+#pragma unroll
+        for (int j = 0; j < kMaxExperts / 32; ++j) {
+            int e = lane + 32 * j;
+            keys[j] = (e < E) ? logit_key(lgt[e], e) : 0ull;
+        }
+        float sel[kMaxTopK];
+        int seli[kMaxTopK];
+#pragma unroll
+        for (int s = 0; s < kMaxTopK; ++s) {
+            if (s < k) {
+                unsigned long long best = 0ull;
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j) best = keys[j] > best ? keys[j] : best;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                    best = other > best ? other : best;
+                }
+                int e = 0x7fffffff - (int)(uint32_t)(best & 0xffffffffull);
+                seli[s] = e;
+                sel[s] = lgt[e];
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j)
+                    if (lane + 32 * j == e) keys[j] = 0ull;
+            }
+        }
+        if (lane == 0) {
+            float m = sel[0], den = 0.f, pr[kMaxTopK];
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    pr[s] = expf(sel[s] - m);
+                    den += pr[s];
+                }
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    idx[t * k + s] = seli[s];
+                    w[t * k + s] = pr[s] / den;
+                }
+        }
+    }
+}
+
 // combine_kernel for the main path (programmatic dependent launch aware).
 __global__ void combine_main_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, int T, int H, int k,
                                     float* __restrict__ out) {

@@ -618,7 +618,17 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
 static void launch_router(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, int32_t* idx, float* w,
                           float* tok_amax, cudaStream_t st) {
     const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k;
-    if (h->path == 2)
+    if (h->path == 2 && T > 64) {  // large batches never need the token maxima (128-token tiles scale per block)
+        const size_t smem = (size_t)8 * H * 2 + (size_t)8 * E * sizeof(float);
+        static bool configured[kMaxDevicesAttr] = {};
+        if (!configured[h->cfg.device]) {
+            cudaFuncSetAttribute(router_topk_block8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+            configured[h->cfg.device] = true;
+        }
+        launch_k(h->pdl != 0, router_topk_block8_kernel, dim3((T + 7) / 8), dim3(1024), smem, st,
+                 static_cast<const uint16_t*>(hidden), (const uint16_t*)h->router_w, (const uint16_t*)h->router_b, logit_bias, T, H,
+                 E, k, idx, w);
+    } else if (h->path == 2)
         launch_k(h->pdl != 0, router_topk_wide_kernel, dim3(T), dim3(1024), H * 2 + E * sizeof(float), st,
                  static_cast<const uint16_t*>(hidden), (const uint16_t*)h->router_w, (const uint16_t*)h->router_b, logit_bias, T, H,
                  E, k, idx, w, tok_amax);

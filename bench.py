@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the gpt-oss-shaped MoE layer (tokens/s) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2|cfg4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2|cfg3|cfg4] [--impl reference]
 
 A step is one pass of the MoE layer over one batch of seeded synthetic hidden states.
 Default workload at one GPU is the batched-decode configuration (T=64 tokens, Zipf-skewed
@@ -16,6 +16,8 @@ One JSON line is printed by rank 0:
   roofline  achieved HBM GB/s of the dominant kernel (gate_up expert product) = its
             algorithmic bytes / its mean launch duration, against the measured copy peak
   cpu_baseline  the CPU oracle on a bounded sample of the same workload, on the host cores
+`--workload cfg3` runs the whole gpt-oss-20b-shaped decoder (24 layers, decode batch 8, 4096-token
+K/V cache, 201088-token vocabulary; one step = one new token per sequence, tokens fed back).
 `--impl reference` times the CPU oracle alone (the nominal reference engine has no
 implementation of this path; the oracle is its stand-in on the host cores).
 """
@@ -44,6 +46,8 @@ WORKLOADS = {
     "cfg0": (1, 32, False, "gpt-oss-20b MoE layer, decode T=1"),
     "cfg1": (64, 32, True, "gpt-oss-20b MoE layer, batched decode T=64, Zipf(1.1) router bias"),
     "cfg2": (4096, 32, False, "gpt-oss-20b MoE layer, prefill T=4096, uniform routing"),
+    "cfg3": (8, 32, False, "gpt-oss-20b-shaped decoder, 24 layers, decode batch 8, 4096-token bf16 K/V cache, "
+                           "vocabulary 201088, random-init weights"),
     "cfg4": (8192, 128, False, "gpt-oss-120b-shaped MoE layer, 128 experts, T=8192 tokens per GPU, uniform routing, "
                                "experts sharded over the GPUs (expert parallel) when more than one"),
 }
@@ -162,6 +166,169 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def decoder_cpu_sample(vocab_slice=8192):
+    """Times the CPU restatement of one decode step on a bounded sample: ONE layer at the real
+    widths (batch 8, 4096-token cache) plus a `vocab_slice`-row slice of the unembedding, and
+    extrapolates to 24 layers and the whole vocabulary.  Returns (tokens/s, cores, description)."""
+    import dataclasses
+    import oracle
+    from oracle import decoder_oracle as dor
+    from neonengine_b200.decoder_synth import DecoderShape, make_decoder_weights, make_kv
+    oracle.lib()
+    full = DecoderShape()
+    shape = dataclasses.replace(full, n_layers=1, vocab=vocab_slice)
+    B, ctx = 8, 4096
+    w = make_decoder_weights(shape, 0)
+    k, v = make_kv(shape, 0, B, ctx, 0)
+    tokens = np.arange(B, dtype=np.int32) * 977 % shape.vocab
+    pos = np.full(B, ctx - 1, np.int32)
+    moe_s = [0.0]
+
+    def moe_fn(l, xn):
+        t0 = time.perf_counter()
+        out = oracle.moe_forward(np.ascontiguousarray(xn), w.moe[l])[0]
+        moe_s[0] += time.perf_counter() - t0
+        return out
+    t0 = time.perf_counter()
+    r = dor.decoder_step(w, [k], [v], tokens, pos, moe_fn)
+    t_all = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    dor.linear(r["xn"], w.unembed)
+    t_head = time.perf_counter() - t0
+    t_layer = t_all - t_head
+    t_step = full.n_layers * t_layer + t_head * full.vocab / vocab_slice
+    desc = (f"one decode step of batch {B}: 1 of {full.n_layers} layers at the real widths ({t_layer:.2f} s, of which "
+            f"MoE {moe_s[0]:.2f} s) and {vocab_slice} of {full.vocab} unembedding rows ({t_head:.2f} s), "
+            f"extrapolated to the whole step ({t_step:.1f} s); numpy float64 + OpenMP C MoE")
+    return B / t_step, oracle.n_threads(), desc
+
+
+def run_decoder_reference(args):
+    tps, cores, desc = decoder_cpu_sample()
+    line = {"impl": "reference", "metric": "decoder_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": 1, "warmup": 0, "ms_per_step": 8 / tps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": "cfg3", "description": WORKLOADS["cfg3"][3]},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_decoder(args, local_rank):
+    """cfg3: N independent replicas of the decoder (one per GPU; the stack does not shard),
+    value = tokens all replicas produce per second."""
+    import torch
+    import torch.distributed as dist
+    from neonengine_b200.decoder_synth import AttentionWeights, DecoderShape
+    from neonengine_b200.decoder_system import DecoderSystem
+    from neonengine_b200.synth import MoeWeights
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dev = torch.device("cuda", local_rank)
+    shape = DecoderShape()
+    B, ctx = 8, 4096
+    H = shape.hidden
+    dec = DecoderSystem(shape, B, ctx, device=local_rank)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+
+    def normal(dims, std, mean=0.0):
+        return (torch.randn(dims, generator=gen, device=dev, dtype=torch.float32) * std + mean).to(torch.bfloat16).contiguous()
+
+    embed, unembed = normal((shape.vocab, H), 0.02), normal((shape.vocab, H), 0.02)
+    dec.set_embeddings(embed, unembed, normal((H,), 0.1, 1.0))
+    del embed, unembed
+    # expert tensors: one seeded host generation, uploaded once; every layer keeps its own
+    # re-tiled copy in HBM (distinct memory), routers and attention blocks differ per layer
+    mw = synth.make_weights(shape.moe, 0)
+    dev_moe = [torch.from_numpy(a).to(dev) for a in (mw.gate_up_blocks, mw.gate_up_scales, mw.gate_up_bias.view(np.int16),
+                                                     mw.down_blocks, mw.down_scales, mw.down_bias.view(np.int16))]
+    for l in range(shape.n_layers):
+        dec.set_attention(l, AttentionWeights(
+            ln1=normal((H,), 0.1, 1.0), wqkv=normal((shape.qkv_rows, H), 0.02), bqkv=normal((shape.qkv_rows,), 0.02),
+            sinks=normal((shape.n_q_heads,), 1.0), wo=normal((H, shape.q_dim), 0.02), bo=normal((H,), 0.02),
+            ln2=normal((H,), 0.1, 1.0)))
+        dec.set_moe(l, MoeWeights(shape.moe, normal((shape.moe.n_experts, H), 0.02), normal((shape.moe.n_experts,), 0.02),
+                                  dev_moe[0], dev_moe[1], dev_moe[2], dev_moe[3], dev_moe[4], dev_moe[5]))
+        dec.load_kv(l, normal((B, ctx - 1, shape.n_kv_heads, 64), 1.0), normal((B, ctx - 1, shape.n_kv_heads, 64), 1.0))
+    del dev_moe
+    torch.cuda.synchronize()
+
+    tokens = (torch.arange(B, device=dev, dtype=torch.int32) * 977 + 11 * rank) % shape.vocab
+    positions = torch.full((B,), ctx - 1, device=dev, dtype=torch.int32)
+    pos_host = np.full(B, ctx - 1, np.int32)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(n):  # the argmax of one step is the next step's input token
+        for _ in range(n):
+            dec.step(tokens, positions, next_tokens=tokens)
+
+    warm = max(args.warmup, 3)
+    run(warm)
+    barrier()
+    l0 = dec.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        run(args.steps)
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        launches = dec.launch_count() - l0
+        dense_b, kv_b, moe_b = dec.step_bytes(pos_host)
+        # end to end: host token ids in, host next tokens out, one blocking call per step
+        e2e_steps = max(10, min(args.steps, 200))
+        tok_pin = torch.from_numpy(tokens.cpu().numpy().copy()).pin_memory()
+        pos_pin = torch.from_numpy(pos_host.copy()).pin_memory()
+        nxt_pin = torch.zeros(B, dtype=torch.int32).pin_memory()
+        for _ in range(3):
+            dec.step_host_ptr(tok_pin.data_ptr(), pos_pin.data_ptr(), B, nxt_pin.data_ptr())
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            dec.step_host_ptr(tok_pin.data_ptr(), pos_pin.data_ptr(), B, nxt_pin.data_ptr())
+            tok_pin.copy_(nxt_pin)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+    step_s = ms / args.steps * 1e-3
+    peaks, peak_kind = measured_peaks()
+    step_bytes = dense_b + kv_b + moe_b
+    achieved = step_bytes / step_s / 1e9
+    line = {"metric": "decoder_tokens_per_s", "value": world * B / step_s, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg3", "description": WORKLOADS["cfg3"][3], "batch": B, "cache_tokens": ctx,
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (the stack does not shard)",
+                       "l2_policy": f"each step streams {step_bytes / 1e9:.1f} GB of weights and cache, far beyond the 126 MB L2; "
+                                    "the tokens of a step are the previous step's argmax"},
+            "e2e": {"value": world * B * e2e_steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * 4,
+                    "d2h_bytes_per_step": B * 4, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "whole decode step (one CUDA graph of %d kernels)" % (launches // max(args.steps, 1)),
+                         "achieved": achieved, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes_per_launch": step_bytes,
+                         "bytes": {"dense_weights": dense_b, "kv_cache": kv_b, "moe_experts_touched": moe_b},
+                         "ms_per_launch": ms / args.steps},
+            "clocks": clocks.summary()}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tps, cores, desc = decoder_cpu_sample()
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    dec.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -177,8 +344,12 @@ def main():
     if args.workload is None:
         args.workload = "cfg1" if max(world, args.gpus) == 1 else "cfg4"
     if args.steps is None:
-        args.steps = 2000 if WORKLOADS[args.workload][0] <= 64 else 50
+        args.steps = 200 if args.workload == "cfg3" else 2000 if WORKLOADS[args.workload][0] <= 64 else 50
     if args.impl == "reference":
+        if args.workload == "cfg3":
+            if rank == 0:
+                run_decoder_reference(args)
+            return
         if args.steps > 64:
             args.steps = 8
         run_reference(args, rank)
@@ -195,6 +366,10 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    if args.workload == "cfg3":
+        run_decoder(args, local_rank)
+        return
 
     T, E, zipf, desc = WORKLOADS[args.workload]
     shape = synth.MoeShape(n_experts=E)

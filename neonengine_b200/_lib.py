@@ -23,6 +23,33 @@ class NeonMoeConfig(ctypes.Structure):
                 ("max_tokens", c_int), ("ep_rank", c_int), ("ep_size", c_int), ("device", c_int)]
 
 
+class NeonDecoderConfig(ctypes.Structure):
+    """Mirror of ``neon_decoder_config`` (include/neon_decoder.h)."""
+    _fields_ = [("n_layers", c_int), ("hidden", c_int), ("n_q_heads", c_int), ("n_kv_heads", c_int),
+                ("head_dim", c_int), ("vocab", c_int), ("max_batch", c_int), ("max_ctx", c_int), ("window", c_int),
+                ("rope_theta", ctypes.c_float), ("rope_factor", ctypes.c_float), ("rope_orig_ctx", ctypes.c_float),
+                ("rope_beta_fast", ctypes.c_float), ("rope_beta_slow", ctypes.c_float), ("rms_eps", ctypes.c_float),
+                ("inter", c_int), ("n_experts", c_int), ("top_k", c_int),
+                ("swiglu_limit", ctypes.c_float), ("swiglu_alpha", ctypes.c_float), ("device", c_int)]
+
+
+# name -> (restype, argtypes); must list every symbol include/neon_decoder.h declares
+DECODER_SIGNATURES = {
+    "neon_decoder_create": (c_int, [ctypes.POINTER(NeonDecoderConfig), ctypes.POINTER(c_void_p)]),
+    "neon_decoder_destroy": (c_int, [c_void_p]),
+    "neon_decoder_last_error": (ctypes.c_char_p, [c_void_p]),
+    "neon_decoder_set_embeddings": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
+    "neon_decoder_set_attention": (c_int, [c_void_p, c_int] + [c_void_p] * 7 + [c_int]),
+    "neon_decoder_set_moe": (c_int, [c_void_p, c_int] + [c_void_p] * 8 + [c_int]),
+    "neon_decoder_load_kv": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "neon_decoder_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "neon_decoder_step_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "neon_decoder_read": (c_int, [c_void_p, ctypes.c_char_p, c_void_p, ctypes.c_uint64]),
+    "neon_decoder_set_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.c_int64]),
+    "neon_decoder_launch_count": (ctypes.c_int64, [c_void_p]),
+    "neon_decoder_step_bytes": (c_int, [c_void_p, c_void_p, c_int, ctypes.POINTER(ctypes.c_double)]),
+}
+
 # name -> (restype, argtypes); must list every symbol include/neon_moe.h declares
 SIGNATURES = {
     "neon_moe_create": (c_int, [ctypes.POINTER(NeonMoeConfig), ctypes.POINTER(c_void_p)]),
@@ -60,7 +87,7 @@ def load() -> ctypes.CDLL:
         raise ImportError(f"{SO_PATH} is missing: build it with `python -m neonengine_b200.build` "
                           "(there is no CPU fallback)")
     lib = ctypes.CDLL(SO_PATH)
-    for name, (res, args) in SIGNATURES.items():
+    for name, (res, args) in {**SIGNATURES, **DECODER_SIGNATURES}.items():
         fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
         fn.restype = res
         fn.argtypes = args

@@ -12,9 +12,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libneon_moe.so")
-SOURCES = ["neon_moe.cu"]
+SOURCES = ["neon_moe.cu", "neon_decoder.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math=false", "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]
+              "-Xcompiler", "-fPIC", "-cudart", "static"]
 
 
 def _newest_source() -> float:
@@ -26,16 +26,30 @@ def _newest_source() -> float:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles every source to an object (in parallel) and links the shared library."""
     if not force and os.path.exists(SO) and os.path.getmtime(SO) >= _newest_source():
         return SO
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
-    cmd = ["nvcc", *flags, *(["-Xptxas", "-v"] if verbose else []),
-           *[os.path.join(CSRC, s) for s in SOURCES], "-o", SO, "-ldl"]
+    objdir = os.path.join(HERE, "_obj")
+    os.makedirs(objdir, exist_ok=True)
+    procs = []
+    for src in SOURCES:
+        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", os.path.join(CSRC, src), "-o", obj]
+        procs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    objs = []
+    for cmd, obj, proc in procs:
+        out, _ = proc.communicate()
+        if verbose or proc.returncode:
+            sys.stderr.write(out)
+        if proc.returncode:
+            raise RuntimeError("nvcc failed: " + " ".join(cmd))
+        objs.append(obj)
+    cmd = ["nvcc", *NVCC_FLAGS, "-shared", *objs, "-o", SO, "-ldl"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode:
-        raise RuntimeError("nvcc failed: " + " ".join(cmd))
+        raise RuntimeError("nvcc link failed: " + " ".join(cmd))
     return SO
 
 

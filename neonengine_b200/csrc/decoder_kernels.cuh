@@ -1,0 +1,386 @@
+// Kernels of the gpt-oss-shaped decoder around the MoE layer (decode step, small batch):
+// embedding gather, RMSNorm, bf16 GEMV for the attention projections and the unembedding,
+// YaRN rotary embedding + KV-cache append, grouped-query attention over the cache with
+// per-head sink logits and an optional sliding window, residual adds, argmax.
+// All of them are HBM/L2 streaming work on CUDA cores; activations between them are fp32
+// (residual stream, q, attention partials) or bf16 (normalised activations, K/V cache).
+#pragma once
+#include "moe_common.cuh"
+
+namespace neon {
+
+constexpr int kDecMaxBatch = 8;
+
+__device__ __forceinline__ uint16_t f32_to_bf16_rn(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+
+// x[b, :] = embed[token[b], :] (bf16 -> fp32 residual stream).
+__global__ void embed_kernel(const uint16_t* __restrict__ embed, const int32_t* __restrict__ tokens, int H,
+                             float* __restrict__ x) {
+    const int b = blockIdx.x;
+    const uint16_t* row = embed + (size_t)tokens[b] * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) x[(size_t)b * H + i] = bf16_bits_to_float(row[i]);
+}
+
+// x[b, :] += addend[b, :] (when addend != nullptr; x is written back), then
+// y[b, :] = bf16( x[b, :] * rsqrt(mean(x^2) + eps) * w[:] ), one CTA per token.  The sum of
+// squares is reduced in a fixed order (thread-strided partials, shuffle tree, warp 0).
+__global__ void __launch_bounds__(256) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ addend,
+                                                      const uint16_t* __restrict__ w, int H, float eps,
+                                                      uint16_t* __restrict__ y) {
+    __shared__ float part[8];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    float* xr = x + (size_t)b * H;
+    float s = 0.f;
+    if (addend) {
+        const float* ar = addend + (size_t)b * H;
+        for (int i = tid; i < H; i += 256) {
+            const float v = xr[i] + ar[i];
+            xr[i] = v;
+            s = fmaf(v, v, s);
+        }
+    } else {
+        for (int i = tid; i < H; i += 256) s = fmaf(xr[i], xr[i], s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((tid & 31) == 0) part[tid >> 5] = s;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += part[i];
+    const float r = rsqrtf(tot / (float)H + eps);
+    for (int i = tid; i < H; i += 256) y[(size_t)b * H + i] = f32_to_bf16_rn(xr[i] * r * bf16_bits_to_float(w[i]));
+}
+
+// Padding (in bf16 elements) that makes a K-element activation row start 16 banks after the
+// previous one, so that the eight rows a quarter-warp reads together never share a bank.
+__host__ __device__ inline int gemv_row_pad(int K) { return ((16 - (K / 2) % 32 + 32) % 32) * 2; }
+
+// out[b, r] (+)= sum_k W[r, k] * x[b, k] + bias[r] for b < B <= 8: a skinny GEMM whose N is the
+// batch, on mma.sync m16n8k16 (bf16 in, fp32 accumulate).  W bf16 [rows, K] row-major is
+// streamed from HBM exactly once; x bf16 [B, K] is staged in shared memory (missing batch rows
+// are zero).  A CTA owns 16-row tiles; its 8 warps split K in interleaved 32-element blocks
+// (together they read 512 contiguous bytes of each row) and their accumulators are summed
+// through shared memory.  The sum over k does not depend on which mma slot a k lands in, so
+// each thread feeds the 8 consecutive elements of one 16-byte load to two mma's and reads the
+// matching 16 bytes of x: no shuffles, no scalar loads.  K % 32 == 0.
+// accumulate != 0: out += result (residual add); otherwise out = result.
+__global__ void __launch_bounds__(256, 3) gemv_mma_kernel(const uint16_t* __restrict__ W, const uint16_t* __restrict__ bias,
+                                                          const uint16_t* __restrict__ x, int B, int rows, int K,
+                                                          int accumulate, float* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char gsm[];
+    constexpr int U = 3;  // k-blocks per warp in flight
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int xstride = K + gemv_row_pad(K);  // elements
+    uint16_t* xs = reinterpret_cast<uint16_t*>(gsm);
+    float* red = reinterpret_cast<float*>(gsm + (size_t)8 * xstride * 2);  // [8 warps][128]
+    const int nkb = K / 32, n_tiles = (rows + 15) / 16;
+
+    auto load_batch = [&](uint4 (&wa)[U], uint4 (&wb)[U], const uint16_t* ra, const uint16_t* rb, int kb0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int kb = kb0 + u * 8;
+            if (kb < nkb) {
+                wa[u] = ldg_stream(reinterpret_cast<const uint4*>(ra + kb * 32 + t * 8));
+                wb[u] = ldg_stream(reinterpret_cast<const uint4*>(rb + kb * 32 + t * 8));
+            } else {
+                wa[u] = wb[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    int tile = blockIdx.x;
+    uint4 wa[U], wb[U];
+    const uint16_t *ra = nullptr, *rb = nullptr;
+    if (tile < n_tiles) {  // first weights are already in flight while x is staged
+        ra = W + (size_t)min(tile * 16 + g, rows - 1) * K;
+        rb = W + (size_t)min(tile * 16 + g + 8, rows - 1) * K;
+        load_batch(wa, wb, ra, rb, warp);
+    }
+    for (int i = tid; i < 8 * (K / 8); i += 256) {
+        const int b = i / (K / 8), c = i % (K / 8);
+        const uint4 v = b < B ? reinterpret_cast<const uint4*>(x)[(size_t)b * (K / 8) + c] : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(xs + (size_t)b * xstride + c * 8) = v;
+    }
+    __syncthreads();
+    for (; tile < n_tiles; tile += gridDim.x) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int kb0 = warp; kb0 < nkb; kb0 += 8 * U) {
+            uint4 na[U], nb[U];
+            const int next = kb0 + 8 * U;
+            if (next < nkb) load_batch(na, nb, ra, rb, next);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int kb = kb0 + u * 8;
+                if (kb < nkb) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)g * xstride + kb * 32 + t * 8);
+                    const uint32_t a0[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
+                    const uint32_t a1[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+                    mma_bf16_16816(c, a0, xv.x, xv.y);
+                    mma_bf16_16816(c, a1, xv.z, xv.w);
+                }
+            }
+            if (next < nkb) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) { wa[u] = na[u]; wb[u] = nb[u]; }
+            }
+        }
+        // next tile's first weights go in flight before the reduction
+        const int this_tile = tile, nt = tile + gridDim.x;
+        if (nt < n_tiles) {
+            ra = W + (size_t)min(nt * 16 + g, rows - 1) * K;
+            rb = W + (size_t)min(nt * 16 + g + 8, rows - 1) * K;
+            load_batch(wa, wb, ra, rb, warp);
+        }
+        *reinterpret_cast<float4*>(red + warp * 128 + lane * 4) = make_float4(c[0], c[1], c[2], c[3]);
+        __syncthreads();
+        if (tid < 128) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) v += red[w * 128 + tid];
+            const int l = tid >> 2, j = tid & 3;
+            const int row = this_tile * 16 + (l >> 2) + (j >= 2 ? 8 : 0), n = (l & 3) * 2 + (j & 1);
+            if (row < rows && n < B) {
+                v += bias ? bf16_bits_to_float(bias[row]) : 0.f;
+                float* dst = out + (size_t)n * rows + row;
+                *dst = accumulate ? *dst + v : v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// K/V cache element (sequence b, kv head h, position p, dimension d), bf16:
+// cache[((b * nkv + h) * ctx + p) * 64 + d] - positions of one head are contiguous.
+
+// YaRN rotary embedding on q and k (rotate-half pairing: element i pairs with i + D/2) and
+// append of k, v to the cache.  qkv fp32 [B, (nq + 2*nkv) * D]; cos/sin are computed from
+// inv_freq[D/2] (fp32) and the token position; `mscale` multiplies cos and sin.  q is rotated
+// in place; k (rotated) and v are written as bf16 at the token's cache position.
+// One CTA per (head or value head, sequence).
+__global__ void __launch_bounds__(64) rope_cache_kernel(float* __restrict__ qkv, const float* __restrict__ inv_freq,
+                                                        const int32_t* __restrict__ pos, int nq, int nkv, float mscale, int ctx,
+                                                        uint16_t* __restrict__ kcache, uint16_t* __restrict__ vcache) {
+    constexpr int D = 64, half = 32;
+    const int head = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
+    const int p = pos[b];
+    float* hrow = qkv + ((size_t)b * (nq + 2 * nkv) + head) * D;
+    if (head >= nq + nkv) {  // value head: plain copy into the cache
+        vcache[(((size_t)b * nkv + (head - nq - nkv)) * ctx + p) * D + j] = f32_to_bf16_rn(hrow[j]);
+        return;
+    }
+    if (j >= half) return;
+    float sn, cs;
+    sincosf((float)p * inv_freq[j], &sn, &cs);
+    sn *= mscale;
+    cs *= mscale;
+    const float a = hrow[j], bb = hrow[j + half];
+    const float r0 = a * cs - bb * sn, r1 = bb * cs + a * sn;
+    if (head < nq) {
+        hrow[j] = r0;
+        hrow[j + half] = r1;
+    } else {
+        uint16_t* dst = kcache + (((size_t)b * nkv + (head - nq)) * ctx + p) * D;
+        dst[j] = f32_to_bf16_rn(r0);
+        dst[j + half] = f32_to_bf16_rn(r1);
+    }
+}
+
+// dst cache [batch][nkv][ctx][64] <- src [batch][n_pos][nkv][64] for positions < n_pos (16-byte vectors).
+__global__ void kv_load_kernel(const uint4* __restrict__ src, int batch, int n_pos, int nkv, int ctx, uint4* __restrict__ dst) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over batch * n_pos * nkv * 8
+    if (i >= (size_t)batch * n_pos * nkv * 8) return;
+    const int v = (int)(i % 8), h = (int)((i / 8) % nkv);
+    const size_t bp = i / 8 / nkv;
+    const int p = (int)(bp % n_pos), b = (int)(bp / n_pos);
+    dst[(((size_t)b * nkv + h) * ctx + p) * 8 + v] = src[i];
+}
+
+constexpr int kAttnChunk = 256;  // cache positions per CTA of attn_partial_kernel
+
+// Grouped-query attention of one new token per sequence over its cache.  One CTA per
+// (kv head, sequence, chunk of 256 positions); the G = nq/nkv query heads of the group share
+// every K/V load.  The range lo..p (lo = max(0, p - window + 1) when window > 0) is cut into
+// chunks from lo; a CTA whose chunk is empty writes a neutral partial.  Each CTA writes an
+// unnormalised partial (chunk maximum m, sum l, accumulator) and attn_merge_kernel folds the
+// chunks together with the head's sink logit, which enters the softmax denominator only.
+// Scores are q.k * scale.  D == 64, G <= 8, 256 threads.
+//   phase 1: thread i scores position i of the chunk against all G heads (q broadcast from
+//            shared memory, the 128-byte key row in registers);
+//   softmax: chunk maximum and sum per head by shuffles + shared memory, probabilities to smem;
+//   phase 2: warp w accumulates positions 32w..32w+31, lane = two of the 64 value dimensions
+//            (128-byte coalesced value rows), then the 8 warps are summed in fixed order.
+template <int G>
+__global__ void __launch_bounds__(256) attn_partial_kernel(const float* __restrict__ qkv, const uint16_t* __restrict__ kcache,
+                                                           const uint16_t* __restrict__ vcache, const int32_t* __restrict__ pos,
+                                                           int nq, int nkv, int ctx, int window, float scale, int splits,
+                                                           float* __restrict__ part /* [B][nq][splits][66] */) {
+    constexpr int D = 64;
+    __shared__ __align__(16) float qs[G][D];
+    __shared__ float ps[G][kAttnChunk];
+    __shared__ float wm[8][G], wl[8][G];
+    __shared__ float red[8][G][D];
+    const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int p = pos[b];
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int s0 = lo + sp * kAttnChunk, s1 = min(p + 1, s0 + kAttnChunk);
+    float* dst = part + (((size_t)b * nq + kvh * G) * splits + sp) * (D + 2);
+    if (s0 >= s1) {  // empty chunk (uniform over the CTA)
+        for (int i = tid; i < G * (D + 2); i += 256) {
+            const int g = i / (D + 2), c = i % (D + 2);
+            dst[(size_t)g * splits * (D + 2) + c] = c == 0 ? -INFINITY : 0.f;
+        }
+        return;
+    }
+    const float* qrow = qkv + (size_t)b * (nq + 2 * nkv) * D + (size_t)kvh * G * D;
+    for (int i = tid; i < G * D; i += 256) qs[i / D][i % D] = qrow[i] * scale;
+    const size_t head_base = ((size_t)b * nkv + kvh) * ctx;
+    const bool valid = s0 + tid < s1;
+    uint4 kr[8];
+    if (valid) {
+        const uint4* krow = reinterpret_cast<const uint4*>(kcache + (head_base + s0 + tid) * D);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kr[j] = __ldg(krow + j);
+    }
+    __syncthreads();
+    float s[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) s[g] = 0.f;
+    if (valid) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t w4[4] = {kr[j].x, kr[j].y, kr[j].z, kr[j].w};
+            float kf[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                kf[2 * i] = __uint_as_float(w4[i] << 16);
+                kf[2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float4 qa = *reinterpret_cast<const float4*>(&qs[g][j * 8]);
+                const float4 qb = *reinterpret_cast<const float4*>(&qs[g][j * 8 + 4]);
+                s[g] = fmaf(kf[0], qa.x, s[g]); s[g] = fmaf(kf[1], qa.y, s[g]);
+                s[g] = fmaf(kf[2], qa.z, s[g]); s[g] = fmaf(kf[3], qa.w, s[g]);
+                s[g] = fmaf(kf[4], qb.x, s[g]); s[g] = fmaf(kf[5], qb.y, s[g]);
+                s[g] = fmaf(kf[6], qb.z, s[g]); s[g] = fmaf(kf[7], qb.w, s[g]);
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float m = valid ? s[g] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) wm[warp][g] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float m = wm[0][g];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, wm[w][g]);
+        const float pr = valid ? __expf(s[g] - m) : 0.f;
+        ps[g][tid] = pr;
+        float l = pr;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) wl[warp][g] = l;
+        s[g] = m;  // keep the chunk maximum
+    }
+    __syncthreads();
+    float a0[G], a1[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) a0[g] = a1[g] = 0.f;
+    const int n_here = min(32, s1 - (s0 + warp * 32));  // positions of this warp (may be <= 0)
+    const uint32_t* vbase = reinterpret_cast<const uint32_t*>(vcache + (head_base + s0 + warp * 32) * D) + lane;
+    for (int i0 = 0; i0 < n_here; i0 += 4) {
+        uint32_t vv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) vv[u] = i0 + u < n_here ? __ldg(vbase + (size_t)(i0 + u) * (D / 2)) : 0u;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i0 + u < n_here) {
+                const float v0 = __uint_as_float(vv[u] << 16), v1 = __uint_as_float(vv[u] & 0xffff0000u);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pr = ps[g][warp * 32 + i0 + u];
+                    a0[g] = fmaf(pr, v0, a0[g]);
+                    a1[g] = fmaf(pr, v1, a1[g]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) *reinterpret_cast<float2*>(&red[warp][g][2 * lane]) = make_float2(a0[g], a1[g]);
+    __syncthreads();
+    for (int i = tid; i < G * D; i += 256) {
+        const int g = i / D, d = i % D;
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) acc += red[w][g][d];
+        float* o = dst + (size_t)g * splits * (D + 2);
+        o[2 + d] = acc;
+        if (d == 0) {
+            float l = 0.f, m = wm[0][g];
+#pragma unroll
+            for (int w = 0; w < 8; ++w) { l += wl[w][g]; m = fmaxf(m, wm[w][g]); }
+            o[0] = m;
+            o[1] = l;
+        }
+    }
+}
+
+// out[b, head*64 + d] = bf16( sum_splits acc*exp(m - M) / (sum_splits l*exp(m - M) + exp(sink - M)) ).
+__global__ void attn_merge_kernel(const float* __restrict__ part, const uint16_t* __restrict__ sinks, int nq, int splits,
+                                  uint16_t* __restrict__ out) {
+    constexpr int D = 64;
+    const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const float* src = part + ((size_t)b * nq + head) * splits * (D + 2);
+    const float sink = bf16_bits_to_float(sinks[head]);
+    float M = sink;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, src[s * (D + 2)]);
+    float den = __expf(sink - M), acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = src[s * (D + 2)];
+        const float c = m == -INFINITY ? 0.f : __expf(m - M);
+        den += src[s * (D + 2) + 1] * c;
+        acc += src[s * (D + 2) + 2 + d] * c;
+    }
+    out[((size_t)b * nq + head) * D + d] = f32_to_bf16_rn(acc / den);
+}
+
+// x += y (residual add of the MoE output), n elements.
+__global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += y[i];
+}
+
+// next[b] = argmax_v logits[b, v], lowest index among equals.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int V, int32_t* __restrict__ next) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)b * V;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < V; i += 1024) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((tid & 31) == 0) { sv[tid >> 5] = best; si[tid >> 5] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < 32; ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        next[b] = bi;
+    }
+}
+
+}  // namespace neon

@@ -17,10 +17,10 @@ def lib():
     return _lib.load()
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "neon_moe.h")).read()
+def declared_symbols(header="neon_moe.h", prefix="neon_moe_"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(neon_moe_[a-z_0-9]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(" + prefix + r"[a-z_0-9]+)\s*\(", text)))
 
 
 def test_exports_every_declared_symbol(lib):
@@ -29,6 +29,23 @@ def test_exports_every_declared_symbol(lib):
     for n in names:
         assert hasattr(lib, n), f"{n} declared in neon_moe.h but not exported"
     assert set(names) == set(_lib.SIGNATURES), "python binding table out of sync with the header"
+
+
+def test_exports_every_declared_decoder_symbol(lib):
+    names = declared_symbols("neon_decoder.h", "neon_decoder_")
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in neon_decoder.h but not exported"
+    assert set(names) == set(_lib.DECODER_SIGNATURES), "python binding table out of sync with the header"
+
+
+def test_decoder_create_rejects_bad_config(lib):
+    h = ctypes.c_void_p()
+    cfg = _lib.NeonDecoderConfig(1, 128, 8, 2, 32, 1000, 2, 64, 0, 150000.0, 32.0, 4096.0, 32.0, 1.0, 1e-5,
+                                 64, 8, 4, 7.0, 1.702, 0)  # head_dim 32 is not supported
+    assert lib.neon_decoder_create(ctypes.byref(cfg), ctypes.byref(h)) == 1
+    assert b"head_dim" in lib.neon_decoder_last_error(None)
+    assert lib.neon_decoder_step(None, None, None, 1, None, None, None) == 1
 
 
 def test_version(lib):

@@ -23,7 +23,8 @@
  *     orig_ctx as in the YaRN paper; cos and sin are multiplied by 0.1*ln(factor) + 1.
  *   - Attention scores are q.k/8; the softmax denominator includes exp(sink[head]); layers with
  *     even index attend to the last `window` positions only, odd layers to the whole cache.
- *   - K/V cache per layer (internal): bf16 [max_batch][n_kv_heads][max_ctx][64].
+ *   - K/V cache per layer (internal): keys bf16 [max_batch][n_kv_heads][max_ctx][64], values
+ *     transposed [max_batch][n_kv_heads][64][max_ctx].
  *   - The MoE of a layer receives the bf16 normalised activations; its config is
  *     {hidden, inter, n_experts, top_k, swiglu_limit, swiglu_alpha} (neon_moe.h).
  *
@@ -50,7 +51,7 @@ typedef struct neon_decoder_config {
     int head_dim;        /* 64 (only value supported)                                */
     int vocab;           /* 201088                                                   */
     int max_batch;       /* sequences per step, <= 8                                 */
-    int max_ctx;         /* cache positions per sequence (4096)                      */
+    int max_ctx;         /* cache positions per sequence (4096), multiple of 8       */
     int window;          /* sliding window of even layers (128); 0 = none anywhere   */
     float rope_theta;    /* 150000                                                   */
     float rope_factor;   /* 32 (1 = plain rotary embedding)                          */

@@ -149,8 +149,10 @@ __global__ void __launch_bounds__(256, 3) gemv_mma_kernel(const uint16_t* __rest
     }
 }
 
-// K/V cache element (sequence b, kv head h, position p, dimension d), bf16:
-// cache[((b * nkv + h) * ctx + p) * 64 + d] - positions of one head are contiguous.
+// K/V cache of one layer, bf16.  Keys:   kcache[((b * nkv + h) * ctx + p) * 64 + d]  (positions of
+// a head contiguous, one 128-byte row each).  Values are kept TRANSPOSED: vcache[((b * nkv + h) * 64
+// + d) * ctx + p], so that eight consecutive positions of one dimension are one 16-byte load, which
+// is what the tensor-core P.V product wants as its B operand.  ctx % 8 == 0.
 
 // YaRN rotary embedding on q and k (rotate-half pairing: element i pairs with i + D/2) and
 // append of k, v to the cache.  qkv fp32 [B, (nq + 2*nkv) * D]; cos/sin are computed from
@@ -164,8 +166,8 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(float* __restrict__ qkv,
     const int head = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
     const int p = pos[b];
     float* hrow = qkv + ((size_t)b * (nq + 2 * nkv) + head) * D;
-    if (head >= nq + nkv) {  // value head: plain copy into the cache
-        vcache[(((size_t)b * nkv + (head - nq - nkv)) * ctx + p) * D + j] = f32_to_bf16_rn(hrow[j]);
+    if (head >= nq + nkv) {  // value head: one element per dimension row of the transposed cache
+        vcache[(((size_t)b * nkv + (head - nq - nkv)) * D + j) * ctx + p] = f32_to_bf16_rn(hrow[j]);
         return;
     }
     if (j >= half) return;
@@ -185,8 +187,8 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(float* __restrict__ qkv,
     }
 }
 
-// dst cache [batch][nkv][ctx][64] <- src [batch][n_pos][nkv][64] for positions < n_pos (16-byte vectors).
-__global__ void kv_load_kernel(const uint4* __restrict__ src, int batch, int n_pos, int nkv, int ctx, uint4* __restrict__ dst) {
+// Key cache [batch][nkv][ctx][64] <- src [batch][n_pos][nkv][64] for positions < n_pos (16-byte vectors).
+__global__ void k_load_kernel(const uint4* __restrict__ src, int batch, int n_pos, int nkv, int ctx, uint4* __restrict__ dst) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over batch * n_pos * nkv * 8
     if (i >= (size_t)batch * n_pos * nkv * 8) return;
     const int v = (int)(i % 8), h = (int)((i / 8) % nkv);
@@ -195,138 +197,173 @@ __global__ void kv_load_kernel(const uint4* __restrict__ src, int batch, int n_p
     dst[(((size_t)b * nkv + h) * ctx + p) * 8 + v] = src[i];
 }
 
+// Value cache [batch][nkv][64][ctx] <- src [batch][n_pos][nkv][64]: one thread per element,
+// consecutive threads write consecutive positions.
+__global__ void v_load_kernel(const uint16_t* __restrict__ src, int batch, int n_pos, int nkv, int ctx, uint16_t* __restrict__ dst) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over batch * nkv * 64 * n_pos
+    if (i >= (size_t)batch * nkv * 64 * n_pos) return;
+    const int p = (int)(i % n_pos), d = (int)((i / n_pos) % 64);
+    const size_t bh = i / n_pos / 64;
+    const int h = (int)(bh % nkv), b = (int)(bh / nkv);
+    dst[(((size_t)b * nkv + h) * 64 + d) * ctx + p] = src[(((size_t)b * n_pos + p) * nkv + h) * 64 + d];
+}
+
 constexpr int kAttnChunk = 256;  // cache positions per CTA of attn_partial_kernel
 
-// Grouped-query attention of one new token per sequence over its cache.  One CTA per
-// (kv head, sequence, chunk of 256 positions); the G = nq/nkv query heads of the group share
-// every K/V load.  The range lo..p (lo = max(0, p - window + 1) when window > 0) is cut into
-// chunks from lo; a CTA whose chunk is empty writes a neutral partial.  Each CTA writes an
-// unnormalised partial (chunk maximum m, sum l, accumulator) and attn_merge_kernel folds the
-// chunks together with the head's sink logit, which enters the softmax denominator only.
-// Scores are q.k * scale.  D == 64, G <= 8, 256 threads.
-//   phase 1: thread i scores position i of the chunk against all G heads (q broadcast from
-//            shared memory, the 128-byte key row in registers);
-//   softmax: chunk maximum and sum per head by shuffles + shared memory, probabilities to smem;
-//   phase 2: warp w accumulates positions 32w..32w+31, lane = two of the 64 value dimensions
-//            (128-byte coalesced value rows), then the 8 warps are summed in fixed order.
+// fp32 pair -> bf16x2 "high" word and the bf16x2 of what is left (x ~= hi + lo to ~2^-17).
+__device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const uint16_t h0 = f32_to_bf16_rn(x0), h1 = f32_to_bf16_rn(x1);
+    hi = (uint32_t)h0 | ((uint32_t)h1 << 16);
+    lo = (uint32_t)f32_to_bf16_rn(x0 - bf16_bits_to_float(h0)) | ((uint32_t)f32_to_bf16_rn(x1 - bf16_bits_to_float(h1)) << 16);
+}
+
+// Grouped-query attention of one new token per sequence over its cache, on mma.sync
+// m16n8k16.  One CTA per (kv head, sequence, chunk of 256 positions); the G = nq/nkv <= 8
+// query heads of the group are rows 0..G-1 of the 16-row tiles (the rest is zero), so every
+// K/V byte is loaded once for all of them.  The range lo..p (lo = max(0, p - window + 1) when
+// window > 0) is cut into chunks from lo rounded down to a multiple of 8; positions outside
+// lo..p are masked.  Each CTA writes an unnormalised partial (chunk maximum m, sum l,
+// accumulator) per head and attn_merge_kernel folds the chunks together with the head's sink
+// logit, which enters the softmax denominator only.  Scores are q.k * scale.
+// Warp w owns 32 positions.  Scores: four n-tiles of 8 positions, position = 4*n + tile, so
+// that thread (g, t) ends up with the probabilities of positions 8t..8t+7 - exactly the k
+// slots it feeds to the P.V mma's, whose B operand is one 16-byte load (8 positions of one
+// dimension) from the transposed value cache.  The sums over dimensions / positions do not
+// depend on the mma slot order, so each 16-byte load feeds two mma's.  q and the
+// probabilities enter as hi + lo bf16 pairs (two mma's each), which keeps fp32-grade accuracy.
 template <int G>
-__global__ void __launch_bounds__(256) attn_partial_kernel(const float* __restrict__ qkv, const uint16_t* __restrict__ kcache,
-                                                           const uint16_t* __restrict__ vcache, const int32_t* __restrict__ pos,
-                                                           int nq, int nkv, int ctx, int window, float scale, int splits,
-                                                           float* __restrict__ part /* [B][nq][splits][66] */) {
+__global__ void __launch_bounds__(256, 2) attn_partial_kernel(const float* __restrict__ qkv, const uint16_t* __restrict__ kcache,
+                                                              const uint16_t* __restrict__ vcache, const int32_t* __restrict__ pos,
+                                                              int nq, int nkv, int ctx, int window, float scale, int splits,
+                                                              float* __restrict__ part /* [B][nq][splits][66] */) {
     constexpr int D = 64;
-    __shared__ __align__(16) float qs[G][D];
-    __shared__ float ps[G][kAttnChunk];
-    __shared__ float wm[8][G], wl[8][G];
-    __shared__ float red[8][G][D];
+    __shared__ float wm[8][8], wl[8][8];
+    __shared__ __align__(16) float red[8][8][D];
     const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int p = pos[b];
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int s0 = lo + sp * kAttnChunk, s1 = min(p + 1, s0 + kAttnChunk);
+    const int s0 = (lo & ~7) + sp * kAttnChunk;
     float* dst = part + (((size_t)b * nq + kvh * G) * splits + sp) * (D + 2);
-    if (s0 >= s1) {  // empty chunk (uniform over the CTA)
+    if (s0 > p) {  // empty chunk (uniform over the CTA)
         for (int i = tid; i < G * (D + 2); i += 256) {
-            const int g = i / (D + 2), c = i % (D + 2);
-            dst[(size_t)g * splits * (D + 2) + c] = c == 0 ? -INFINITY : 0.f;
+            const int gg = i / (D + 2), c = i % (D + 2);
+            dst[(size_t)gg * splits * (D + 2) + c] = c == 0 ? -INFINITY : 0.f;
         }
         return;
     }
-    const float* qrow = qkv + (size_t)b * (nq + 2 * nkv) * D + (size_t)kvh * G * D;
-    for (int i = tid; i < G * D; i += 256) qs[i / D][i % D] = qrow[i] * scale;
-    const size_t head_base = ((size_t)b * nkv + kvh) * ctx;
-    const bool valid = s0 + tid < s1;
-    uint4 kr[8];
-    if (valid) {
-        const uint4* krow = reinterpret_cast<const uint4*>(kcache + (head_base + s0 + tid) * D);
+    const int wbase = s0 + warp * 32;  // first position of this warp (multiple of 8)
+    const size_t head = (size_t)b * nkv + kvh;
+    // keys: tile j, row n = g -> position wbase + 4g + j; two 16-byte halves of dims [8t, 8t+8) and [32+8t, ..)
+    uint4 kr[4][2];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) kr[j] = __ldg(krow + j);
-    }
-    __syncthreads();
-    float s[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) s[g] = 0.f;
-    if (valid) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t w4[4] = {kr[j].x, kr[j].y, kr[j].z, kr[j].w};
-            float kf[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                kf[2 * i] = __uint_as_float(w4[i] << 16);
-                kf[2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float4 qa = *reinterpret_cast<const float4*>(&qs[g][j * 8]);
-                const float4 qb = *reinterpret_cast<const float4*>(&qs[g][j * 8 + 4]);
-                s[g] = fmaf(kf[0], qa.x, s[g]); s[g] = fmaf(kf[1], qa.y, s[g]);
-                s[g] = fmaf(kf[2], qa.z, s[g]); s[g] = fmaf(kf[3], qa.w, s[g]);
-                s[g] = fmaf(kf[4], qb.x, s[g]); s[g] = fmaf(kf[5], qb.y, s[g]);
-                s[g] = fmaf(kf[6], qb.z, s[g]); s[g] = fmaf(kf[7], qb.w, s[g]);
-            }
+    for (int j = 0; j < 4; ++j) {
+        const int kp = wbase + 4 * g + j;
+        if (kp < ctx && wbase <= p) {
+            const uint4* row = reinterpret_cast<const uint4*>(kcache + (head * ctx + kp) * D);
+            kr[j][0] = __ldg(row + t);
+            kr[j][1] = __ldg(row + 4 + t);
+        } else {
+            kr[j][0] = kr[j][1] = make_uint4(0, 0, 0, 0);
         }
     }
+    // q of head g (rows >= G are zero), scaled, as hi/lo bf16 pairs in the same slot order as the key loads
+    uint32_t qh[2][4], ql[2][4];
+    {
+        const float* qrow = qkv + (size_t)b * (nq + 2 * nkv) * D + (size_t)(kvh * G + min(g, G - 1)) * D;
+        const float on = g < G ? scale : 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        float m = valid ? s[g] : -INFINITY;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) wm[warp][g] = m;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        float m = wm[0][g];
-#pragma unroll
-        for (int w = 1; w < 8; ++w) m = fmaxf(m, wm[w][g]);
-        const float pr = valid ? __expf(s[g] - m) : 0.f;
-        ps[g][tid] = pr;
-        float l = pr;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        if (lane == 0) wl[warp][g] = l;
-        s[g] = m;  // keep the chunk maximum
-    }
-    __syncthreads();
-    float a0[G], a1[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) a0[g] = a1[g] = 0.f;
-    const int n_here = min(32, s1 - (s0 + warp * 32));  // positions of this warp (may be <= 0)
-    const uint32_t* vbase = reinterpret_cast<const uint32_t*>(vcache + (head_base + s0 + warp * 32) * D) + lane;
-    for (int i0 = 0; i0 < n_here; i0 += 4) {
-        uint32_t vv[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) vv[u] = i0 + u < n_here ? __ldg(vbase + (size_t)(i0 + u) * (D / 2)) : 0u;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (i0 + u < n_here) {
-                const float v0 = __uint_as_float(vv[u] << 16), v1 = __uint_as_float(vv[u] & 0xffff0000u);
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const float pr = ps[g][warp * 32 + i0 + u];
-                    a0[g] = fmaf(pr, v0, a0[g]);
-                    a1[g] = fmaf(pr, v1, a1[g]);
-                }
-            }
+        for (int i = 0; i < 2; ++i) {
+            const float4 u = *reinterpret_cast<const float4*>(qrow + i * 32 + t * 8);
+            const float4 v = *reinterpret_cast<const float4*>(qrow + i * 32 + t * 8 + 4);
+            split_bf16x2(u.x * on, u.y * on, qh[i][0], ql[i][0]);
+            split_bf16x2(u.z * on, u.w * on, qh[i][1], ql[i][1]);
+            split_bf16x2(v.x * on, v.y * on, qh[i][2], ql[i][2]);
+            split_bf16x2(v.z * on, v.w * on, qh[i][3], ql[i][3]);
         }
     }
+    // scores: c[j][0] = (head g, position 8t + j), c[j][1] = (head g, position 8t + 4 + j)
+    float sc[4][2];
 #pragma unroll
-    for (int g = 0; g < G; ++g) *reinterpret_cast<float2*>(&red[warp][g][2 * lane]) = make_float2(a0[g], a1[g]);
+    for (int j = 0; j < 4; ++j) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t kw[4] = {kr[j][i].x, kr[j][i].y, kr[j][i].z, kr[j][i].w};
+            const uint32_t ah0[4] = {qh[i][0], 0u, qh[i][1], 0u}, al0[4] = {ql[i][0], 0u, ql[i][1], 0u};
+            const uint32_t ah1[4] = {qh[i][2], 0u, qh[i][3], 0u}, al1[4] = {ql[i][2], 0u, ql[i][3], 0u};
+            mma_bf16_16816(c, ah0, kw[0], kw[1]);
+            mma_bf16_16816(c, al0, kw[0], kw[1]);
+            mma_bf16_16816(c, ah1, kw[2], kw[3]);
+            mma_bf16_16816(c, al1, kw[2], kw[3]);
+        }
+        // C columns 2t, 2t+1 are rows n = 2t, 2t+1 of the tile: positions 4*(2t) + j and 4*(2t+1) + j
+        const int p0 = wbase + 8 * t + j, p1 = p0 + 4;
+        sc[j][0] = (p0 >= lo && p0 <= p) ? c[0] : -INFINITY;
+        sc[j][1] = (p1 >= lo && p1 <= p) ? c[1] : -INFINITY;
+    }
+    // values: dimension tile dt, row n = g -> dimension 8*dt + g; positions wbase + 8t .. +7 in one load
+    uint4 vr[8];
+#pragma unroll
+    for (int dt = 0; dt < 8; ++dt) {
+        const int vp = wbase + 8 * t;
+        vr[dt] = (vp < ctx && wbase <= p) ? __ldg(reinterpret_cast<const uint4*>(vcache + (head * D + dt * 8 + g) * ctx + vp))
+                                          : make_uint4(0, 0, 0, 0);
+    }
+    // chunk maximum per head: over this thread's 8 positions, the 4 threads of a row, the 8 warps
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m = fmaxf(m, fmaxf(sc[j][0], sc[j][1]));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    if (t == 0) wm[warp][g] = m;
+    __syncthreads();
+    m = wm[0][g];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, wm[w][g]);
+    // probabilities (0 where masked, and everywhere when the head saw no valid position)
+    float pr[4][2], l = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        pr[j][0] = sc[j][0] == -INFINITY ? 0.f : __expf(sc[j][0] - m);
+        pr[j][1] = sc[j][1] == -INFINITY ? 0.f : __expf(sc[j][1] - m);
+        l += pr[j][0] + pr[j][1];
+    }
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (t == 0) wl[warp][g] = l;
+    // P as A operand: mma #0 covers positions 8t..8t+3 (a0 = +0,+1; a2 = +2,+3), mma #1 positions 8t+4..8t+7
+    uint32_t ph[2][2], pl[2][2];
+    split_bf16x2(pr[0][0], pr[1][0], ph[0][0], pl[0][0]);
+    split_bf16x2(pr[2][0], pr[3][0], ph[0][1], pl[0][1]);
+    split_bf16x2(pr[0][1], pr[1][1], ph[1][0], pl[1][0]);
+    split_bf16x2(pr[2][1], pr[3][1], ph[1][1], pl[1][1]);
+#pragma unroll
+    for (int dt = 0; dt < 8; ++dt) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t a0h[4] = {ph[0][0], 0u, ph[0][1], 0u}, a0l[4] = {pl[0][0], 0u, pl[0][1], 0u};
+        const uint32_t a1h[4] = {ph[1][0], 0u, ph[1][1], 0u}, a1l[4] = {pl[1][0], 0u, pl[1][1], 0u};
+        mma_bf16_16816(c, a0h, vr[dt].x, vr[dt].y);
+        mma_bf16_16816(c, a0l, vr[dt].x, vr[dt].y);
+        mma_bf16_16816(c, a1h, vr[dt].z, vr[dt].w);
+        mma_bf16_16816(c, a1l, vr[dt].z, vr[dt].w);
+        // c[0], c[1] = (head g, dimensions 8*dt + 2t, +1)
+        *reinterpret_cast<float2*>(&red[warp][g][dt * 8 + 2 * t]) = make_float2(c[0], c[1]);
+    }
     __syncthreads();
     for (int i = tid; i < G * D; i += 256) {
-        const int g = i / D, d = i % D;
+        const int gg = i / D, d = i % D;
         float acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) acc += red[w][g][d];
-        float* o = dst + (size_t)g * splits * (D + 2);
+        for (int w = 0; w < 8; ++w) acc += red[w][gg][d];
+        float* o = dst + (size_t)gg * splits * (D + 2);
         o[2 + d] = acc;
         if (d == 0) {
-            float l = 0.f, m = wm[0][g];
+            float ls = 0.f, mm = wm[0][gg];
 #pragma unroll
-            for (int w = 0; w < 8; ++w) { l += wl[w][g]; m = fmaxf(m, wm[w][g]); }
-            o[0] = m;
-            o[1] = l;
+            for (int w = 0; w < 8; ++w) { ls += wl[w][gg]; mm = fmaxf(mm, wm[w][gg]); }
+            o[0] = mm;
+            o[1] = ls;
         }
     }
 }

@@ -140,7 +140,8 @@ int launch_gemv(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias,
 int launch_attention(neon_decoder_handle* h, const LayerW& L, int layer, int B, const int32_t* pos, cudaStream_t st) {
     const auto& c = h->cfg;
     const int window = (c.window > 0 && layer % 2 == 0) ? c.window : 0;
-    const int span = window > 0 ? std::min(window, c.max_ctx) : c.max_ctx;
+    // chunks start at the window start rounded down to a multiple of 8
+    const int span = window > 0 ? std::min(window + 7, c.max_ctx) : c.max_ctx;
     const int splits = (span + kAttnChunk - 1) / kAttnChunk;
     const int G = c.n_q_heads / c.n_kv_heads;
     const dim3 grid(c.n_kv_heads, B, splits);
@@ -219,8 +220,8 @@ int neon_decoder_create(const neon_decoder_config* cfg, neon_decoder_handle** ou
     *out = nullptr;
     const auto& c = *cfg;
     if (c.head_dim != 64) return dfail(nullptr, NEON_MOE_EINVAL, "head_dim must be 64");
-    if (c.n_layers <= 0 || c.hidden <= 0 || c.hidden % 64 || c.vocab <= 0 || c.max_ctx <= 0)
-        return dfail(nullptr, NEON_MOE_EINVAL, "bad layer count, hidden size, vocabulary or context");
+    if (c.n_layers <= 0 || c.hidden <= 0 || c.hidden % 64 || c.vocab <= 0 || c.max_ctx <= 0 || c.max_ctx % 8)
+        return dfail(nullptr, NEON_MOE_EINVAL, "bad layer count, hidden size, vocabulary or context (a multiple of 8)");
     if (c.max_batch < 1 || c.max_batch > kDecMaxBatch) return dfail(nullptr, NEON_MOE_EINVAL, "max_batch must be 1..8");
     if (c.n_kv_heads <= 0 || c.n_q_heads % c.n_kv_heads) return dfail(nullptr, NEON_MOE_EINVAL, "n_q_heads %% n_kv_heads != 0");
     const int G = c.n_q_heads / c.n_kv_heads;
@@ -385,11 +386,10 @@ int neon_decoder_load_kv(neon_decoder_handle* h, int layer, const void* k, const
             ks = tmp;
             vs = static_cast<char*>(tmp) + bytes;
         }
-        const unsigned blocks = (unsigned)((vecs + 255) / 256);
-        kv_load_kernel<<<blocks, 256>>>(static_cast<const uint4*>(ks), batch, n_pos, c.n_kv_heads, c.max_ctx,
-                                        reinterpret_cast<uint4*>(L.kc));
-        kv_load_kernel<<<blocks, 256>>>(static_cast<const uint4*>(vs), batch, n_pos, c.n_kv_heads, c.max_ctx,
-                                        reinterpret_cast<uint4*>(L.vc));
+        k_load_kernel<<<(unsigned)((vecs + 255) / 256), 256>>>(static_cast<const uint4*>(ks), batch, n_pos, c.n_kv_heads,
+                                                               c.max_ctx, reinterpret_cast<uint4*>(L.kc));
+        v_load_kernel<<<(unsigned)((bytes / 2 + 255) / 256), 256>>>(static_cast<const uint16_t*>(vs), batch, n_pos, c.n_kv_heads,
+                                                                    c.max_ctx, L.vc);
         h->launches += 2;
         cudaError_t e = cudaDeviceSynchronize();
         if (tmp) cudaFree(tmp);

@@ -230,6 +230,9 @@ def run_decoder(args, local_rank):
     B, ctx = 8, 4096
     H = shape.hidden
     dec = DecoderSystem(shape, B, ctx, device=local_rank)
+    for opt in args.option:
+        name, value = opt.split("=")
+        dec.set_option(name, int(value))
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
 
@@ -337,6 +340,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library option to set before timing (e.g. pdl=0); for experiments")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -383,6 +388,9 @@ def main():
     batches, lb = make_batches(T, W, zipf, n_batches, base_stream=100 * rank)
     dev = torch.device("cuda", local_rank)
     layer = MoeLayerSystem(shape, W, max_tokens=T, device=local_rank, ep_rank=rank, ep_size=world)
+    for opt in args.option:
+        name, value = opt.split("=")
+        layer.set_option(name, int(value))
     if ep:
         ids = [MoeLayerSystem.ep_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)

@@ -112,7 +112,8 @@ int neon_decoder_step_host(neon_decoder_handle* h, const int32_t* tokens, const 
  * "moe_out" fp32 [B,H]; "logits" fp32 [B,vocab]; "inv_freq" fp32 [32]. */
 int neon_decoder_read(neon_decoder_handle* h, const char* name, void* dst, uint64_t bytes);
 
-/* Options: "use_graphs" (default 1), "stop_after_layer" (debug: run only the first n layers
+/* Options: "use_graphs" (default 1), "pdl" (programmatic dependent launch: bit 0 the
+ * GEMV kernels, bit 1 the others; default 1), "moe.<option>" (passed to every layer, see neon_moe.h), "stop_after_layer" (debug: run only the first n layers
  * and skip the head; 0 = all). */
 int neon_decoder_set_option(neon_decoder_handle* h, const char* name, int64_t value);
 

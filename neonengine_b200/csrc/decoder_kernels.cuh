@@ -4,6 +4,10 @@
 // per-head sink logits and an optional sliding window, residual adds, argmax.
 // All of them are HBM/L2 streaming work on CUDA cores; activations between them are fp32
 // (residual stream, q, attention partials) or bf16 (normalised activations, K/V cache).
+// Every kernel may be launched with programmatic stream serialization: it lets its successor
+// start launching at once (pdl_launch_dependents) and waits for its predecessor's results
+// (pdl_wait) before touching anything a predecessor writes; only loads of weights, which no
+// kernel writes, are issued ahead of the wait.
 #pragma once
 #include "moe_common.cuh"
 
@@ -16,40 +20,53 @@ __device__ __forceinline__ uint16_t f32_to_bf16_rn(float f) { return __bfloat16_
 // x[b, :] = embed[token[b], :] (bf16 -> fp32 residual stream).
 __global__ void embed_kernel(const uint16_t* __restrict__ embed, const int32_t* __restrict__ tokens, int H,
                              float* __restrict__ x) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x;
     const uint16_t* row = embed + (size_t)tokens[b] * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) x[(size_t)b * H + i] = bf16_bits_to_float(row[i]);
 }
 
 // x[b, :] += addend[b, :] (when addend != nullptr; x is written back), then
-// y[b, :] = bf16( x[b, :] * rsqrt(mean(x^2) + eps) * w[:] ), one CTA per token.  The sum of
-// squares is reduced in a fixed order (thread-strided partials, shuffle tree, warp 0).
-__global__ void __launch_bounds__(256) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ addend,
-                                                      const uint16_t* __restrict__ w, int H, float eps,
-                                                      uint16_t* __restrict__ y) {
-    __shared__ float part[8];
+// y[b, :] = bf16( x[b, :] * rsqrt(mean(x^2) + eps) * w[:] ).  One CTA of 1024 threads per token;
+// a thread keeps its (at most one) 4-element vector in registers between the two phases, so the
+// row is read once.  H % 4 == 0, H <= 4096.  The sum of squares is reduced in a fixed order.
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ addend,
+                                                       const uint16_t* __restrict__ w, int H, float eps,
+                                                       uint16_t* __restrict__ y) {
+    __shared__ float part[32];
     const int b = blockIdx.x, tid = threadIdx.x;
-    float* xr = x + (size_t)b * H;
-    float s = 0.f;
-    if (addend) {
-        const float* ar = addend + (size_t)b * H;
-        for (int i = tid; i < H; i += 256) {
-            const float v = xr[i] + ar[i];
-            xr[i] = v;
-            s = fmaf(v, v, s);
+    const bool have = tid * 4 < H;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint2 wv = make_uint2(0u, 0u);
+    pdl_launch_dependents();
+    if (have) wv = *reinterpret_cast<const uint2*>(w + tid * 4);
+    pdl_wait();
+    if (have) {
+        float4* xr = reinterpret_cast<float4*>(x + (size_t)b * H) + tid;
+        v = *xr;
+        if (addend) {
+            const float4 a = reinterpret_cast<const float4*>(addend + (size_t)b * H)[tid];
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            *xr = v;
         }
-    } else {
-        for (int i = tid; i < H; i += 256) s = fmaf(xr[i], xr[i], s);
     }
+    float s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if ((tid & 31) == 0) part[tid >> 5] = s;
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) tot += part[i];
+    for (int i = 0; i < 32; ++i) tot += part[i];
     const float r = rsqrtf(tot / (float)H + eps);
-    for (int i = tid; i < H; i += 256) y[(size_t)b * H + i] = f32_to_bf16_rn(xr[i] * r * bf16_bits_to_float(w[i]));
+    if (have) {
+        const uint32_t lo = (uint32_t)f32_to_bf16_rn(v.x * r * __uint_as_float(wv.x << 16)) |
+                            ((uint32_t)f32_to_bf16_rn(v.y * r * __uint_as_float(wv.x & 0xffff0000u)) << 16);
+        const uint32_t hi = (uint32_t)f32_to_bf16_rn(v.z * r * __uint_as_float(wv.y << 16)) |
+                            ((uint32_t)f32_to_bf16_rn(v.w * r * __uint_as_float(wv.y & 0xffff0000u)) << 16);
+        *reinterpret_cast<uint2*>(y + (size_t)b * H + tid * 4) = make_uint2(lo, hi);
+    }
 }
 
 // Padding (in bf16 elements) that makes a K-element activation row start 16 banks after the
@@ -65,11 +82,11 @@ __host__ __device__ inline int gemv_row_pad(int K) { return ((16 - (K / 2) % 32 
 // each thread feeds the 8 consecutive elements of one 16-byte load to two mma's and reads the
 // matching 16 bytes of x: no shuffles, no scalar loads.  K % 32 == 0.
 // accumulate != 0: out += result (residual add); otherwise out = result.
-__global__ void __launch_bounds__(256, 3) gemv_mma_kernel(const uint16_t* __restrict__ W, const uint16_t* __restrict__ bias,
+__global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const uint16_t* __restrict__ W, const uint16_t* __restrict__ bias,
                                                           const uint16_t* __restrict__ x, int B, int rows, int K,
                                                           int accumulate, float* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char gsm[];
-    constexpr int U = 3;  // k-blocks per warp in flight
+    constexpr int U = 6;  // k-blocks per warp and batch; two batches are in flight
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int xstride = K + gemv_row_pad(K);  // elements
     uint16_t* xs = reinterpret_cast<uint16_t*>(gsm);
@@ -91,15 +108,28 @@ __global__ void __launch_bounds__(256, 3) gemv_mma_kernel(const uint16_t* __rest
     int tile = blockIdx.x;
     uint4 wa[U], wb[U];
     const uint16_t *ra = nullptr, *rb = nullptr;
-    if (tile < n_tiles) {  // first weights are already in flight while x is staged
+    pdl_launch_dependents();
+    if (tile < n_tiles) {  // first weights go in flight before the predecessor has even finished
         ra = W + (size_t)min(tile * 16 + g, rows - 1) * K;
         rb = W + (size_t)min(tile * 16 + g + 8, rows - 1) * K;
         load_batch(wa, wb, ra, rb, warp);
     }
-    for (int i = tid; i < 8 * (K / 8); i += 256) {
-        const int b = i / (K / 8), c = i % (K / 8);
-        const uint4 v = b < B ? reinterpret_cast<const uint4*>(x)[(size_t)b * (K / 8) + c] : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(xs + (size_t)b * xstride + c * 8) = v;
+    pdl_wait();
+    {   // stage x: eight independent 16-byte loads per thread in flight, then the stores
+        const int nvec = K / 8, total = 8 * nvec;
+        for (int base = tid; base < total; base += 256 * 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * 256;
+                v[u] = (i < total && i / nvec < B) ? reinterpret_cast<const uint4*>(x)[i] : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * 256;
+                if (i < total) *reinterpret_cast<uint4*>(xs + (size_t)(i / nvec) * xstride + (i % nvec) * 8) = v[u];
+            }
+        }
     }
     __syncthreads();
     for (; tile < n_tiles; tile += gridDim.x) {
@@ -164,6 +194,8 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(float* __restrict__ qkv,
                                                         uint16_t* __restrict__ kcache, uint16_t* __restrict__ vcache) {
     constexpr int D = 64, half = 32;
     const int head = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int p = pos[b];
     float* hrow = qkv + ((size_t)b * (nq + 2 * nkv) + head) * D;
     if (head >= nq + nkv) {  // value head: one element per dimension row of the transposed cache
@@ -241,6 +273,8 @@ __global__ void __launch_bounds__(256, 2) attn_partial_kernel(const float* __res
     __shared__ __align__(16) float red[8][8][D];
     const int kvh = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    pdl_launch_dependents();
+    pdl_wait();
     const int p = pos[b];
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int s0 = (lo & ~7) + sp * kAttnChunk;
@@ -373,11 +407,15 @@ __global__ void attn_merge_kernel(const float* __restrict__ part, const uint16_t
                                   uint16_t* __restrict__ out) {
     constexpr int D = 64;
     const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* src = part + ((size_t)b * nq + head) * splits * (D + 2);
     const float sink = bf16_bits_to_float(sinks[head]);
     float M = sink;
+#pragma unroll 8
     for (int s = 0; s < splits; ++s) M = fmaxf(M, src[s * (D + 2)]);
     float den = __expf(sink - M), acc = 0.f;
+#pragma unroll 8
     for (int s = 0; s < splits; ++s) {
         const float m = src[s * (D + 2)];
         const float c = m == -INFINITY ? 0.f : __expf(m - M);
@@ -389,6 +427,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part, const uint16_t
 
 // x += y (residual add of the MoE output), n elements.
 __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += y[i];
 }
@@ -397,6 +437,8 @@ __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, i
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int V, int32_t* __restrict__ next) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)b * V;
     float best = -INFINITY;

@@ -40,6 +40,7 @@ struct neon_decoder_handle {
     float mscale = 1.f;
     int64_t launches = 0;
     int use_graphs = 1, stop_after = 0;
+    int pdl = 1;  // bit 0: GEMV launches, bit 1: the other kernels (both together measured slower)
     cudaStream_t own_stream = nullptr, last_stream = nullptr;
     // one cached graph
     struct {
@@ -116,10 +117,29 @@ void yarn_inv_freq(const neon_decoder_config& c, float* inv, float* mscale) {
     *mscale = factor > 1.0 ? (float)(0.1 * std::log(factor) + 1.0) : 1.f;
 }
 
+// Launch with programmatic stream serialization (option "pdl"): the kernel may be scheduled
+// while its predecessor drains; every kernel waits for its predecessor before it reads or writes
+// anything a predecessor touches.
+template <typename... KArgs, typename... Args>
+void launch_pdl(neon_decoder_handle* h, bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    h->launches++;
+}
+
 template <typename... KArgs, typename... Args>
 void launch(neon_decoder_handle* h, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    kernel<<<grid, block, smem, st>>>(args...);
-    h->launches++;
+    launch_pdl(h, (h->pdl & 2) != 0, kernel, grid, block, smem, st, args...);
 }
 
 int launch_gemv(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias, const uint16_t* x, int B, int rows, int K,
@@ -132,8 +152,8 @@ int launch_gemv(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias,
         DCU(h, cudaFuncSetAttribute(gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
         configured[h->cfg.device & 63] = true;
     }
-    const int grid = std::min((rows + 15) / 16, 148 * 3);
-    launch(h, gemv_mma_kernel, dim3(grid), dim3(256), smem, st, W, bias, x, B, rows, K, accumulate, out);
+    const int grid = std::min((rows + 15) / 16, 148 * 2);
+    launch_pdl(h, (h->pdl & 1) != 0, gemv_mma_kernel, dim3(grid), dim3(256), smem, st, W, bias, x, B, rows, K, accumulate, out);
     return NEON_MOE_OK;
 }
 
@@ -170,7 +190,7 @@ int step_eager(neon_decoder_handle* h, const int32_t* tokens, const int32_t* pos
     const float* pending = nullptr;  // MoE output of the previous layer, added by the next RMSNorm kernel
     for (int l = 0; l < n_layers; ++l) {
         LayerW& L = h->layers[l];
-        launch(h, rmsnorm_kernel, dim3(B), dim3(256), 0, st, h->x, pending, (const uint16_t*)L.ln1, H, c.rms_eps, h->xn);
+        launch(h, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, pending, (const uint16_t*)L.ln1, H, c.rms_eps, h->xn);
         int rc = launch_gemv(h, L.wqkv, L.bqkv, h->xn, B, QKV, H, 0, h->qkv, st);
         if (rc) return rc;
         launch(h, rope_cache_kernel, dim3(c.n_q_heads + 2 * c.n_kv_heads, B), dim3(64), 0, st, h->qkv,
@@ -179,7 +199,7 @@ int step_eager(neon_decoder_handle* h, const int32_t* tokens, const int32_t* pos
         if (rc) return rc;
         rc = launch_gemv(h, L.wo, L.bo, h->attn, B, H, QD, 1, h->x, st);
         if (rc) return rc;
-        launch(h, rmsnorm_kernel, dim3(B), dim3(256), 0, st, h->x, (const float*)nullptr, (const uint16_t*)L.ln2, H, c.rms_eps,
+        launch(h, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, (const float*)nullptr, (const uint16_t*)L.ln2, H, c.rms_eps,
                h->xn2);
         const int64_t before = neon_moe_launch_count(L.moe);
         rc = neon_moe_forward(L.moe, h->xn2, B, nullptr, h->moe_out, nullptr, nullptr, st);
@@ -191,7 +211,7 @@ int step_eager(neon_decoder_handle* h, const int32_t* tokens, const int32_t* pos
         launch(h, add_kernel, dim3((B * H + 255) / 256), dim3(256), 0, st, h->x, pending, B * H);
         return NEON_MOE_OK;
     }
-    launch(h, rmsnorm_kernel, dim3(B), dim3(256), 0, st, h->x, pending, (const uint16_t*)h->final_norm, H, c.rms_eps, h->xn);
+    launch(h, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, pending, (const uint16_t*)h->final_norm, H, c.rms_eps, h->xn);
     float* lg = logits ? logits : h->logits;
     int rc = launch_gemv(h, h->unembed, nullptr, h->xn, B, c.vocab, H, 0, lg, st);
     if (rc) return rc;
@@ -488,6 +508,13 @@ int neon_decoder_set_option(neon_decoder_handle* h, const char* name, int64_t va
     if (!h || !name) return NEON_MOE_EINVAL;
     drop_graph(h);
     if (!strcmp(name, "use_graphs")) h->use_graphs = (int)value;
+    else if (!strcmp(name, "pdl")) h->pdl = (int)value;
+    else if (!strncmp(name, "moe.", 4)) {  // pass an option on to every layer's MoE handle
+        for (auto& L : h->layers) {
+            int rc = neon_moe_set_option(L.moe, name + 4, value);
+            if (rc) return dfail(h, rc, "MoE option: %s", neon_moe_last_error(L.moe));
+        }
+    }
     else if (!strcmp(name, "stop_after_layer")) h->stop_after = (int)value;
     else return dfail(h, NEON_MOE_EINVAL, "unknown option '%s'", name);
     return NEON_MOE_OK;

@@ -227,6 +227,8 @@ def run_decoder(args, local_rank):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     dev = torch.device("cuda", local_rank)
     shape = DecoderShape()
+    if args.decoder_layers:
+        shape.n_layers = args.decoder_layers
     B, ctx = 8, 4096
     H = shape.hidden
     dec = DecoderSystem(shape, B, ctx, device=local_rank)
@@ -310,6 +312,7 @@ def run_decoder(args, local_rank):
             "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "cfg3", "description": WORKLOADS["cfg3"][3], "batch": B, "cache_tokens": ctx,
+                       "layers": shape.n_layers,
                        "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (the stack does not shard)",
                        "l2_policy": f"each step streams {step_bytes / 1e9:.1f} GB of weights and cache, far beyond the 126 MB L2; "
                                     "the tokens of a step are the previous step's argmax"},
@@ -340,6 +343,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decoder-layers", type=int, default=None,
+                    help="cfg3 only: run fewer than 24 layers (for small profiler captures; not a bench result)")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="library option to set before timing (e.g. pdl=0); for experiments")
     args = ap.parse_args()

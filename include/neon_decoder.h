@@ -112,8 +112,8 @@ int neon_decoder_step_host(neon_decoder_handle* h, const int32_t* tokens, const 
  * "moe_out" fp32 [B,H]; "logits" fp32 [B,vocab]; "inv_freq" fp32 [32]. */
 int neon_decoder_read(neon_decoder_handle* h, const char* name, void* dst, uint64_t bytes);
 
-/* Options: "use_graphs" (default 1), "pdl" (programmatic dependent launch: bit 0 the
- * GEMV kernels, bit 1 the others; default 1), "moe.<option>" (passed to every layer, see neon_moe.h), "stop_after_layer" (debug: run only the first n layers
+/* Options: "use_graphs" (default 1), "pdl" (programmatic dependent launch, a bit per
+ * kernel kind: 1 GEMV, 2 RMSNorm, 4 rotary/cache, 8 attention, 16 merge, 32 others; default 29), "moe.<option>" (passed to every layer, see neon_moe.h), "stop_after_layer" (debug: run only the first n layers
  * and skip the head; 0 = all). */
 int neon_decoder_set_option(neon_decoder_handle* h, const char* name, int64_t value);
 

@@ -27,12 +27,13 @@ __global__ void embed_kernel(const uint16_t* __restrict__ embed, const int32_t* 
     for (int i = threadIdx.x; i < H; i += blockDim.x) x[(size_t)b * H + i] = bf16_bits_to_float(row[i]);
 }
 
-// x[b, :] += addend[b, :] (when addend != nullptr; x is written back), then
+// x[b, :] += sum_i addend[i * add_stride + b * H + :] for i < n_add (x is written back when
+// n_add > 0; the addends are added in order), then
 // y[b, :] = bf16( x[b, :] * rsqrt(mean(x^2) + eps) * w[:] ).  One CTA of 1024 threads per token;
 // a thread keeps its (at most one) 4-element vector in registers between the two phases, so the
 // row is read once.  H % 4 == 0, H <= 4096.  The sum of squares is reduced in a fixed order.
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ addend,
-                                                       const uint16_t* __restrict__ w, int H, float eps,
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ addend, int n_add,
+                                                       long long add_stride, const uint16_t* __restrict__ w, int H, float eps,
                                                        uint16_t* __restrict__ y) {
     __shared__ float part[32];
     const int b = blockIdx.x, tid = threadIdx.x;
@@ -45,9 +46,14 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, co
     if (have) {
         float4* xr = reinterpret_cast<float4*>(x + (size_t)b * H) + tid;
         v = *xr;
-        if (addend) {
-            const float4 a = reinterpret_cast<const float4*>(addend + (size_t)b * H)[tid];
-            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        if (n_add > 0) {
+            float4 a[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                a[i] = i < n_add ? reinterpret_cast<const float4*>(addend + (size_t)i * add_stride + (size_t)b * H)[tid]
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { v.x += a[i].x; v.y += a[i].y; v.z += a[i].z; v.w += a[i].w; }
             *xr = v;
         }
     }
@@ -179,6 +185,86 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const uint16_t* __rest
     }
 }
 
+constexpr int kGemvSplitU = 6;  // k-blocks per warp of gemv_mma_split_kernel (all loaded at once)
+
+// The same product for matrices with few rows, cut along K over gridDim.y CTAs per 16-row tile
+// so that enough CTAs exist to keep HBM busy: CTA (tile, ks) handles k-blocks
+// [ks * nkb / KS, (ks + 1) * nkb / KS) (nkb = K / 32, at most 8 * kGemvSplitU of them), loads all
+// of its weights up front (before it waits for its predecessor), stages only its slice of x,
+// and writes the partial result parts[ks][b][r]; part 0 carries the bias.  The consumer adds
+// the parts in order, which keeps the result independent of scheduling.
+__global__ void __launch_bounds__(256, 3) gemv_mma_split_kernel(const uint16_t* __restrict__ W, const uint16_t* __restrict__ bias,
+                                                                const uint16_t* __restrict__ x, int B, int rows, int K,
+                                                                float* __restrict__ parts, long long part_stride) {
+    extern __shared__ __align__(16) unsigned char gsm[];
+    constexpr int U = kGemvSplitU;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int nkb = K / 32, KS = gridDim.y, ks = blockIdx.y, tile = blockIdx.x;
+    const int kb_lo = ks * nkb / KS, kb_hi = (ks + 1) * nkb / KS, span = (kb_hi - kb_lo) * 32;  // elements of this slice
+    const int xstride = span + gemv_row_pad(span);
+    uint16_t* xs = reinterpret_cast<uint16_t*>(gsm);
+    float* red = reinterpret_cast<float*>(gsm + (size_t)8 * xstride * 2);  // [8 warps][128]
+    pdl_launch_dependents();
+    const uint16_t* ra = W + (size_t)min(tile * 16 + g, rows - 1) * K;
+    const uint16_t* rb = W + (size_t)min(tile * 16 + g + 8, rows - 1) * K;
+    uint4 wa[U], wb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int kb = kb_lo + warp + u * 8;
+        if (kb < kb_hi) {
+            wa[u] = ldg_stream(reinterpret_cast<const uint4*>(ra + kb * 32 + t * 8));
+            wb[u] = ldg_stream(reinterpret_cast<const uint4*>(rb + kb * 32 + t * 8));
+        } else {
+            wa[u] = wb[u] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    pdl_wait();
+    {
+        const int nvec = span / 8, total = 8 * nvec;
+        for (int base = tid; base < total; base += 256 * 4) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * 256;
+                v[u] = (i < total && i / nvec < B)
+                           ? reinterpret_cast<const uint4*>(x + (size_t)(i / nvec) * K + kb_lo * 32)[i % nvec]
+                           : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * 256;
+                if (i < total) *reinterpret_cast<uint4*>(xs + (size_t)(i / nvec) * xstride + (i % nvec) * 8) = v[u];
+            }
+        }
+    }
+    __syncthreads();
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int kb = warp + u * 8;  // relative to the slice
+        if (kb_lo + kb < kb_hi) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)g * xstride + kb * 32 + t * 8);
+            const uint32_t a0[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
+            const uint32_t a1[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+            mma_bf16_16816(c, a0, xv.x, xv.y);
+            mma_bf16_16816(c, a1, xv.z, xv.w);
+        }
+    }
+    *reinterpret_cast<float4*>(red + warp * 128 + lane * 4) = make_float4(c[0], c[1], c[2], c[3]);
+    __syncthreads();
+    if (tid < 128) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w * 128 + tid];
+        const int l = tid >> 2, j = tid & 3;
+        const int row = tile * 16 + (l >> 2) + (j >= 2 ? 8 : 0), n = (l & 3) * 2 + (j & 1);
+        if (row < rows && n < B) {
+            if (ks == 0 && bias) v += bf16_bits_to_float(bias[row]);
+            parts[(size_t)ks * part_stride + (size_t)n * rows + row] = v;
+        }
+    }
+}
+
 // K/V cache of one layer, bf16.  Keys:   kcache[((b * nkv + h) * ctx + p) * 64 + d]  (positions of
 // a head contiguous, one 128-byte row each).  Values are kept TRANSPOSED: vcache[((b * nkv + h) * 64
 // + d) * ctx + p], so that eight consecutive positions of one dimension are one 16-byte load, which
@@ -188,26 +274,34 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const uint16_t* __rest
 // append of k, v to the cache.  qkv fp32 [B, (nq + 2*nkv) * D]; cos/sin are computed from
 // inv_freq[D/2] (fp32) and the token position; `mscale` multiplies cos and sin.  q is rotated
 // in place; k (rotated) and v are written as bf16 at the token's cache position.
+// qkv arrives as n_parts partial results of the K-split projection (part i at qkv + i *
+// part_stride), which are added in order first; the rotated q lands in part 0.
 // One CTA per (head or value head, sequence).
-__global__ void __launch_bounds__(64) rope_cache_kernel(float* __restrict__ qkv, const float* __restrict__ inv_freq,
-                                                        const int32_t* __restrict__ pos, int nq, int nkv, float mscale, int ctx,
-                                                        uint16_t* __restrict__ kcache, uint16_t* __restrict__ vcache) {
+__global__ void __launch_bounds__(64) rope_cache_kernel(float* __restrict__ qkv, int n_parts, long long part_stride,
+                                                        const float* __restrict__ inv_freq, const int32_t* __restrict__ pos,
+                                                        int nq, int nkv, float mscale, int ctx, uint16_t* __restrict__ kcache,
+                                                        uint16_t* __restrict__ vcache) {
     constexpr int D = 64, half = 32;
     const int head = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     const int p = pos[b];
     float* hrow = qkv + ((size_t)b * (nq + 2 * nkv) + head) * D;
+    float mine = hrow[j];  // element j of the head, parts summed
+    for (int i = 1; i < n_parts; ++i) mine += hrow[(size_t)i * part_stride + j];
     if (head >= nq + nkv) {  // value head: one element per dimension row of the transposed cache
-        vcache[(((size_t)b * nkv + (head - nq - nkv)) * D + j) * ctx + p] = f32_to_bf16_rn(hrow[j]);
+        vcache[(((size_t)b * nkv + (head - nq - nkv)) * D + j) * ctx + p] = f32_to_bf16_rn(mine);
         return;
     }
+    __shared__ float hv[D];  // the head's 64 summed elements (the branch above is uniform over the CTA)
+    hv[j] = mine;
+    __syncthreads();
     if (j >= half) return;
     float sn, cs;
     sincosf((float)p * inv_freq[j], &sn, &cs);
     sn *= mscale;
     cs *= mscale;
-    const float a = hrow[j], bb = hrow[j + half];
+    const float a = hv[j], bb = hv[j + half];
     const float r0 = a * cs - bb * sn, r1 = bb * cs + a * sn;
     if (head < nq) {
         hrow[j] = r0;
@@ -264,7 +358,7 @@ __device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t& hi, u
 // depend on the mma slot order, so each 16-byte load feeds two mma's.  q and the
 // probabilities enter as hi + lo bf16 pairs (two mma's each), which keeps fp32-grade accuracy.
 template <int G>
-__global__ void __launch_bounds__(256, 2) attn_partial_kernel(const float* __restrict__ qkv, const uint16_t* __restrict__ kcache,
+__global__ void __launch_bounds__(256, 3) attn_partial_kernel(const float* __restrict__ qkv, const uint16_t* __restrict__ kcache,
                                                               const uint16_t* __restrict__ vcache, const int32_t* __restrict__ pos,
                                                               int nq, int nkv, int ctx, int window, float scale, int splits,
                                                               float* __restrict__ part /* [B][nq][splits][66] */) {
@@ -301,6 +395,14 @@ __global__ void __launch_bounds__(256, 2) attn_partial_kernel(const float* __res
             kr[j][0] = kr[j][1] = make_uint4(0, 0, 0, 0);
         }
     }
+    // values: dimension tile dt, row n = g -> dimension 8*dt + g; positions wbase + 8t .. +7 in one load
+    uint4 vr[8];
+#pragma unroll
+    for (int dt = 0; dt < 8; ++dt) {
+        const int vp = wbase + 8 * t;
+        vr[dt] = (vp < ctx && wbase <= p) ? __ldg(reinterpret_cast<const uint4*>(vcache + (head * D + dt * 8 + g) * ctx + vp))
+                                          : make_uint4(0, 0, 0, 0);
+    }
     // q of head g (rows >= G are zero), scaled, as hi/lo bf16 pairs in the same slot order as the key loads
     uint32_t qh[2][4], ql[2][4];
     {
@@ -335,14 +437,6 @@ __global__ void __launch_bounds__(256, 2) attn_partial_kernel(const float* __res
         const int p0 = wbase + 8 * t + j, p1 = p0 + 4;
         sc[j][0] = (p0 >= lo && p0 <= p) ? c[0] : -INFINITY;
         sc[j][1] = (p1 >= lo && p1 <= p) ? c[1] : -INFINITY;
-    }
-    // values: dimension tile dt, row n = g -> dimension 8*dt + g; positions wbase + 8t .. +7 in one load
-    uint4 vr[8];
-#pragma unroll
-    for (int dt = 0; dt < 8; ++dt) {
-        const int vp = wbase + 8 * t;
-        vr[dt] = (vp < ctx && wbase <= p) ? __ldg(reinterpret_cast<const uint4*>(vcache + (head * D + dt * 8 + g) * ctx + vp))
-                                          : make_uint4(0, 0, 0, 0);
     }
     // chunk maximum per head: over this thread's 8 positions, the 4 threads of a row, the 8 warps
     float m = -INFINITY;

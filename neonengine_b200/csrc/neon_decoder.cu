@@ -35,12 +35,14 @@ struct neon_decoder_handle {
     uint16_t *embed = nullptr, *unembed = nullptr, *final_norm = nullptr;
     bool has_embed = false;
     float *x = nullptr, *qkv = nullptr, *moe_out = nullptr, *logits = nullptr, *part = nullptr, *inv_freq = nullptr;
+    float* oproj = nullptr;  // K-split parts of the attention output projection
+    int qkv_split = 1, o_split = 1;
     uint16_t *xn = nullptr, *xn2 = nullptr, *attn = nullptr;
     int32_t *tok_dev = nullptr, *pos_dev = nullptr, *next_dev = nullptr;
     float mscale = 1.f;
     int64_t launches = 0;
     int use_graphs = 1, stop_after = 0;
-    int pdl = 1;  // bit 0: GEMV launches, bit 1: the other kernels (both together measured slower)
+    int pdl = 29;  // programmatic dependent launch per kernel kind (PdlBit); RMSNorm measured slower with it
     cudaStream_t own_stream = nullptr, last_stream = nullptr;
     // one cached graph
     struct {
@@ -137,9 +139,12 @@ void launch_pdl(neon_decoder_handle* h, bool pdl, void (*kernel)(KArgs...), dim3
     h->launches++;
 }
 
+enum PdlBit { kPdlGemv = 1, kPdlNorm = 2, kPdlRope = 4, kPdlAttn = 8, kPdlMerge = 16, kPdlOther = 32 };
+
 template <typename... KArgs, typename... Args>
-void launch(neon_decoder_handle* h, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    launch_pdl(h, (h->pdl & 2) != 0, kernel, grid, block, smem, st, args...);
+void launch(neon_decoder_handle* h, int bit, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+            Args... args) {
+    launch_pdl(h, (h->pdl & bit) != 0, kernel, grid, block, smem, st, args...);
 }
 
 int launch_gemv(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias, const uint16_t* x, int B, int rows, int K,
@@ -153,7 +158,18 @@ int launch_gemv(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias,
         configured[h->cfg.device & 63] = true;
     }
     const int grid = std::min((rows + 15) / 16, 148 * 2);
-    launch_pdl(h, (h->pdl & 1) != 0, gemv_mma_kernel, dim3(grid), dim3(256), smem, st, W, bias, x, B, rows, K, accumulate, out);
+    launch_pdl(h, (h->pdl & kPdlGemv) != 0, gemv_mma_kernel, dim3(grid), dim3(256), smem, st, W, bias, x, B, rows, K, accumulate, out);
+    return NEON_MOE_OK;
+}
+
+int launch_gemv_split(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias, const uint16_t* x, int B, int rows, int K,
+                      int splits, float* parts, long long part_stride, cudaStream_t st) {
+    if (K % 32) return dfail(h, NEON_MOE_EINVAL, "GEMV depth %d is not a multiple of 32", K);
+    const int nkb = K / 32, span = ((nkb + splits - 1) / splits) * 32;
+    if ((nkb + splits - 1) / splits > 8 * kGemvSplitU) return dfail(h, NEON_MOE_EINVAL, "GEMV depth %d needs more K-splits", K);
+    const size_t smem = (size_t)8 * (span + 64) * 2 + 8 * 128 * sizeof(float);
+    launch_pdl(h, (h->pdl & kPdlGemv) != 0, gemv_mma_split_kernel, dim3((rows + 15) / 16, splits), dim3(256), smem, st, W, bias, x,
+               B, rows, K, parts, part_stride);
     return NEON_MOE_OK;
 }
 
@@ -168,7 +184,7 @@ int launch_attention(neon_decoder_handle* h, const LayerW& L, int layer, int B, 
     const float scale = 1.f / std::sqrt((float)c.head_dim);
 #define ATTN_CASE(GG)                                                                                               \
     case GG:                                                                                                        \
-        launch(h, attn_partial_kernel<GG>, grid, dim3(256), 0, st, (const float*)h->qkv, (const uint16_t*)L.kc,     \
+        launch(h, kPdlAttn, attn_partial_kernel<GG>, grid, dim3(256), 0, st, (const float*)h->qkv, (const uint16_t*)L.kc,     \
                (const uint16_t*)L.vc, pos, c.n_q_heads, c.n_kv_heads, c.max_ctx, window, scale, splits, h->part);   \
         break;
     switch (G) {
@@ -176,7 +192,7 @@ int launch_attention(neon_decoder_handle* h, const LayerW& L, int layer, int B, 
         default: return dfail(h, NEON_MOE_EINVAL, "unsupported query group size %d", G);
     }
 #undef ATTN_CASE
-    launch(h, attn_merge_kernel, dim3(c.n_q_heads, B), dim3(64), 0, st, (const float*)h->part, (const uint16_t*)L.sinks,
+    launch(h, kPdlMerge, attn_merge_kernel, dim3(c.n_q_heads, B), dim3(64), 0, st, (const float*)h->part, (const uint16_t*)L.sinks,
            c.n_q_heads, splits, h->attn);
     return NEON_MOE_OK;
 }
@@ -185,22 +201,25 @@ int step_eager(neon_decoder_handle* h, const int32_t* tokens, const int32_t* pos
                cudaStream_t st) {
     const auto& c = h->cfg;
     const int H = c.hidden, QKV = (c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim, QD = c.n_q_heads * c.head_dim;
-    launch(h, embed_kernel, dim3(B), dim3(256), 0, st, (const uint16_t*)h->embed, tokens, H, h->x);
+    launch(h, kPdlOther, embed_kernel, dim3(B), dim3(256), 0, st, (const uint16_t*)h->embed, tokens, H, h->x);
     const int n_layers = h->stop_after > 0 ? std::min(h->stop_after, c.n_layers) : c.n_layers;
     const float* pending = nullptr;  // MoE output of the previous layer, added by the next RMSNorm kernel
     for (int l = 0; l < n_layers; ++l) {
         LayerW& L = h->layers[l];
-        launch(h, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, pending, (const uint16_t*)L.ln1, H, c.rms_eps, h->xn);
-        int rc = launch_gemv(h, L.wqkv, L.bqkv, h->xn, B, QKV, H, 0, h->qkv, st);
+        launch(h, kPdlNorm, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, pending, pending ? 1 : 0, 0ll,
+               (const uint16_t*)L.ln1, H, c.rms_eps, h->xn);
+        int rc = launch_gemv_split(h, L.wqkv, L.bqkv, h->xn, B, QKV, H, h->qkv_split, h->qkv, (long long)B * QKV, st);
         if (rc) return rc;
-        launch(h, rope_cache_kernel, dim3(c.n_q_heads + 2 * c.n_kv_heads, B), dim3(64), 0, st, h->qkv,
-               (const float*)h->inv_freq, positions, c.n_q_heads, c.n_kv_heads, h->mscale, c.max_ctx, L.kc, L.vc);
+        launch(h, kPdlRope, rope_cache_kernel, dim3(c.n_q_heads + 2 * c.n_kv_heads, B), dim3(64), 0, st, h->qkv, h->qkv_split,
+               (long long)B * QKV, (const float*)h->inv_freq, positions, c.n_q_heads, c.n_kv_heads, h->mscale, c.max_ctx, L.kc,
+               L.vc);
         rc = launch_attention(h, L, l, B, positions, st);
         if (rc) return rc;
-        rc = launch_gemv(h, L.wo, L.bo, h->attn, B, H, QD, 1, h->x, st);
+        rc = launch_gemv_split(h, L.wo, L.bo, h->attn, B, H, QD, h->o_split, h->oproj, (long long)B * H, st);
         if (rc) return rc;
-        launch(h, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, (const float*)nullptr, (const uint16_t*)L.ln2, H, c.rms_eps,
-               h->xn2);
+        // residual add of the projection's parts, then the second norm
+        launch(h, kPdlNorm, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, (const float*)h->oproj, h->o_split,
+               (long long)B * H, (const uint16_t*)L.ln2, H, c.rms_eps, h->xn2);
         const int64_t before = neon_moe_launch_count(L.moe);
         rc = neon_moe_forward(L.moe, h->xn2, B, nullptr, h->moe_out, nullptr, nullptr, st);
         if (rc) return dfail(h, rc, "layer %d MoE: %s", l, neon_moe_last_error(L.moe));
@@ -208,14 +227,15 @@ int step_eager(neon_decoder_handle* h, const int32_t* tokens, const int32_t* pos
         pending = h->moe_out;
     }
     if (h->stop_after > 0) {
-        launch(h, add_kernel, dim3((B * H + 255) / 256), dim3(256), 0, st, h->x, pending, B * H);
+        launch(h, kPdlOther, add_kernel, dim3((B * H + 255) / 256), dim3(256), 0, st, h->x, pending, B * H);
         return NEON_MOE_OK;
     }
-    launch(h, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, pending, (const uint16_t*)h->final_norm, H, c.rms_eps, h->xn);
+    launch(h, kPdlNorm, rmsnorm_kernel, dim3(B), dim3(1024), 0, st, h->x, pending, pending ? 1 : 0, 0ll,
+           (const uint16_t*)h->final_norm, H, c.rms_eps, h->xn);
     float* lg = logits ? logits : h->logits;
     int rc = launch_gemv(h, h->unembed, nullptr, h->xn, B, c.vocab, H, 0, lg, st);
     if (rc) return rc;
-    if (next) launch(h, argmax_kernel, dim3(B), dim3(1024), 0, st, (const float*)lg, c.vocab, next);
+    if (next) launch(h, kPdlOther, argmax_kernel, dim3(B), dim3(1024), 0, st, (const float*)lg, c.vocab, next);
     DCU(h, cudaGetLastError());
     return NEON_MOE_OK;
 }
@@ -274,7 +294,12 @@ int neon_decoder_create(const neon_decoder_config* cfg, neon_decoder_handle** ou
     TRY(alloc(h->final_norm, (size_t)H * 2));
     TRY(alloc(h->x, (size_t)B * H * 4));
     TRY(alloc(h->moe_out, (size_t)B * H * 4));
-    TRY(alloc(h->qkv, (size_t)B * QKV * 4));
+    // K-split factors of the two small projections: every warp of a CTA gets at most kGemvSplitU k-blocks
+    auto split_for = [](int K) { return std::min(4, (K / 32 + 8 * kGemvSplitU - 1) / (8 * kGemvSplitU)); };
+    h->qkv_split = split_for(H);
+    h->o_split = split_for(QD);
+    TRY(alloc(h->qkv, (size_t)h->qkv_split * B * QKV * 4));
+    TRY(alloc(h->oproj, (size_t)h->o_split * B * H * 4));
     TRY(alloc(h->logits, (size_t)B * c.vocab * 4));
     TRY(alloc(h->part, (size_t)B * c.n_q_heads * ((c.max_ctx + kAttnChunk - 1) / kAttnChunk) * 66 * 4));
     TRY(alloc(h->inv_freq, 32 * 4));
@@ -326,7 +351,7 @@ int neon_decoder_destroy(neon_decoder_handle* h) {
         if (L.moe) neon_moe_destroy(L.moe);
     }
     for (void* p : {(void*)h->embed, (void*)h->unembed, (void*)h->final_norm, (void*)h->x, (void*)h->qkv, (void*)h->moe_out,
-                    (void*)h->logits, (void*)h->part, (void*)h->inv_freq, (void*)h->xn, (void*)h->xn2, (void*)h->attn,
+                    (void*)h->logits, (void*)h->part, (void*)h->oproj, (void*)h->inv_freq, (void*)h->xn, (void*)h->xn2, (void*)h->attn,
                     (void*)h->tok_dev, (void*)h->pos_dev, (void*)h->next_dev})
         if (p) cudaFree(p);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);

@@ -33,6 +33,30 @@ class NeonDecoderConfig(ctypes.Structure):
                 ("swiglu_limit", ctypes.c_float), ("swiglu_alpha", ctypes.c_float), ("device", c_int)]
 
 
+class NeonWaterConfig(ctypes.Structure):
+    """Mirror of ``neon_water_config`` (include/neon_water.h)."""
+    _fields_ = [("n_particles", c_int), ("nx", c_int), ("ny", c_int), ("nz", c_int),
+                ("cell_size", ctypes.c_float), ("over_relaxation", ctypes.c_float), ("rest_density", ctypes.c_float),
+                ("damping", ctypes.c_float), ("mass", ctypes.c_float), ("dt", ctypes.c_float),
+                ("box_min", ctypes.c_float * 3), ("box_max", ctypes.c_float * 3), ("gravity", ctypes.c_float * 3),
+                ("collision_substeps", c_int), ("jacobi_iterations", c_int), ("device", c_int)]
+
+
+# name -> (restype, argtypes); must list every symbol include/neon_water.h declares
+WATER_SIGNATURES = {
+    "neon_water_create": (c_int, [ctypes.POINTER(NeonWaterConfig), c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "neon_water_destroy": (c_int, [c_void_p]),
+    "neon_water_last_error": (ctypes.c_char_p, [c_void_p]),
+    "neon_water_set_particles": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "neon_water_step": (c_int, [c_void_p, c_int, c_void_p]),
+    "neon_water_step_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "neon_water_particles_device": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]),
+    "neon_water_read_particles": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "neon_water_read_grid": (c_int, [c_void_p, ctypes.c_char_p, c_void_p, ctypes.c_uint64]),
+    "neon_water_set_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.c_int64]),
+    "neon_water_launch_count": (ctypes.c_int64, [c_void_p]),
+}
+
 # name -> (restype, argtypes); must list every symbol include/neon_decoder.h declares
 DECODER_SIGNATURES = {
     "neon_decoder_create": (c_int, [ctypes.POINTER(NeonDecoderConfig), ctypes.POINTER(c_void_p)]),
@@ -87,7 +111,7 @@ def load() -> ctypes.CDLL:
         raise ImportError(f"{SO_PATH} is missing: build it with `python -m neonengine_b200.build` "
                           "(there is no CPU fallback)")
     lib = ctypes.CDLL(SO_PATH)
-    for name, (res, args) in {**SIGNATURES, **DECODER_SIGNATURES}.items():
+    for name, (res, args) in {**SIGNATURES, **DECODER_SIGNATURES, **WATER_SIGNATURES}.items():
         fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
         fn.restype = res
         fn.argtypes = args

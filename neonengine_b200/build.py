@@ -12,7 +12,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libneon_moe.so")
-SOURCES = ["neon_moe.cu", "neon_decoder.cu"]
+SOURCES = ["neon_moe.cu", "neon_decoder.cu", "neon_water.cu"]
+# the water step reproduces the reference shader's float arithmetic bit for bit: no fused multiply-add there
+SOURCE_FLAGS = {"neon_water.cu": ["-fmad=false"]}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-cudart", "static"]
 
@@ -34,7 +36,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in SOURCES:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
-        cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = ["nvcc", *NVCC_FLAGS, *SOURCE_FLAGS.get(src, []), *(["-Xptxas", "-v"] if verbose else []), "-c",
+               os.path.join(CSRC, src), "-o", obj]
         procs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     objs = []
     for cmd, obj, proc in procs:

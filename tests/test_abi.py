@@ -39,6 +39,23 @@ def test_exports_every_declared_decoder_symbol(lib):
     assert set(names) == set(_lib.DECODER_SIGNATURES), "python binding table out of sync with the header"
 
 
+def test_exports_every_declared_water_symbol(lib):
+    names = declared_symbols("neon_water.h", "neon_water_")
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in neon_water.h but not exported"
+    assert set(names) == set(_lib.WATER_SIGNATURES), "python binding table out of sync with the header"
+
+
+def test_water_create_rejects_bad_config(lib):
+    h = ctypes.c_void_p()
+    cfg = _lib.NeonWaterConfig(8, 1, 4, 4, 0.1, 1.0, 1.0, 0.0, 1.0, 0.002)  # one cell along x
+    buf = (ctypes.c_float * 32)()
+    assert lib.neon_water_create(ctypes.byref(cfg), buf, 0, ctypes.byref(h)) == 1
+    assert b"grid" in lib.neon_water_last_error(None)
+    assert lib.neon_water_step(None, 1, None) == 1
+
+
 def test_decoder_create_rejects_bad_config(lib):
     h = ctypes.c_void_p()
     cfg = _lib.NeonDecoderConfig(1, 128, 8, 2, 32, 1000, 2, 64, 0, 150000.0, 32.0, 4096.0, 32.0, 1.0, 1e-5,

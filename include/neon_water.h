@@ -84,7 +84,18 @@ int neon_water_read_particles(neon_water_handle* h, float* pos4, float* vel4);
  * passes 6-8 read), "density" (floats, nx*ny*nz) or "flags" (uint32). */
 int neon_water_read_grid(neon_water_handle* h, const char* name, void* dst, uint64_t bytes);
 
-/* Options: "use_graphs" (default 1). */
+/* Runs ONE step eagerly with CUDA events between the pass groups and waits; ms4 receives the
+ * milliseconds of {separation (pass 1), particles->grid (passes 0, 2-4), pressure Jacobi
+ * (pass 5), pressure apply + grid->particles + integrate (passes 6-8)}. */
+int neon_water_profile_step(neon_water_handle* h, double* ms4, void* cuda_stream);
+
+/* Reads (and clears) the device status word: non-zero when the fused Jacobi kernel's bounded
+ * grid-barrier wait gave up (the step's result is then invalid).  Synchronises the last stream. */
+int neon_water_status(neon_water_handle* h, int* device_status_word);
+
+/* Options: "use_graphs" (default 1); "fused_jacobi" (default 1 where the device supports
+ * cooperative launches and the grid has at most 2 cells per resident thread: all pressure
+ * iterations in one cooperative kernel with a grid-wide barrier; 0 = one launch per iteration). */
 int neon_water_set_option(neon_water_handle* h, const char* name, int64_t value);
 
 int64_t neon_water_launch_count(const neon_water_handle* h);

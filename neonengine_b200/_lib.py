@@ -53,6 +53,8 @@ WATER_SIGNATURES = {
     "neon_water_particles_device": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]),
     "neon_water_read_particles": (c_int, [c_void_p, c_void_p, c_void_p]),
     "neon_water_read_grid": (c_int, [c_void_p, ctypes.c_char_p, c_void_p, ctypes.c_uint64]),
+    "neon_water_status": (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    "neon_water_profile_step": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), c_void_p]),
     "neon_water_set_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.c_int64]),
     "neon_water_launch_count": (ctypes.c_int64, [c_void_p]),
 }

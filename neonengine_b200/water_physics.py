@@ -87,6 +87,17 @@ class WaterPhysics:
         self._check(self._lib.neon_water_particles_device(self._h, ctypes.byref(p), ctypes.byref(v)), "neon_water_particles_device")
         return p.value, v.value
 
+    def profile_step(self) -> dict:
+        """One eager step timed in four groups (ms)."""
+        ms = (ctypes.c_double * 4)()
+        self._check(self._lib.neon_water_profile_step(self._h, ms, None), "neon_water_profile_step")
+        return dict(zip(("separate", "particles_to_grid", "jacobi", "apply_g2p_integrate"), ms))
+
+    def status(self) -> int:
+        word = ctypes.c_int(0)
+        self._lib.neon_water_status(self._h, ctypes.byref(word))
+        return word.value
+
     def set_option(self, name: str, value: int) -> None:
         self._check(self._lib.neon_water_set_option(self._h, name.encode(), int(value)), "neon_water_set_option")
 

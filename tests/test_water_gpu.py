@@ -25,6 +25,7 @@ def _gpu(cfg, pos0):
 
 
 def _compare(sim, pos, vel, grids):
+    assert sim.status() == 0
     gp, gv = sim.read_particles()
     np.testing.assert_array_equal(gp, pos)
     np.testing.assert_array_equal(gv, vel)
@@ -116,6 +117,22 @@ def test_odd_substeps_and_no_jacobi():
     _compare(sim2, pos, vel, grids)
     sim.close()
     sim2.close()
+
+
+def test_fused_and_per_iteration_jacobi_agree():
+    cfg = WaterConfig()
+    pos0 = spawn_particles(cfg)
+    outs = []
+    for fused in (1, 0):
+        sim = _gpu(cfg, pos0)
+        sim.set_option("fused_jacobi", fused)
+        sim.run_simulation(3)
+        assert sim.status() == 0
+        outs.append((sim.read_particles(), sim.read_grid("pressure")))
+        sim.close()
+    np.testing.assert_array_equal(outs[0][0][0], outs[1][0][0])
+    np.testing.assert_array_equal(outs[0][0][1], outs[1][0][1])
+    np.testing.assert_array_equal(outs[0][1], outs[1][1])
 
 
 def test_rejects_bad_arguments():

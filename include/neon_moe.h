@@ -76,6 +76,20 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w_bf16, const vo
                          const void* gate_up_bias_bf16, const uint8_t* down_blocks,
                          const uint8_t* down_scales, const void* down_bias_bf16, int on_device);
 
+/* Weight files (this library's own format; the engine serialises nothing).  A file is a 64-byte
+ * header {magic "NMOEW1", version 1, layout, hidden, inter, n_experts, expert_lo, n_local, top_k,
+ * n_sections}, a table of {name[16], offset, bytes} sections and the sections' bytes on 256-byte
+ * boundaries.  Layout 0 ("raw") holds the eight tensors exactly as neon_moe_set_weights takes them
+ * and is re-tiled on the GPU at load; layout 1 ("tiled") holds the tensor-core layout byte for byte
+ * as it sits in HBM, so loading is a straight copy - but it does not hold the mma.sync layout, so
+ * "path" 1 and neon_moe_forward_static refuse to run on a handle loaded from it.
+ * neon_moe_save_weights writes layout 1 from a handle that has weights; raw files are written by
+ * the host (neonengine_b200/weight_file.py).  neon_moe_load_weights_file checks the header against
+ * the handle's configuration and every section's size against the file before it touches the GPU.
+ * Follows: model files read once at start-up, NeonEngine/src/lve_model.cpp:45-51 (createModelFromFile). */
+int neon_moe_save_weights(neon_moe_handle* h, const char* path);
+int neon_moe_load_weights_file(neon_moe_handle* h, const char* path);
+
 /* One layer pass over T tokens, enqueued on `cuda_stream` (a cudaStream_t; NULL = default
  * stream).  All pointers are device memory: hidden bf16 [T,H]; logit_bias fp32 [E] or
  * NULL (added to the router logits); out fp32 [T,H]; topk_idx int32 [T,k] and topk_w

@@ -80,6 +80,8 @@ DECODER_SIGNATURES = {
 SIGNATURES = {
     "neon_moe_create": (c_int, [ctypes.POINTER(NeonMoeConfig), ctypes.POINTER(c_void_p)]),
     "neon_moe_set_weights": (c_int, [c_void_p] * 9 + [c_int]),
+    "neon_moe_save_weights": (c_int, [c_void_p, ctypes.c_char_p]),
+    "neon_moe_load_weights_file": (c_int, [c_void_p, ctypes.c_char_p]),
     "neon_moe_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_forward_static": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_ep_unique_id": (c_int, [c_void_p]),

@@ -12,6 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libneon_moe.so")
+APP = os.path.join(HERE, "moe_app")
 SOURCES = ["neon_moe.cu", "neon_decoder.cu", "neon_water.cu"]
 # the water step reproduces the reference shader's float arithmetic bit for bit: no fused multiply-add there
 SOURCE_FLAGS = {"neon_water.cu": ["-fmad=false"]}
@@ -53,6 +54,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode:
         raise RuntimeError("nvcc link failed: " + " ".join(cmd))
+    # the headless application loop (engine-style owner of the layer), linked against the library
+    cmd = ["nvcc", "-O2", "-std=c++17", "-cudart", "static", os.path.join(CSRC, "moe_app.cpp"), "-o", APP,
+           "-L" + HERE, "-lneon_moe", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode:
+        raise RuntimeError("building moe_app failed: " + " ".join(cmd))
     return SO
 
 

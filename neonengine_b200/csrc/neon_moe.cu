@@ -888,6 +888,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     drop_graphs(h);
     if (!strcmp(name, "path")) {
         if (value != 1 && value != 2) return fail(h, NEON_MOE_EINVAL, "path must be 1 (mma.sync) or 2 (tcgen05)");
+        if (value == 1 && !h->gu_wq && h->has_weights)
+            return fail(h, NEON_MOE_ESTATE, "path 1 needs the mma.sync weight layout, which a tiled weight file does not hold");
         h->path = (int)value;
     } else if (!strcmp(name, "a_tx_bytes")) {
         h->a_tx_bytes = (uint32_t)value;
@@ -936,6 +938,157 @@ int neon_moe_read_profile(neon_moe_handle* h, double* ms, int* n_forwards) {
     return NEON_MOE_OK;
 }
 
+// ---- weight files ----------------------------------------------------------------------------
+// Layout of a weight file (all integers little-endian):
+//   neon_moe_file_header (64 bytes), n_sections x neon_moe_file_section (32 bytes), then the
+//   sections' bytes, each starting on a 256-byte boundary.
+//   layout 0 "raw": sections router_w, router_b, gu_blocks, gu_scales, gu_bias, dn_blocks,
+//     dn_scales, dn_bias exactly as neon_moe_set_weights takes them (re-tiled on the GPU at load);
+//   layout 1 "tiled": router_w, router_b, gu_bias, dn_bias as above and gu_tiles, gu_sfa, dn_tiles,
+//     dn_sfa = the tensor-core layout byte for byte as it sits in HBM (box-contiguous nibbles and
+//     512-byte scale atoms), so loading is a straight copy.
+namespace {
+struct FileSection { char name[16]; uint64_t offset, bytes; };
+struct FileHeader {
+    char magic[8];
+    uint32_t version, layout;
+    int32_t hidden, inter, n_experts, expert_lo, n_local, top_k;
+    uint32_t n_sections, reserved[5];
+};
+static_assert(sizeof(FileHeader) == 64 && sizeof(FileSection) == 32, "file structs");
+constexpr char kFileMagic[8] = {'N', 'M', 'O', 'E', 'W', '1', 0, 0};
+
+const FileSection* find_section(const std::vector<FileSection>& secs, const char* name) {
+    for (const auto& sec : secs)
+        if (!strncmp(sec.name, name, sizeof sec.name)) return &sec;
+    return nullptr;
+}
+}  // namespace
+
+int neon_moe_save_weights(neon_moe_handle* h, const char* path) {
+    if (!h || !path) return NEON_MOE_EINVAL;
+    if (!h->has_weights || !h->gu_wt) return fail(h, NEON_MOE_ESTATE, "save_weights before set_weights");
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaDeviceSynchronize());
+    const size_t H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts, EL = h->n_local;
+    const size_t mt_gu = (2 * I + 127) / 128, mt_dn = (H + 127) / 128, nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
+    struct Item { const char* name; const void* dev; size_t bytes; };
+    const Item items[] = {{"router_w", h->router_w, E * H * 2},       {"router_b", h->router_b, E * 2},
+                          {"gu_bias", h->gu_bias, EL * 2 * I * 2},    {"dn_bias", h->dn_bias, EL * H * 2},
+                          {"gu_tiles", h->gu_wt, EL * mt_gu * nch_h * 8192}, {"gu_sfa", h->gu_sfa, EL * mt_gu * nch_h * 512},
+                          {"dn_tiles", h->dn_wt, EL * mt_dn * nch_i * 8192}, {"dn_sfa", h->dn_sfa, EL * mt_dn * nch_i * 512}};
+    const uint32_t ns = sizeof items / sizeof items[0];
+    FileHeader hd{};
+    memcpy(hd.magic, kFileMagic, 8);
+    hd.version = 1; hd.layout = 1;
+    hd.hidden = (int)H; hd.inter = (int)I; hd.n_experts = (int)E; hd.expert_lo = h->e_lo; hd.n_local = (int)EL; hd.top_k = h->cfg.top_k;
+    hd.n_sections = ns;
+    std::vector<FileSection> secs(ns);
+    uint64_t off = (sizeof hd + ns * sizeof(FileSection) + 255) & ~uint64_t(255);
+    for (uint32_t i = 0; i < ns; ++i) {
+        memset(&secs[i], 0, sizeof secs[i]);
+        strncpy(secs[i].name, items[i].name, sizeof secs[i].name - 1);
+        secs[i].offset = off;
+        secs[i].bytes = items[i].bytes;
+        off = (off + items[i].bytes + 255) & ~uint64_t(255);
+    }
+    FILE* f = fopen(path, "wb");
+    if (!f) return fail(h, NEON_MOE_EINVAL, "cannot open '%s' for writing", path);
+    bool ok = fwrite(&hd, sizeof hd, 1, f) == 1 && fwrite(secs.data(), sizeof(FileSection), ns, f) == ns;
+    std::vector<unsigned char> buf;
+    for (uint32_t i = 0; ok && i < ns; ++i) {
+        buf.resize(items[i].bytes);
+        if (cudaMemcpy(buf.data(), items[i].dev, items[i].bytes, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = false; break; }
+        ok = fseek(f, (long)secs[i].offset, SEEK_SET) == 0 && fwrite(buf.data(), 1, items[i].bytes, f) == items[i].bytes;
+    }
+    if (ok && ns && secs[ns - 1].offset + secs[ns - 1].bytes < off)  // zero padding up to the aligned end
+        ok = fseek(f, (long)off - 1, SEEK_SET) == 0 && fputc(0, f) != EOF;
+    ok = (fclose(f) == 0) && ok;
+    cudaGetLastError();
+    if (!ok) return fail(h, NEON_MOE_ECUDA, "writing '%s' failed", path);
+    return NEON_MOE_OK;
+}
+
+int neon_moe_load_weights_file(neon_moe_handle* h, const char* path) {
+    if (!h || !path) return NEON_MOE_EINVAL;
+    FILE* f = fopen(path, "rb");
+    if (!f) return fail(h, NEON_MOE_EINVAL, "cannot open '%s'", path);
+    struct Closer { FILE* f; ~Closer() { fclose(f); } } closer{f};
+    FileHeader hd{};
+    if (fread(&hd, sizeof hd, 1, f) != 1 || memcmp(hd.magic, kFileMagic, 8) != 0 || hd.version != 1)
+        return fail(h, NEON_MOE_EINVAL, "'%s' is not a version-1 weight file", path);
+    if (hd.hidden != h->cfg.hidden || hd.inter != h->cfg.inter || hd.n_experts != h->cfg.n_experts || hd.top_k != h->cfg.top_k ||
+        hd.n_local != h->n_local || hd.expert_lo != h->e_lo)
+        return fail(h, NEON_MOE_EINVAL, "'%s' holds H=%d I=%d E=%d experts [%d,%d) top_k=%d; the handle expects H=%d I=%d E=%d [%d,%d) k=%d",
+                    path, hd.hidden, hd.inter, hd.n_experts, hd.expert_lo, hd.expert_lo + hd.n_local, hd.top_k, h->cfg.hidden,
+                    h->cfg.inter, h->cfg.n_experts, h->e_lo, h->e_lo + h->n_local, h->cfg.top_k);
+    if (hd.layout > 1 || hd.n_sections == 0 || hd.n_sections > 64) return fail(h, NEON_MOE_EINVAL, "'%s': bad layout or section count", path);
+    std::vector<FileSection> secs(hd.n_sections);
+    if (fread(secs.data(), sizeof(FileSection), hd.n_sections, f) != hd.n_sections) return fail(h, NEON_MOE_EINVAL, "'%s' is truncated", path);
+    if (fseek(f, 0, SEEK_END) != 0) return fail(h, NEON_MOE_EINVAL, "'%s': seek failed", path);
+    const uint64_t file_bytes = (uint64_t)ftell(f);
+    const size_t H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts, EL = h->n_local;
+    const size_t mt_gu = (2 * I + 127) / 128, mt_dn = (H + 127) / 128, nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
+    std::vector<std::vector<unsigned char>> data;
+    auto read_section = [&](const char* name, size_t expect, const unsigned char** out) -> int {
+        const FileSection* sec = find_section(secs, name);
+        if (!sec) return fail(h, NEON_MOE_EINVAL, "'%s' has no section '%s'", path, name);
+        if (sec->bytes != expect) return fail(h, NEON_MOE_EINVAL, "'%s': section '%s' holds %llu bytes, %zu expected", path, name,
+                                              (unsigned long long)sec->bytes, expect);
+        if (sec->offset + sec->bytes > file_bytes) return fail(h, NEON_MOE_EINVAL, "'%s' is truncated inside section '%s'", path, name);
+        data.emplace_back(expect);
+        if (fseek(f, (long)sec->offset, SEEK_SET) != 0 || fread(data.back().data(), 1, expect, f) != expect)
+            return fail(h, NEON_MOE_EINVAL, "'%s': reading section '%s' failed", path, name);
+        *out = data.back().data();
+        return NEON_MOE_OK;
+    };
+    int rc;
+    const unsigned char *rw, *rb, *gub, *dnb;
+    if ((rc = read_section("router_w", E * H * 2, &rw)) || (rc = read_section("router_b", E * 2, &rb)) ||
+        (rc = read_section("gu_bias", EL * 2 * I * 2, &gub)) || (rc = read_section("dn_bias", EL * H * 2, &dnb)))
+        return rc;
+    if (hd.layout == 0) {
+        const unsigned char *g1, *g2, *d1, *d2;
+        if ((rc = read_section("gu_blocks", EL * 2 * I * (H / 2), &g1)) || (rc = read_section("gu_scales", EL * 2 * I * (H / 32), &g2)) ||
+            (rc = read_section("dn_blocks", EL * H * (I / 2), &d1)) || (rc = read_section("dn_scales", EL * H * (I / 32), &d2)))
+            return rc;
+        return neon_moe_set_weights(h, rw, rb, g1, g2, gub, d1, d2, dnb, 0);
+    }
+    // tiled: straight copies into the tensor-core buffers; the mma.sync layout is not in the file
+    const unsigned char *gt, *gs, *dt, *ds;
+    if ((rc = read_section("gu_tiles", EL * mt_gu * nch_h * 8192, &gt)) || (rc = read_section("gu_sfa", EL * mt_gu * nch_h * 512, &gs)) ||
+        (rc = read_section("dn_tiles", EL * mt_dn * nch_i * 8192, &dt)) || (rc = read_section("dn_sfa", EL * mt_dn * nch_i * 512, &ds)))
+        return rc;
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaDeviceSynchronize());
+    h->has_weights = false;
+    drop_graphs(h);
+    if ((rc = copy_in(h, &h->router_w, rw, E * H, 0)) || (rc = copy_in(h, &h->router_b, rb, E, 0)) ||
+        (rc = copy_in(h, &h->gu_bias, gub, EL * 2 * I, 0)) || (rc = copy_in(h, &h->dn_bias, dnb, EL * H, 0)))
+        return rc;
+    struct Tiled { uint8_t** dst; const unsigned char* src; size_t bytes; };
+    const Tiled tiled[] = {{&h->gu_wt, gt, EL * mt_gu * nch_h * 8192}, {&h->gu_sfa, gs, EL * mt_gu * nch_h * 512},
+                           {&h->dn_wt, dt, EL * mt_dn * nch_i * 8192}, {&h->dn_sfa, ds, EL * mt_dn * nch_i * 512}};
+    for (const auto& t : tiled) {
+        if (!*t.dst && (rc = dev_alloc(h, t.dst, t.bytes))) return rc;
+        CU(h, cudaMemcpy(*t.dst, t.src, t.bytes, cudaMemcpyHostToDevice));
+    }
+    const uint64_t rows_gu = (uint64_t)EL * mt_gu * nch_h * 128, rows_dn = (uint64_t)EL * mt_dn * nch_i * 128;
+    if ((rc = make_weight_map(h, &h->tm_gu, h->gu_wt, rows_gu, 128, false)) || (rc = make_weight_map(h, &h->tm_gu2, h->gu_wt, rows_gu, 256, false)) ||
+        (rc = make_weight_map(h, &h->tm4_gu, h->gu_wt, rows_gu, 128, true)) || (rc = make_weight_map(h, &h->tm4_gu2, h->gu_wt, rows_gu, 256, true)) ||
+        (rc = make_weight_map(h, &h->tm_dn, h->dn_wt, rows_dn, 128, false)) || (rc = make_weight_map(h, &h->tm_dn2, h->dn_wt, rows_dn, 256, false)) ||
+        (rc = make_weight_map(h, &h->tm4_dn, h->dn_wt, rows_dn, 128, true)) || (rc = make_weight_map(h, &h->tm4_dn2, h->dn_wt, rows_dn, 256, true)))
+        return rc;
+    // the mma.sync kernels' layout was not loaded: those paths refuse to run until set_weights is called
+    for (void** p : {(void**)&h->gu_wq, (void**)&h->dn_wq, (void**)&h->gu_sq, (void**)&h->dn_sq}) {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
+    }
+    h->path = 2;
+    h->has_weights = true;
+    return NEON_MOE_OK;
+}
+
 int neon_moe_status(neon_moe_handle* h, int* word) {
     if (!h || !word) return NEON_MOE_EINVAL;
     CU(h, cudaSetDevice(h->cfg.device));
@@ -973,6 +1126,7 @@ extern "C" int neon_moe_forward_static(const neon_moe_handle* h, const void* hid
                                        void* cuda_stream) {
     if (!h) return fail(nullptr, NEON_MOE_EINVAL, "null handle");
     if (!h->has_weights) return fail(nullptr, NEON_MOE_ESTATE, "forward_static before set_weights");
+    if (!h->gu_wq) return fail(nullptr, NEON_MOE_ESTATE, "forward_static needs the mma.sync weight layout, which a tiled weight file does not hold");
     if (h->cfg.ep_size != 1) return fail(nullptr, NEON_MOE_ESTATE, "forward_static needs ep_size == 1");
     if (T < 0) return fail(nullptr, NEON_MOE_EINVAL, "negative T");
     if (T == 0) return NEON_MOE_OK;

@@ -17,7 +17,7 @@ from .synth import MoeShape, MoeWeights
 
 
 class MoeLayerSystem:
-    def __init__(self, shape: MoeShape, weights: MoeWeights, max_tokens: int, device: int = 0,
+    def __init__(self, shape: MoeShape, weights: MoeWeights | None, max_tokens: int, device: int = 0,
                  ep_rank: int = 0, ep_size: int = 1):
         self._lib = _lib.load()
         self.shape = shape
@@ -32,7 +32,8 @@ class MoeLayerSystem:
         if rc != 0:
             raise RuntimeError(f"neon_moe_create failed ({rc}): {self._lib.neon_moe_last_error(None).decode()}")
         self._h = handle
-        self.set_weights(weights)
+        if weights is not None:  # None: weights come from a file (load_weights_file)
+            self.set_weights(weights)
 
     # -- helpers -------------------------------------------------------------------------
     def _check(self, rc: int, what: str) -> None:
@@ -47,6 +48,14 @@ class MoeLayerSystem:
         arrs = [np.ascontiguousarray(a) for a in (w.router_w, w.router_b, w.gate_up_blocks, w.gate_up_scales,
                                                   w.gate_up_bias, w.down_blocks, w.down_scales, w.down_bias)]
         self._check(self._lib.neon_moe_set_weights(self._h, *[self._np_ptr(a) for a in arrs], 0), "neon_moe_set_weights")
+
+    def save_weights(self, path: str) -> None:
+        """Writes the tensor-core layout as it sits in HBM ("tiled" weight file)."""
+        self._check(self._lib.neon_moe_save_weights(self._h, str(path).encode()), "neon_moe_save_weights")
+
+    def load_weights_file(self, path: str) -> None:
+        """Loads a raw or tiled weight file (see include/neon_moe.h)."""
+        self._check(self._lib.neon_moe_load_weights_file(self._h, str(path).encode()), "neon_moe_load_weights_file")
 
     # -- device path ---------------------------------------------------------------------
     def run(self, hidden, logit_bias=None, out=None, want_routing=False, stream=None):

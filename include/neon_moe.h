@@ -185,6 +185,9 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * "mx4" (default 0): 1 runs decode-sized passes on tcgen05.mma.kind::mxf4 (weights stay packed
  * 4-bit in shared memory, activations as six e2m1 terms): ~5 % faster, errors ~40x larger (still
  * inside the 2e-2 / 5e-3 contract on random inputs, not on inputs whose errors add coherently).
+ * "fuse_dispatch" (default 0): 1 = at decode-sized passes the router CTA that finishes last also
+ * runs the dispatch, saving one launch (identical results; measured no faster than the separate
+ * kernel under programmatic dependent launch, 0.1086 vs 0.1078 ms per 64-token pass).
  * "sync_debug": synchronise after every kernel and name the one that failed.
  * "a_tx_bytes": bytes a 128x128 4-bit TMA box reports to its mbarrier (default 8192).
  * Others ("n_ctas", "ctas_per_sm", "max_stages", "trace_ptr") are measurement aids.

@@ -168,19 +168,15 @@ __global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __r
 
 // The same for at most 1024 entries (decode batches): one entry per thread, four barriers, all
 // scans done by warps in shared memory.  Identical results to dispatch_tiles_kernel.
-__global__ void __launch_bounds__(1024) dispatch_tiles_small_kernel(const int32_t* __restrict__ idx, int n, int e_lo,
-                                                                    int n_local, DispatchArrays d, int tile_tokens,
-                                                                    TileList tl) {
-    pdl_launch_dependents();
-    pdl_wait();
-    extern __shared__ int dsmem[];
+__device__ __forceinline__ void dispatch_tiles_small_body(const int32_t* idx, int n, int e_lo, int n_local, DispatchArrays d,
+                                                          int tile_tokens, TileList tl, int* dsmem) {
     int* wc = dsmem;                // [32][n_local] entries of each expert per warp, then their prefix
     __shared__ int cnt[kMaxExperts], off[kMaxExperts + 1], first[kMaxExperts + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int j = tid; j < 32 * n_local; j += 1024) wc[j] = 0;
     int e = -1;
     if (tid < n) {
-        e = idx[tid] - e_lo;
+        e = __ldcg(idx + tid) - e_lo;  // L2: the entries may have been written by other CTAs of this launch
         if (e < 0 || e >= n_local) e = -1;
     }
     __syncthreads();
@@ -254,6 +250,42 @@ __global__ void __launch_bounds__(1024) dispatch_tiles_small_kernel(const int32_
             tl.rows[t] = min(tile_tokens, c - r);
         }
     }
+}
+
+__global__ void __launch_bounds__(1024) dispatch_tiles_small_kernel(const int32_t* __restrict__ idx, int n, int e_lo,
+                                                                    int n_local, DispatchArrays d, int tile_tokens,
+                                                                    TileList tl) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int dsmem[];
+    dispatch_tiles_small_body(idx, n, e_lo, n_local, d, tile_tokens, tl, dsmem);
+}
+
+// Router and dispatch in one launch for decode batches (T * k <= 1024): one CTA of 1024 threads
+// routes each token; the CTA that finishes last (a counter in global memory) then runs the
+// dispatch + token-tile construction over all entries, so the pass needs no separate dispatch
+// launch.  Results are identical to router_topk_wide_kernel followed by
+// dispatch_tiles_small_kernel.  Dynamic shared memory: max(router need, 32 * n_local ints).
+__global__ void __launch_bounds__(1024)
+router_dispatch_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr, const uint16_t* __restrict__ br,
+                       const float* __restrict__ logit_bias, int T, int H, int E, int k, int32_t* idx, float* __restrict__ w,
+                       float* __restrict__ tok_amax, unsigned* done, DispatchArrays d, int tile_tokens, TileList tl) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char rsmem[];
+    __shared__ int is_last;
+    router_topk_wide_body(x, wr, br, logit_bias, T, H, E, k, idx, w, tok_amax, rsmem);
+    __syncthreads();  // this token's entries are written
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(done, 1u);
+        is_last = prev == gridDim.x - 1;
+        if (is_last) *done = 0u;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    dispatch_tiles_small_body(idx, T * k, 0, E, d, tile_tokens, tl, reinterpret_cast<int*>(rsmem));
 }
 
 // ---------------------------------------------------------------------------------------

@@ -231,13 +231,11 @@ router_topk_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
 // a dot product issued before the first use.  Same arithmetic contract as above: fp32
 // accumulation in a fixed order that is identical for every expert, ties to the lower id.
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-router_topk_wide_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
-                        const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H, int E,
-                        int k, int32_t* __restrict__ idx, float* __restrict__ w, float* __restrict__ tok_amax) {
-    pdl_launch_dependents();
-    pdl_wait();
-    extern __shared__ __align__(16) unsigned char rsmem[];
+__device__ __forceinline__ void
+router_topk_wide_body(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
+                      const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H, int E,
+                      int k, int32_t* __restrict__ idx, float* __restrict__ w, float* __restrict__ tok_amax,
+                      unsigned char* rsmem) {
     uint4* xs = reinterpret_cast<uint4*>(rsmem);            // [H/8] bf16 x 8
     float* lg = reinterpret_cast<float*>(rsmem + H * 2);    // [E]
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -339,6 +337,16 @@ router_topk_wide_kernel(const uint16_t* __restrict__ x, const uint16_t* __restri
                 }
         }
     }
+}
+
+__global__ void __launch_bounds__(1024)
+router_topk_wide_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr,
+                        const uint16_t* __restrict__ br, const float* __restrict__ logit_bias, int T, int H, int E,
+                        int k, int32_t* __restrict__ idx, float* __restrict__ w, float* __restrict__ tok_amax) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char rsmem[];
+    router_topk_wide_body(x, wr, br, logit_bias, T, H, E, k, idx, w, tok_amax, rsmem);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -37,6 +37,8 @@ struct neon_moe_handle {
     cudaStream_t own_stream = nullptr;
     int last_n = 0;
     int n_sms = 148;
+    unsigned* route_done = nullptr;  // CTA counter of router_dispatch_kernel
+    int fuse_dispatch = 0;          // decode passes: the last router CTA runs the dispatch (measured: no gain over PDL)
     // weights
     uint16_t *router_w = nullptr, *router_b = nullptr, *gu_bias = nullptr, *dn_bias = nullptr;
     uint4 *gu_wq = nullptr, *dn_wq = nullptr;
@@ -474,6 +476,7 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
             if (cudaEventCreate(&ev) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaEventCreate failed"));
     }
     if (cudaMemset(h->status, 0, 16) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
+    h->route_done = reinterpret_cast<unsigned*>(h->status + 2);  // third word of the zeroed status block
     if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(fail(h, NEON_MOE_ECUDA, "cudaStreamCreate failed"));
     *out = h;
@@ -520,7 +523,8 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
 // (rows = tokens, k_eff = top_k) and by the expert-parallel local pass (rows = received
 // rows, k_eff = 1, route_w = 1).
 static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_eff, const int32_t* idx, int e_lo,
-                        const float* route_w, const float* hidden_amax, float* out, cudaStream_t st, bool prof) {
+                        const float* route_w, const float* hidden_amax, float* out, cudaStream_t st, bool prof,
+                        bool dispatched = false) {
     const int H = h->cfg.hidden, I = h->cfg.inter, EL = h->n_local;
     const int n = rows * k_eff;
     DispatchArrays d{h->count, h->offset, h->perm, h->inv};
@@ -530,13 +534,15 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         TileList tl2{h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2};
         const TileList& tld = tt2 ? tl2 : tl;
         const bool stacked = tt <= 32;
-        if (n <= 1024)
+        if (dispatched) {
+            // the router launch already produced the dispatch arrays and the tile list
+        } else if (n <= 1024)
             launch_k(h->pdl != 0, dispatch_tiles_small_kernel, dim3(1), dim3(1024), (size_t)(32 * EL) * sizeof(int), st, idx, n,
                      e_lo, EL, d, tt, tl);
         else
             launch_k(h->pdl != 0, dispatch_tiles_kernel, dim3(1), dim3(1024), (size_t)(33 * EL) * sizeof(int), st, idx, n, e_lo,
                      EL, d, tt, tl, tt2, tl2, (unsigned*)nullptr);
-        h->launches++;
+        if (!dispatched) h->launches++;
         DBG_SYNC(h, st, "dispatch_tiles_kernel");
         const int nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
         if (stacked && !hidden_amax) {  // no producer kernel measured the rows: do it here
@@ -710,8 +716,21 @@ static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const fl
     const int k = h->cfg.top_k, n = T * k;
     const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
     mark(h, st, prof);
-    launch_router(h, hidden, T, logit_bias, h->idx, h->route_w, h->x_amax, st);
-    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, h->path == 2 ? h->x_amax : nullptr, out, st, prof);
+    // decode passes on the main path: the last router CTA also runs the dispatch
+    const bool fused = h->path == 2 && h->fuse_dispatch && T <= 64 && n <= 1024 && h->n_local == h->cfg.n_experts;
+    if (fused) {
+        const int H = h->cfg.hidden, E = h->cfg.n_experts;
+        const size_t smem = std::max((size_t)H * 2 + E * sizeof(float), (size_t)32 * E * sizeof(int));
+        DispatchArrays d{h->count, h->offset, h->perm, h->inv};
+        TileList tl{h->tile_expert, h->tile_row0, h->tile_rows, h->n_tiles, h->row_tile};
+        launch_k(h->pdl != 0, router_dispatch_kernel, dim3(T), dim3(1024), smem, st, static_cast<const uint16_t*>(hidden),
+                 (const uint16_t*)h->router_w, (const uint16_t*)h->router_b, logit_bias, T, H, E, k, h->idx, h->route_w, h->x_amax,
+                 h->route_done, d, tile_tokens_for(T), tl);
+        h->launches++;
+    } else {
+        launch_router(h, hidden, T, logit_bias, h->idx, h->route_w, h->x_amax, st);
+    }
+    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, h->path == 2 ? h->x_amax : nullptr, out, st, prof, fused);
     if (rc) return rc;
     if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
     if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
@@ -901,6 +920,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->n_sms = (int)value;
     } else if (!strcmp(name, "pdl")) {
         h->pdl = (int)value;
+    } else if (!strcmp(name, "fuse_dispatch")) {
+        h->fuse_dispatch = (int)value;
     } else if (!strcmp(name, "mx4")) {
         h->mx4 = (int)value;
     } else if (!strcmp(name, "use_graphs")) {

@@ -234,3 +234,24 @@ def test_packed_fp4_decode_option(full20b):
             check_against_oracle(layer, W, hidden, logit_bias=lb, what=f"mx4 T={T}")
     finally:
         layer.set_option("mx4", 0)
+
+
+def test_fused_router_dispatch_equals_separate_kernels(full20b):
+    """Option fuse_dispatch: the last router CTA running the dispatch gives the same routing,
+    dispatch arrays and outputs (bit for bit) as the separate dispatch kernel."""
+    shape, W, layer = full20b
+    lb = synth.zipf_logit_bias(shape.n_experts)
+    try:
+        for T, seed in ((64, 41), (8, 42), (1, 43), (17, 44)):
+            hidden = synth.make_hidden(T, W, seed, logit_bias=lb)
+            layer.set_option("fuse_dispatch", 1)
+            out1, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, what=f"fused T={T}")
+            d1 = layer.read_dispatch()
+            layer.set_option("fuse_dispatch", 0)
+            out0, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, what=f"separate T={T}")
+            d0 = layer.read_dispatch()
+            np.testing.assert_array_equal(out1, out0)
+            for a, b in zip(d1, d0):
+                np.testing.assert_array_equal(a, b)
+    finally:
+        layer.set_option("fuse_dispatch", 0)

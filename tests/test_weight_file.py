@@ -110,8 +110,6 @@ def test_loader_matches_set_weights_and_tiled_bytes(tmp_path):
         data = f.read()
     with open(tmp_path / "cut.nmoe", "wb") as f:
         f.write(data[:len(data) // 2])
-    with pytest.raises(RuntimeError, match="truncated"):
-        other.load_weights_file(str(tmp_path / "cut.nmoe"))
     c = MoeLayerSystem(SHAPE, None, max_tokens=4)
     with pytest.raises(RuntimeError, match="truncated"):
         c.load_weights_file(str(tmp_path / "cut.nmoe"))

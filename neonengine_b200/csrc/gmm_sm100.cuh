@@ -295,7 +295,7 @@ router_dispatch_kernel(const uint16_t* __restrict__ x, const uint16_t* __restric
 //
 // Output: one block per (token tile, chunk), written as the exact shared-memory image the
 // GEMM stage wants, so a single bulk copy brings in all terms and their scales:
-//   [TERMS x 512 B scale atoms][row group 0: term 0 | term 1 | ...][row group 1: ...] ...
+//   [TERMS x 512 B scale atoms, padded to 1024 B][row group 0: term 0 | term 1 | ...][row group 1: ...] ...
 // A row group is 8 rows x 128 B of one term in the 128-byte-swizzled K-major layout (the
 // 16-byte unit u of row r sits at unit u ^ (r % 8)).  Block stride = act_block_bytes().
 // FROM_BF16: source rows are bf16 hidden states gathered through perm (token = perm[p]/k);
@@ -308,9 +308,13 @@ router_dispatch_kernel(const uint16_t* __restrict__ x, const uint16_t* __restric
 // power-of-two scale per ROW (term t: row scale / 16^t) instead of per 32-block scales; it is
 // applied by the GEMM epilogue when it adds the terms' columns, so the tensor core sees unit
 // activation scales and no activation scale factor ever travels (split_rows_stacked_kernel).
+// Bytes the scale atoms take at the head of a sequential block: TERMS x 512 B, rounded up to the
+// 1024-byte alignment the 128-byte-swizzled row groups behind them need.
+__host__ __device__ constexpr int act_header_bytes(int terms) { return (terms * 512 + 1023) / 1024 * 1024; }
+
 __host__ __device__ inline size_t act_block_bytes(int terms, int tile_tokens, bool stacked) {
     if (stacked) return (size_t)terms * tile_tokens * 128;
-    return (size_t)terms * 512 + (size_t)(tile_tokens / 8) * terms * 1024;
+    return (size_t)act_header_bytes(terms) + (size_t)(tile_tokens / 8) * terms * 1024;
 }
 
 template <int TERMS, bool FROM_BF16, bool STACK>
@@ -358,7 +362,7 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
         // row of this term inside the block and the place of its scale word
         const int n = STACK ? t * npad + j : j;
         uint8_t* row_ptr = STACK ? blk + 1024 + (size_t)(n >> 3) * 1024
-                                 : blk + TERMS * 512 + ((size_t)(n >> 3) * TERMS + t) * 1024;
+                                 : blk + act_header_bytes(TERMS) + ((size_t)(n >> 3) * TERMS + t) * 1024;
         *reinterpret_cast<uint32_t*>(row_ptr + (n & 7) * 128 + (((lane >> 2) ^ (n & 7)) << 4) + ((lane & 3) << 2)) =
             (uint32_t)lo | ((uint32_t)hi << 16);
         if (t + 1 < TERMS) {
@@ -570,7 +574,7 @@ struct GmmSmem {
     static_assert(!MX4 || STACK, "packed 4-bit operands are a stacked-mode feature");
     static constexpr int kABytes = MX4 ? 8192 : 16384;  // one 128 x 128 weight box in shared memory
     static constexpr int kActBytes = MX4 ? TERMS * BN_MAX * 64
-                                         : (STACK ? TERMS * BN_MAX * 128 : TERMS * 512 + (BN_MAX / 8) * TERMS * 1024);
+                                         : (STACK ? TERMS * BN_MAX * 128 : act_header_bytes(TERMS) + (BN_MAX / 8) * TERMS * 1024);
     static constexpr int kStage = (KC * (kABytes + kActBytes + 512) + 1023) / 1024 * 1024;
     static constexpr int kSfCols = KC * (STACK ? 4 : 4 * (1 + TERMS));  // TMEM columns of scales per stage
     static constexpr int kAccCols = STACK ? TERMS * BN_MAX : BN_MAX;    // TMEM columns of one accumulator buffer
@@ -653,7 +657,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             const int tile = item / p.m_tiles, m = item - tile * p.m_tiles;
             const int e = p.tile_expert[tile], rows = p.tile_rows[tile];
             const uint32_t act_bytes = MX4 ? TERMS * ((rows + 7) >> 3) * 512 : STACK ? TERMS * ((rows + 7) >> 3) * 1024
-                                             : TERMS * 512 + ((rows + 7) >> 3) * TERMS * 1024;
+                                             : act_header_bytes(TERMS) + ((rows + 7) >> 3) * TERMS * 1024;
             const uint32_t box = (uint32_t)((e * p.m_tiles + m) * p.n_chunks);
             int box_row = (int)(box * 128);
             const uint8_t* sfa_src = p.sfa + (size_t)box * 512;
@@ -759,7 +763,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                             for (int t = 0; t < TERMS; ++t) tc_copy_sf(sf_tmem + 4 * (1 + t), make_sf_desc(act_smem + 512 * t));
 #pragma unroll
                             for (int t = 0; t < TERMS; ++t) {
-                                const uint64_t b_desc = make_sw128_desc(act_smem + TERMS * 512 + t * 1024, TERMS * 1024);
+                                const uint64_t b_desc = make_sw128_desc(act_smem + act_header_bytes(TERMS) + t * 1024, TERMS * 1024);
 #pragma unroll
                                 for (int j = 0; j < 4; ++j)
                                     mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * kIdescStep, sf_tmem,

@@ -331,6 +331,11 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
     return NEON_MOE_OK;
 }
 
+// e4m3 terms of the fp32 SwiGLU output fed to the down product of 128-token (prefill) tiles.  Each
+// term carries ~4 significant bits; three would already meet the accuracy contract (measured
+// max-abs 3.4e-3 at T=256) but were measured no faster (0.762 vs 0.757 ms at T=4096: that launch is
+// bound by activation traffic, not by the tensor cores), so four stay for the extra accuracy.
+constexpr int kDownTermsPrefill = 4;
 constexpr int kMx4Terms = 6;  // e2m1 terms per activation value on the packed 4-bit path
 
 template <int TERMS, bool GATE_UP>
@@ -567,7 +572,10 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         mark(h, st, prof);
         // |SwiGLU| <= limit * (limit + 1): a fixed bound replaces the row maximum
         const float a_bound = h->cfg.swiglu_limit * (h->cfg.swiglu_limit + 1.f);
-        launch_split<4, false>(h, tt_dn, tld, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
+        if (tt_dn > 32)
+            launch_split<kDownTermsPrefill, false>(h, tt_dn, tld, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
+        else
+            launch_split<4, false>(h, tt_dn, tld, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
         const bool mx4_dn = tt_dn <= 32 && h->mx4;
         DBG_SYNC(h, st, "split_rows (activation)");
         // down: rows H, K = I
@@ -580,7 +588,8 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
             if (mx4_dn) g.row_scale_const = a_bound * (1.f / 6.f);  // split_rows_fp4_kernel's first-term scale
         }
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
-        rc = launch_gmm<4, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st);
+        rc = tt_dn > 32 ? launch_gmm<kDownTermsPrefill, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st)
+                        : launch_gmm<4, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st);
         if (rc) return rc;
         DBG_SYNC(h, st, "gmm_bs_kernel down");
         mark(h, st, prof);

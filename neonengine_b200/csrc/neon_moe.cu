@@ -53,6 +53,7 @@ struct neon_moe_handle {
     uint32_t a_tx_bytes = 8192;   // bytes one 128x128 4-bit box adds to its mbarrier
     int max_stages = 0, ctas_per_sm = 1;
     int pdl = 1;                  // programmatic dependent launch between the kernels of a pass
+    int tile_override = 0;        // 0 = token-tile size chosen from the batch size; 16 / 32 / 128 force it
     int sync_debug = 0;           // synchronise and check after every kernel (slow; names the failing kernel)
     long long* trace = nullptr;
     uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
@@ -305,6 +306,7 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
 // Token-tile size: decode batches use small tiles with the activation terms stacked along N
 // (one MMA per k-block reads the weight tile once); larger batches use 128-token tiles.
 int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 64 ? 32 : 128); }
+int tile_tokens_for(const neon_moe_handle* h, int T) { return h->tile_override ? h->tile_override : tile_tokens_for(T); }
 
 template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC, bool MX4 = false>
 int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap& tm2, GmmParams p, cudaStream_t st) {
@@ -534,7 +536,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
     const int n = rows * k_eff;
     DispatchArrays d{h->count, h->offset, h->perm, h->inv};
     if (h->path == 2) {
-        const int tt = tile_tokens_for(rows), tt2 = 0, tt_dn = tt;  // one tile list serves both products
+        const int tt = tile_tokens_for(h, rows), tt2 = 0, tt_dn = tt;  // one tile list serves both products
         TileList tl{h->tile_expert, h->tile_row0, h->tile_rows, h->n_tiles, h->row_tile};
         TileList tl2{h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2};
         const TileList& tld = tt2 ? tl2 : tl;
@@ -734,12 +736,14 @@ static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const fl
         TileList tl{h->tile_expert, h->tile_row0, h->tile_rows, h->n_tiles, h->row_tile};
         launch_k(h->pdl != 0, router_dispatch_kernel, dim3(T), dim3(1024), smem, st, static_cast<const uint16_t*>(hidden),
                  (const uint16_t*)h->router_w, (const uint16_t*)h->router_b, logit_bias, T, H, E, k, h->idx, h->route_w, h->x_amax,
-                 h->route_done, d, tile_tokens_for(T), tl);
+                 h->route_done, d, tile_tokens_for(h, T), tl);
         h->launches++;
     } else {
         launch_router(h, hidden, T, logit_bias, h->idx, h->route_w, h->x_amax, st);
     }
-    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, h->path == 2 ? h->x_amax : nullptr, out, st, prof, fused);
+    // the token maxima come from the decode routers only (the token-blocked router does not produce them)
+    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, (h->path == 2 && T <= 64) ? h->x_amax : nullptr, out, st, prof,
+                          fused);
     if (rc) return rc;
     if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
     if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
@@ -931,6 +935,9 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->pdl = (int)value;
     } else if (!strcmp(name, "fuse_dispatch")) {
         h->fuse_dispatch = (int)value;
+    } else if (!strcmp(name, "tile_tokens")) {
+        if (value != 0 && value != 16 && value != 32 && value != 128) return fail(h, NEON_MOE_EINVAL, "tile_tokens must be 0, 16, 32 or 128");
+        h->tile_override = (int)value;
     } else if (!strcmp(name, "mx4")) {
         h->mx4 = (int)value;
     } else if (!strcmp(name, "use_graphs")) {

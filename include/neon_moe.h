@@ -106,6 +106,14 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden_bf16, int T, const f
 int neon_moe_forward_host(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
                           float* out_f32, int32_t* topk_idx, float* topk_w);
 
+/* A run of n_batches passes over HOST memory (T tokens each; hidden[i] bf16 [T,H] in, out[i] fp32
+ * [T,H] out; the same optional logit_bias for all), pipelined: the upload of batch i+1 and the
+ * download of batch i-1 overlap the layer pass of batch i on separate copy streams with two
+ * staging sets, so with pinned host buffers the run proceeds at the device's pace.  Returns when
+ * every result is in host memory.  Results equal n_batches calls of neon_moe_forward_host. */
+int neon_moe_forward_host_batches(neon_moe_handle* h, const void* const* hidden_bf16, int n_batches, int T,
+                                  const float* logit_bias, float* const* out_f32);
+
 /* ---- Expert parallelism (n_experts sharded evenly over ep_size GPUs of one node) -----------
  * The engine is single-GPU (NeonEngine/src/lve_device.cpp:125-148 picks one device), so these
  * have no engine counterpart; they follow the same conventions as neon_moe_forward.

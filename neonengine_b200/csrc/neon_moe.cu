@@ -92,6 +92,11 @@ struct neon_moe_handle {
     // staging for the host-buffer entry point
     uint16_t* st_hidden = nullptr;
     float *st_out = nullptr, *st_bias = nullptr;
+    // second staging set, copy streams and events of the pipelined host-batches call (created on first use)
+    uint16_t* st_hidden2 = nullptr;
+    float* st_out2 = nullptr;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_in[2] = {}, ev_comp[2] = {}, ev_out[2] = {};
 };
 
 namespace {
@@ -156,7 +161,7 @@ int dev_alloc(neon_moe_handle* h, T** p, size_t count) {
 void free_all(neon_moe_handle* h) {
     void* ptrs[] = {h->router_w, h->router_b, h->gu_bias, h->dn_bias, h->gu_wq, h->dn_wq, h->gu_sq, h->dn_sq,
                     h->idx, h->count, h->offset, h->perm, h->inv, h->route_w, h->y, h->a_hi, h->a_lo,
-                    h->status, h->st_hidden, h->st_out, h->st_bias, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
+                    h->status, h->st_hidden, h->st_out, h->st_bias, h->st_hidden2, h->st_out2, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
                     h->x_act, h->a_act, h->x_scale, h->a_scale, h->x_amax, h->a_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
                     h->n_tiles, h->row_tile, h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
                     h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv};
@@ -169,6 +174,11 @@ void free_all(neon_moe_handle* h) {
     for (auto& g : h->graphs)
         if (g.exec) cudaGraphExecDestroy(g.exec);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    if (h->s_in) cudaStreamDestroy(h->s_in);
+    if (h->s_out) cudaStreamDestroy(h->s_out);
+    for (int b = 0; b < 2; ++b)
+        for (cudaEvent_t e : {h->ev_in[b], h->ev_comp[b], h->ev_out[b]})
+            if (e) cudaEventDestroy(e);
     for (cudaEvent_t ev : h->events) cudaEventDestroy(ev);
 }
 
@@ -897,6 +907,57 @@ int neon_moe_forward_host(neon_moe_handle* h, const void* hidden, int T, const f
     if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, n * 4, cudaMemcpyDeviceToHost, st));
     if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, n * 4, cudaMemcpyDeviceToHost, st));
     CU(h, cudaStreamSynchronize(st));
+    return NEON_MOE_OK;
+}
+
+int neon_moe_forward_host_batches(neon_moe_handle* h, const void* const* hidden, int n_batches, int T,
+                                  const float* logit_bias, float* const* out) {
+    if (!h) return NEON_MOE_EINVAL;
+    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
+    if (n_batches < 0) return fail(h, NEON_MOE_EINVAL, "negative batch count");
+    if (T == 0 || n_batches == 0) return NEON_MOE_OK;
+    if (!hidden || !out) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
+    for (int i = 0; i < n_batches; ++i)
+        if (!hidden[i] || !out[i]) return fail(h, NEON_MOE_EINVAL, "null buffer of batch %d", i);
+    CU(h, cudaSetDevice(h->cfg.device));
+    if (!h->s_in) {  // first use: second staging set, two copy streams, events
+        int rc;
+        if ((rc = dev_alloc(h, &h->st_hidden2, (size_t)h->cfg.max_tokens * h->cfg.hidden)) ||
+            (rc = dev_alloc(h, &h->st_out2, (size_t)h->cfg.max_tokens * h->cfg.hidden)))
+            return rc;
+        CU(h, cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking));
+        CU(h, cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking));
+        for (int b = 0; b < 2; ++b) {
+            CU(h, cudaEventCreateWithFlags(&h->ev_in[b], cudaEventDisableTiming));
+            CU(h, cudaEventCreateWithFlags(&h->ev_comp[b], cudaEventDisableTiming));
+            CU(h, cudaEventCreateWithFlags(&h->ev_out[b], cudaEventDisableTiming));
+        }
+    }
+    cudaStream_t sc = h->own_stream;
+    const size_t nh = (size_t)T * h->cfg.hidden;
+    if (logit_bias) {
+        CU(h, cudaMemcpyAsync(h->st_bias, logit_bias, (size_t)h->cfg.n_experts * 4, cudaMemcpyHostToDevice, sc));
+        CU(h, cudaStreamSynchronize(sc));
+    }
+    uint16_t* in_buf[2] = {h->st_hidden, h->st_hidden2};
+    float* out_buf[2] = {h->st_out, h->st_out2};
+    for (int i = 0; i < n_batches; ++i) {
+        const int b = i & 1;
+        // upload batch i while batch i-1 computes; its staging buffer is free once batch i-2 has computed
+        if (i >= 2) CU(h, cudaStreamWaitEvent(h->s_in, h->ev_comp[b], 0));
+        CU(h, cudaMemcpyAsync(in_buf[b], hidden[i], nh * 2, cudaMemcpyHostToDevice, h->s_in));
+        CU(h, cudaEventRecord(h->ev_in[b], h->s_in));
+        CU(h, cudaStreamWaitEvent(sc, h->ev_in[b], 0));
+        if (i >= 2) CU(h, cudaStreamWaitEvent(sc, h->ev_out[b], 0));  // batch i-2's result has left the output buffer
+        int rc = neon_moe_forward(h, in_buf[b], T, logit_bias ? h->st_bias : nullptr, out_buf[b], nullptr, nullptr, sc);
+        if (rc) return rc;
+        CU(h, cudaEventRecord(h->ev_comp[b], sc));
+        CU(h, cudaStreamWaitEvent(h->s_out, h->ev_comp[b], 0));
+        CU(h, cudaMemcpyAsync(out[i], out_buf[b], nh * 4, cudaMemcpyDeviceToHost, h->s_out));
+        CU(h, cudaEventRecord(h->ev_out[b], h->s_out));
+    }
+    CU(h, cudaStreamSynchronize(h->s_out));
+    CU(h, cudaStreamSynchronize(sc));
     return NEON_MOE_OK;
 }
 

@@ -169,6 +169,17 @@ class MoeLayerSystem:
         self._check(self._lib.neon_moe_forward_host(self._h, hidden_ptr, T, logit_bias_ptr, out_ptr, None, None),
                     "neon_moe_forward_host")
 
+    def run_host_batches(self, hidden_ptrs, T: int, logit_bias_ptr, out_ptrs) -> None:
+        """A run of passes over host buffers given by address (pinned memory for real overlap):
+        uploads, layer passes and downloads of consecutive batches are pipelined."""
+        n = len(hidden_ptrs)
+        assert len(out_ptrs) == n
+        hp = (ctypes.c_void_p * n)(*hidden_ptrs)
+        op = (ctypes.c_void_p * n)(*out_ptrs)
+        self._check(self._lib.neon_moe_forward_host_batches(self._h, hp, n, int(T),
+                                                            None if not logit_bias_ptr else ctypes.c_void_p(logit_bias_ptr), op),
+                    "neon_moe_forward_host_batches")
+
     def read_dispatch(self):
         n = ctypes.c_int(0)
         self._check(self._lib.neon_moe_read_dispatch(self._h, None, None, None, None, ctypes.byref(n)), "read_dispatch")

@@ -255,3 +255,18 @@ def test_fused_router_dispatch_equals_separate_kernels(full20b):
                 np.testing.assert_array_equal(a, b)
     finally:
         layer.set_option("fuse_dispatch", 0)
+
+
+def test_pipelined_host_batches_equal_blocking_calls(full20b):
+    """neon_moe_forward_host_batches: same results as one blocking host call per batch."""
+    import torch
+    shape, W, layer = full20b
+    T, n = 16, 7
+    hs = [torch.from_numpy(synth.make_hidden(T, W, 60 + i).view(np.int16)).pin_memory() for i in range(n)]
+    outs = [torch.zeros((T, shape.hidden), dtype=torch.float32).pin_memory() for _ in range(n)]
+    layer.run_host_batches([h.data_ptr() for h in hs], T, None, [o.data_ptr() for o in outs])
+    for h, o in zip(hs, outs):
+        ref = layer.run_host(h.numpy().view(np.uint16))
+        ref = ref[0] if isinstance(ref, tuple) else ref
+        np.testing.assert_array_equal(o.numpy(), ref)
+    assert layer.status() == 0

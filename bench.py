@@ -503,8 +503,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA GPU: the MoE layer has no CPU path")
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner out of the one-JSON-line stdout
+    # NCCL prints its version banner (levels VERSION and WARN) to stdout by default: send its log to
+    # stderr so that stdout carries the one JSON line only
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))

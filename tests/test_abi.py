@@ -99,3 +99,16 @@ def test_product_does_not_import_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"(import\s+oracle|from\s+oracle|moe_oracle|oracle/)", text), \
                     f"{f} reaches into the oracle"
+
+
+def test_cpp_wrappers_compile():
+    """The header-only engine-style C++ owners of the handles compile as C++17."""
+    import subprocess
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "check.cpp")
+        with open(src, "w") as f:
+            f.write('#include "lve_moe_layer_system.hpp"\n#include "lve_water_physics.hpp"\nint main() { return 0; }\n')
+        res = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I" + os.path.join(ROOT, "include"), src],
+                             capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr

@@ -418,18 +418,21 @@ k_jacobi_fused(WP q, const unsigned* __restrict__ flags, const float* __restrict
         // grid barrier number it + 1: all CTAs have added 1 when the counter reaches (it + 1) * gridDim.x
         __syncthreads();
         if (threadIdx.x == 0) {
-            __threadfence();
-            atomicAdd(bar, 1u);
+            // arrive with release semantics (orders this CTA's stores, made visible to thread 0 by the
+            // barrier above, before the count), then poll with acquire loads
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(bar) : "memory");
             const unsigned target = (unsigned)(it + 1) * gridDim.x;
             long long spins = 0;
-            while (*reinterpret_cast<volatile unsigned*>(bar) < target) {
+            for (;;) {
+                unsigned seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar) : "memory");
+                if (seen >= target) break;
                 if (++spins > 2000000ll || *reinterpret_cast<volatile int*>(status) != 0) {
                     atomicExch(status, 1);
                     give_up = 1;
                     break;
                 }
             }
-            __threadfence();
         }
         __syncthreads();
         if (give_up) return;

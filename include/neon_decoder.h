@@ -96,7 +96,8 @@ int neon_decoder_load_kv(neon_decoder_handle* h, int layer, const void* k, const
 /* One decode step for `batch` sequences, enqueued on cuda_stream.  Device pointers:
  * tokens int32 [batch]; positions int32 [batch] (each < max_ctx; the new K/V go to that cache
  * slot and attention covers positions <= it); logits fp32 [batch, vocab] or NULL (internal
- * buffer); next_tokens int32 [batch] or NULL.  The second call with the same arguments is
+ * buffer); next_tokens int32 [batch] or NULL.  Token ids and positions outside their ranges are
+ * clamped into range by the kernels (they live in device memory, so the host cannot check them).  The second call with the same arguments is
  * captured into a CUDA graph and replayed from then on (option use_graphs). */
 int neon_decoder_step(neon_decoder_handle* h, const int32_t* tokens, const int32_t* positions, int batch,
                       float* logits, int32_t* next_tokens, void* cuda_stream);

@@ -18,12 +18,13 @@ constexpr int kDecMaxBatch = 8;
 __device__ __forceinline__ uint16_t f32_to_bf16_rn(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
 
 // x[b, :] = embed[token[b], :] (bf16 -> fp32 residual stream).
-__global__ void embed_kernel(const uint16_t* __restrict__ embed, const int32_t* __restrict__ tokens, int H,
+// Token ids outside [0, vocab) are clamped into range rather than read out of bounds.
+__global__ void embed_kernel(const uint16_t* __restrict__ embed, const int32_t* __restrict__ tokens, int H, int vocab,
                              float* __restrict__ x) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
-    const uint16_t* row = embed + (size_t)tokens[b] * H;
+    const uint16_t* row = embed + (size_t)min(max(tokens[b], 0), vocab - 1) * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) x[(size_t)b * H + i] = bf16_bits_to_float(row[i]);
 }
 
@@ -285,7 +286,7 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(float* __restrict__ qkv,
     const int head = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    const int p = pos[b];
+    const int p = min(max(pos[b], 0), ctx - 1);  // positions outside the cache are clamped, never written out of bounds
     float* hrow = qkv + ((size_t)b * (nq + 2 * nkv) + head) * D;
     float mine = hrow[j];  // element j of the head, parts summed
     for (int i = 1; i < n_parts; ++i) mine += hrow[(size_t)i * part_stride + j];
@@ -369,7 +370,7 @@ __global__ void __launch_bounds__(256, 3) attn_partial_kernel(const float* __res
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     pdl_launch_dependents();
     pdl_wait();
-    const int p = pos[b];
+    const int p = min(max(pos[b], 0), ctx - 1);
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int s0 = (lo & ~7) + sp * kAttnChunk;
     float* dst = part + (((size_t)b * nq + kvh * G) * splits + sp) * (D + 2);

@@ -201,7 +201,7 @@ int step_eager(neon_decoder_handle* h, const int32_t* tokens, const int32_t* pos
                cudaStream_t st) {
     const auto& c = h->cfg;
     const int H = c.hidden, QKV = (c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim, QD = c.n_q_heads * c.head_dim;
-    launch(h, kPdlOther, embed_kernel, dim3(B), dim3(256), 0, st, (const uint16_t*)h->embed, tokens, H, h->x);
+    launch(h, kPdlOther, embed_kernel, dim3(B), dim3(256), 0, st, (const uint16_t*)h->embed, tokens, H, c.vocab, h->x);
     const int n_layers = h->stop_after > 0 ? std::min(h->stop_after, c.n_layers) : c.n_layers;
     const float* pending = nullptr;  // MoE output of the previous layer, added by the next RMSNorm kernel
     for (int l = 0; l < n_layers; ++l) {

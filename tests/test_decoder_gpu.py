@@ -200,3 +200,50 @@ def test_full_width_layer_matches_oracle():
         ea, er = errors(s.read("logits", B), ref["logits"])
         assert ea <= MAX_ABS_TOL and er <= MEAN_REL_TOL, (ea, er)
         s.close()
+
+
+def test_generation_over_several_steps_matches_oracle():
+    """Three consecutive decode steps with advancing positions: the K/V the earlier steps appended
+    are what the later steps attend to.  The oracle follows the device's token choices and, per
+    layer, the device's own bf16 MoE input (so routing is compared on equal bits)."""
+    from oracle import decoder_oracle as dor
+    shape = _small_shape()
+    B, ctx = 3, 32
+    w, s, kc, vc, moe_fn = _setup(shape, B, ctx, seed=17)
+    tokens = np.array([5, 99, 300], np.int32)
+    pos = np.array([10, 0, 28], np.int32)
+    for step in range(3):
+        t_dev, p_dev = torch.from_numpy(tokens).cuda(), torch.from_numpy(pos).cuda()
+        nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
+        override = {}
+        for l in range(shape.n_layers):
+            s.set_option("stop_after_layer", l + 1)
+            s.step(t_dev, p_dev)
+            override[l] = s.read("moe_in", B)
+        s.set_option("stop_after_layer", 0)
+        s.step(t_dev, p_dev, next_tokens=nxt)
+        ref = dor.decoder_step(w, kc, vc, tokens, pos, moe_fn, moe_in_override=override)
+        logits = s.read("logits", B)
+        ea, er = errors(logits, ref["logits"])
+        assert ea <= MAX_ABS_TOL and er <= MEAN_REL_TOL, (step, ea, er)
+        got = nxt.cpu().numpy()
+        np.testing.assert_array_equal(got, np.argmax(logits, axis=-1))
+        tokens, pos = got.astype(np.int32), pos + 1
+    s.close()
+
+
+def test_out_of_range_tokens_and_positions_are_clamped():
+    shape = _small_shape(1)
+    B, ctx = 2, 16
+    w, s, kc, vc, moe_fn = _setup(shape, B, ctx, seed=2)
+    good = (torch.tensor([shape.vocab - 1, 0], dtype=torch.int32, device="cuda"),
+            torch.tensor([ctx - 1, 0], dtype=torch.int32, device="cuda"))
+    bad = (torch.tensor([shape.vocab + 1000, -7], dtype=torch.int32, device="cuda"),
+           torch.tensor([ctx + 50, -3], dtype=torch.int32, device="cuda"))
+    s.set_option("use_graphs", 0)
+    s.step(*good)
+    a = s.read("logits", B).copy()
+    s.step(*bad)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(s.read("logits", B), a)
+    s.close()

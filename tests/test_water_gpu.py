@@ -145,3 +145,30 @@ def test_rejects_bad_arguments():
     with pytest.raises(RuntimeError, match="unknown grid"):
         sim.read_grid("vorticity")
     sim.close()
+
+
+def test_fine_grid_beyond_the_fused_kernel_limit():
+    """Half the cell size: 1.25 M cells, more than the cooperative Jacobi kernel covers (two cells
+    per resident thread), so the step falls back to one launch per iteration, and the prefix sum
+    runs over more than 1024 blocks.  Still bit-exact."""
+    cfg = dataclasses.replace(WaterConfig(), cell_size=0.05, jacobi_iterations=12)
+    assert cfg.n_cells > 2 * 148 * 1024
+    pos0 = spawn_particles(cfg)
+    sim = _gpu(cfg, pos0)
+    sim.run_simulation(2)
+    pos, vel = pos0.copy(), np.zeros_like(pos0)
+    grids = water.step(oracle_params(cfg), pos, vel, 2, collision_mode=1)
+    _compare(sim, pos, vel, grids)
+    sim.close()
+
+
+def test_more_particles_than_the_demo():
+    """27 000 particles (30^3) in the demo box: groups, boxes and bins at a larger size."""
+    cfg = dataclasses.replace(WaterConfig(), particles_per_side=30, jacobi_iterations=10, collision_substeps=2)
+    pos0 = spawn_particles(cfg)
+    sim = _gpu(cfg, pos0)
+    sim.run_simulation(1)
+    pos, vel = pos0.copy(), np.zeros_like(pos0)
+    grids = water.step(oracle_params(cfg), pos, vel, 1, collision_mode=1)
+    _compare(sim, pos, vel, grids)
+    sim.close()

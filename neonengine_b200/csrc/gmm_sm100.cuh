@@ -810,37 +810,102 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             float bias = 0.f;
             if (GATE_UP) bias = bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + 2 * ch + (lane >> 4)]);
             else if (valid) bias = bf16_bits_to_float(p.bias[(size_t)e * p.rows_total + row]);
-            for (int j8 = 0; j8 < npad; j8 += 8) {
-                float v[8];
-                tmem_ld8(taddr + j8, v);
-                if (STACK) {  // add the other terms' columns (term t carries 16^-t), then the row's scale
-                    float f = 1.f;
+            // Per-token factors are fetched once per item, one token per lane (32 at a time), and handed
+            // round by shuffles: the store loop below then has no dependent global loads.
+            constexpr int NW = (BN_MAX + 31) / 32;
+            float tok_scale[NW], tok_w[NW];
 #pragma unroll
+            for (int k = 0; k < NW; ++k) {
+                const int tix = 32 * k + lane;
+                const bool in = tix < rows;
+                tok_scale[k] = STACK ? (in ? (p.row_scale ? p.row_scale[row0 + tix] : p.row_scale_const) : 0.f) : 1.f;
+                tok_w[k] = (!GATE_UP && in) ? p.route_w[p.perm[row0 + tix]] : 0.f;
+            }
+            // one token's value of this lane's row: bias, then SwiGLU (gate_up) or the routing weight (down)
+            auto finish = [&](int tix, float acc, float w_tok) {
+                const int pos = row0 + tix;
+                const float mine = acc + bias;
+                if (GATE_UP) {
+                    const float lin = __shfl_down_sync(0xffffffffu, mine, 16);
+                    if (lane < 16 && tix < rows) {
+                        const float g = fminf(mine, p.limit);
+                        const float l = fminf(fmaxf(lin, -p.limit), p.limit);
+                        p.a_out[(size_t)pos * p.inter + ch] = g / (1.f + expf(-p.alpha * g)) * (l + 1.f);
+                    }
+                } else if (valid && tix < rows) {
+                    p.y[(size_t)pos * p.hidden + row] = w_tok * mine;
+                }
+            };
+            if (BN_MAX <= 32) {
+                // decode tiles: pull the whole accumulator row into registers, hand the TMEM buffer back
+                // to the MMA warp at once, and only then do the arithmetic and the global stores
+                float vals[BN_MAX];
 #pragma unroll
-                    for (int t = 1; t < TERMS; ++t) {
-                        f *= MX4 ? (1.f / 6.f) : 0.0625f;
-                        float u[8];
-                        tmem_ld8(taddr + t * npad + j8, u);
+                for (int j8 = 0; j8 < BN_MAX; j8 += 8) {
+                    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    if (j8 < npad) {
+                        tmem_ld8(taddr + j8, v);
+                        if (STACK) {  // add the other terms' columns (term t carries 16^-t)
+                            float f = 1.f;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) v[i] = fmaf(u[i], f, v[i]);
+                            for (int t = 1; t < TERMS; ++t) {
+                                f *= MX4 ? (1.f / 6.f) : 0.0625f;
+                                float u[8];
+                                tmem_ld8(taddr + t * npad + j8, u);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) v[i] = fmaf(u[i], f, v[i]);
+                            }
+                        }
                     }
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        v[i] *= (j8 + i < rows) ? (p.row_scale ? p.row_scale[row0 + j8 + i] : p.row_scale_const) : 0.f;
+                    for (int i = 0; i < 8; ++i) vals[j8 + i] = v[i];
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[b]);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int pos = row0 + j8 + i;
-                    const float mine = v[i] + bias;
-                    if (GATE_UP) {
-                        const float lin = __shfl_down_sync(0xffffffffu, mine, 16);
-                        if (lane < 16 && j8 + i < rows) {
-                            const float g = fminf(mine, p.limit);
-                            const float l = fminf(fmaxf(lin, -p.limit), p.limit);
-                            p.a_out[(size_t)pos * p.inter + ch] = g / (1.f + expf(-p.alpha * g)) * (l + 1.f);
+                for (int j = 0; j < BN_MAX; ++j) {
+                    if (j < npad) {  // uniform over the warp
+                        const float sc = STACK ? __shfl_sync(0xffffffffu, tok_scale[0], j) : 1.f;
+                        const float wt = GATE_UP ? 0.f : __shfl_sync(0xffffffffu, tok_w[0], j);
+                        finish(j, STACK ? vals[j] * sc : vals[j], wt);
+                    }
+                }
+                continue;
+            }
+#pragma unroll
+            for (int k = 0; k < NW; ++k) {
+                const int jend = min(npad, 32 * (k + 1));
+                for (int j8 = 32 * k; j8 < jend; j8 += 8) {
+                    float v[8];
+                    tmem_ld8(taddr + j8, v);
+                    if (STACK) {
+                        float f = 1.f;
+#pragma unroll
+                        for (int t = 1; t < TERMS; ++t) {
+                            f *= MX4 ? (1.f / 6.f) : 0.0625f;
+                            float u[8];
+                            tmem_ld8(taddr + t * npad + j8, u);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) v[i] = fmaf(u[i], f, v[i]);
                         }
-                    } else if (valid && j8 + i < rows) {
-                        p.y[(size_t)pos * p.hidden + row] = p.route_w[p.perm[pos]] * mine;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int tix = j8 + i, pos = row0 + tix;
+                        const float sc = STACK ? __shfl_sync(0xffffffffu, tok_scale[k], tix & 31) : 1.f;
+                        const float mine = (STACK ? v[i] * sc : v[i]) + bias;
+                        if (GATE_UP) {
+                            const float lin = __shfl_down_sync(0xffffffffu, mine, 16);
+                            if (lane < 16 && tix < rows) {
+                                const float g = fminf(mine, p.limit);
+                                const float l = fminf(fmaxf(lin, -p.limit), p.limit);
+                                p.a_out[(size_t)pos * p.inter + ch] = g / (1.f + expf(-p.alpha * g)) * (l + 1.f);
+                            }
+                        } else {
+                            const float wt = __shfl_sync(0xffffffffu, tok_w[k], tix & 31);
+                            if (valid && tix < rows) p.y[(size_t)pos * p.hidden + row] = wt * mine;
+                        }
                     }
                 }
             }

@@ -653,9 +653,20 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         // stage's three copies.  Stage index, phase and global addresses are carried
         // incrementally: every extra instruction in this loop costs ~10 cycles per stage.
         int s = 0, ph = 0, tr = 0;
+        // the next item's tile record is fetched one item ahead, off the critical path
+        int next_e = 0, next_rows = 0;
+        if ((int)blockIdx.x < n_items) {
+            next_e = p.tile_expert[blockIdx.x / p.m_tiles];
+            next_rows = p.tile_rows[blockIdx.x / p.m_tiles];
+        }
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int tile = item / p.m_tiles, m = item - tile * p.m_tiles;
-            const int e = p.tile_expert[tile], rows = p.tile_rows[tile];
+            const int e = next_e, rows = next_rows;
+            if (item + (int)gridDim.x < n_items) {
+                const int nt = (item + (int)gridDim.x) / p.m_tiles;
+                next_e = p.tile_expert[nt];
+                next_rows = p.tile_rows[nt];
+            }
             const uint32_t act_bytes = MX4 ? TERMS * ((rows + 7) >> 3) * 512 : STACK ? TERMS * ((rows + 7) >> 3) * 1024
                                              : act_header_bytes(TERMS) + ((rows + 7) >> 3) * TERMS * 1024;
             const uint32_t box = (uint32_t)((e * p.m_tiles + m) * p.n_chunks);
@@ -714,9 +725,10 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 }
                 __syncwarp();
             }
+            int next_rows = (int)blockIdx.x < n_items ? p.tile_rows[blockIdx.x / p.m_tiles] : 0;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
-                const int tile = item / p.m_tiles;
-                const int rows = p.tile_rows[tile];
+                const int rows = next_rows;  // fetched one item ahead
+                if (item + (int)gridDim.x < n_items) next_rows = p.tile_rows[(item + (int)gridDim.x) / p.m_tiles];
                 const int npad = (rows + 7) & ~7;
                 const uint32_t n_mma = STACK ? (uint32_t)(TERMS * npad) : (uint32_t)max(16, round_up_int(rows, 16));
                 const uint32_t idesc0 = MX4 ? make_idesc_bs(1, 1, n_mma, 0, 0) : make_idesc_bs(5, 0, n_mma, 0, 0);

@@ -56,6 +56,7 @@ struct neon_moe_handle {
     int tile_override = 0;        // 0 = token-tile size chosen from the batch size; 16 / 32 / 128 force it
     int sync_debug = 0;           // synchronise and check after every kernel (slow; names the failing kernel)
     long long* trace = nullptr;
+    int trace_which = 0;  // 0 = both products (the down product overwrites), 1 = gate_up only, 2 = down only
     uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
     float *x_scale = nullptr, *a_scale = nullptr;  // per-row activation scales (stacked mode)
     float *x_amax = nullptr, *a_amax = nullptr;    // largest magnitude per source row / per sorted row
@@ -570,7 +571,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         launch_split<2, true>(h, tt, tl, hidden, H, n, k_eff, hidden_amax, 0.f, h->x_act, h->x_scale, st);
         DBG_SYNC(h, st, "split_rows (hidden)");
         GmmParams g{};
-        g.a_tx_bytes = h->a_tx_bytes; g.trace = h->trace;
+        g.a_tx_bytes = h->a_tx_bytes; g.trace = h->trace_which == 2 ? nullptr : h->trace;
         g.a_out = h->a_f32; g.inter = I; g.limit = h->cfg.swiglu_limit; g.alpha = h->cfg.swiglu_alpha;
         g.perm = h->perm; g.route_w = route_w; g.y = h->y; g.hidden = H; g.status = h->status;
         // gate_up: rows 2I, K = H
@@ -600,6 +601,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
             if (mx4_dn) g.row_scale_const = a_bound * (1.f / 6.f);  // split_rows_fp4_kernel's first-term scale
         }
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
+        g.trace = h->trace_which == 1 ? nullptr : h->trace;
         rc = tt_dn > 32 ? launch_gmm<kDownTermsPrefill, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st)
                         : launch_gmm<4, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st);
         if (rc) return rc;
@@ -988,6 +990,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->a_tx_bytes = (uint32_t)value;
     } else if (!strcmp(name, "trace_ptr")) {
         h->trace = reinterpret_cast<long long*>(value);
+    } else if (!strcmp(name, "trace_which")) {
+        h->trace_which = (int)value;
     } else if (!strcmp(name, "ctas_per_sm")) {
         h->ctas_per_sm = (int)value;
     } else if (!strcmp(name, "n_ctas")) {

@@ -58,6 +58,28 @@ WORKLOADS = {
 }
 
 
+_JSON_FD = None
+
+
+def claim_stdout():
+    """Libraries (NCCL's version banner, for one) write to file descriptor 1.  From here on fd 1 is
+    stderr for everybody; the one JSON line goes to the original stdout through emit()."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -168,7 +190,7 @@ def run_reference(args, rank):
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                              "sample": f"{args.steps} steps of {sample_T} tokens (CPU oracle, OpenMP, fp64 accumulate)"},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def decoder_cpu_sample(vocab_slice=8192):
@@ -249,7 +271,7 @@ def run_water_reference(args):
             "config": {"workload": "water", "description": WORKLOADS["water"][3]},
             "cpu_baseline": {"value": sps, "unit": "steps/s", "cores": 1, "kind": kind, "sample": desc},
             "e2e": {"value": sps, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_water(args, local_rank):
@@ -325,7 +347,7 @@ def run_water(args, local_rank):
         sps, kind, desc = water_cpu_steps(20)
         line["cpu_baseline"] = {"value": sps, "unit": "steps/s", "cores": 1, "kind": kind, "sample": desc}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     sim.close()
     if world > 1:
         dist.destroy_process_group()
@@ -339,7 +361,7 @@ def run_decoder_reference(args):
             "config": {"workload": "cfg3", "description": WORKLOADS["cfg3"][3]},
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_decoder(args, local_rank):
@@ -457,7 +479,7 @@ def run_decoder(args, local_rank):
         tps, cores, desc = decoder_cpu_sample()
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     dec.close()
     if world > 1:
         dist.destroy_process_group()
@@ -476,6 +498,7 @@ def main():
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="library option to set before timing (e.g. pdl=0); for experiments")
     args = ap.parse_args()
+    claim_stdout()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -503,8 +526,6 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA GPU: the MoE layer has no CPU path")
-    # NCCL prints its version banner (levels VERSION and WARN) to stdout by default: send its log to
-    # stderr so that stdout carries the one JSON line only
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -713,7 +734,7 @@ def main():
                                 "sample": f"{cpu_steps_done} steps of {min(T, 64)} tokens of the same batches "
                                           "(CPU oracle, OpenMP, fp64 accumulate)"}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     layer.close()
     if world > 1:
         dist.destroy_process_group()

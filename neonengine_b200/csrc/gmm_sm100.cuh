@@ -715,7 +715,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         // MMA issuer.  Same shape as the producer: converged warp, all lanes poll, one elected
         // lane issues the tcgen05 instructions.
         {
-            int s = 0, ph = 0, iter = 0;
+            int s = 0, ph = 0, iter = 0, ctr = 0;
             bool ready = false;  // the current stage's barrier was already seen complete
             const uint32_t smem_base = smem_u32(smem);
             if (STACK) {
@@ -740,10 +740,14 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 const uint32_t d_tmem = tmem_base + b * L::kAccCols;
                 uint32_t first = 0;  // becomes non-zero after the item's first stage
                 for (int left = p.n_chunks; left > 0; left -= KC) {
+                    const bool tracing = p.trace && blockIdx.x == 0 && lane == 0 && ctr < 512;
+                    if (tracing) p.trace[(1 * 512 + ctr) * 2] = clock64();  // about to wait for the stage's data
                     if (!ready) {
                         ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
                         if (!__all_sync(0xffffffffu, ok)) goto done;
                     }
+                    if (tracing) p.trace[(1 * 512 + ctr) * 2 + 1] = clock64();  // data present
+                    ++ctr;
                     tc_fence_after();
                     const uint32_t st = smem_base + s * L::kStage;
                     const uint32_t sf_stage = tmem_base + SF_BASE + s * SF_COLS;

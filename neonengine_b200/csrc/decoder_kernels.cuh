@@ -191,20 +191,18 @@ constexpr int kGemvSplitU = 6;  // k-blocks per warp of gemv_mma_split_kernel (a
 // The same product for matrices with few rows, cut along K over gridDim.y CTAs per 16-row tile
 // so that enough CTAs exist to keep HBM busy: CTA (tile, ks) handles k-blocks
 // [ks * nkb / KS, (ks + 1) * nkb / KS) (nkb = K / 32, at most 8 * kGemvSplitU of them), loads all
-// of its weights up front (before it waits for its predecessor), stages only its slice of x,
-// and writes the partial result parts[ks][b][r]; part 0 carries the bias.  The consumer adds
+// of its weights up front (before it waits for its predecessor), reads the matching pieces of x
+// straight from L2 into the mma B fragments, and writes the partial result parts[ks][b][r]; part
+// 0 carries the bias.  The consumer adds
 // the parts in order, which keeps the result independent of scheduling.
 __global__ void __launch_bounds__(256, 3) gemv_mma_split_kernel(const uint16_t* __restrict__ W, const uint16_t* __restrict__ bias,
                                                                 const uint16_t* __restrict__ x, int B, int rows, int K,
                                                                 float* __restrict__ parts, long long part_stride) {
-    extern __shared__ __align__(16) unsigned char gsm[];
+    __shared__ __align__(16) float red[8 * 128];  // [8 warps][128] accumulator fragments
     constexpr int U = kGemvSplitU;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int nkb = K / 32, KS = gridDim.y, ks = blockIdx.y, tile = blockIdx.x;
-    const int kb_lo = ks * nkb / KS, kb_hi = (ks + 1) * nkb / KS, span = (kb_hi - kb_lo) * 32;  // elements of this slice
-    const int xstride = span + gemv_row_pad(span);
-    uint16_t* xs = reinterpret_cast<uint16_t*>(gsm);
-    float* red = reinterpret_cast<float*>(gsm + (size_t)8 * xstride * 2);  // [8 warps][128]
+    const int kb_lo = ks * nkb / KS, kb_hi = (ks + 1) * nkb / KS;
     pdl_launch_dependents();
     const uint16_t* ra = W + (size_t)min(tile * 16 + g, rows - 1) * K;
     const uint16_t* rb = W + (size_t)min(tile * 16 + g + 8, rows - 1) * K;
@@ -220,36 +218,22 @@ __global__ void __launch_bounds__(256, 3) gemv_mma_split_kernel(const uint16_t* 
         }
     }
     pdl_wait();
-    {
-        const int nvec = span / 8, total = 8 * nvec;
-        for (int base = tid; base < total; base += 256 * 4) {
-            uint4 v[4];
+    // the matching 16 bytes of x straight from L2 (row g = token g; rows past the batch are zero):
+    // no shared-memory staging, no barrier before the mma's
+    uint4 xv[U];
+    const uint16_t* xr = x + (size_t)min(g, B - 1) * K;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = base + u * 256;
-                v[u] = (i < total && i / nvec < B)
-                           ? reinterpret_cast<const uint4*>(x + (size_t)(i / nvec) * K + kb_lo * 32)[i % nvec]
-                           : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = base + u * 256;
-                if (i < total) *reinterpret_cast<uint4*>(xs + (size_t)(i / nvec) * xstride + (i % nvec) * 8) = v[u];
-            }
-        }
+    for (int u = 0; u < U; ++u) {
+        const int kb = kb_lo + warp + u * 8;
+        xv[u] = (kb < kb_hi && g < B) ? __ldcg(reinterpret_cast<const uint4*>(xr + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
     }
-    __syncthreads();
     float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-        const int kb = warp + u * 8;  // relative to the slice
-        if (kb_lo + kb < kb_hi) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)g * xstride + kb * 32 + t * 8);
-            const uint32_t a0[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
-            const uint32_t a1[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
-            mma_bf16_16816(c, a0, xv.x, xv.y);
-            mma_bf16_16816(c, a1, xv.z, xv.w);
-        }
+        const uint32_t a0[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
+        const uint32_t a1[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+        mma_bf16_16816(c, a0, xv[u].x, xv[u].y);
+        mma_bf16_16816(c, a1, xv[u].z, xv[u].w);
     }
     *reinterpret_cast<float4*>(red + warp * 128 + lane * 4) = make_float4(c[0], c[1], c[2], c[3]);
     __syncthreads();

@@ -165,10 +165,9 @@ int launch_gemv(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias,
 int launch_gemv_split(neon_decoder_handle* h, const uint16_t* W, const uint16_t* bias, const uint16_t* x, int B, int rows, int K,
                       int splits, float* parts, long long part_stride, cudaStream_t st) {
     if (K % 32) return dfail(h, NEON_MOE_EINVAL, "GEMV depth %d is not a multiple of 32", K);
-    const int nkb = K / 32, span = ((nkb + splits - 1) / splits) * 32;
+    const int nkb = K / 32;
     if ((nkb + splits - 1) / splits > 8 * kGemvSplitU) return dfail(h, NEON_MOE_EINVAL, "GEMV depth %d needs more K-splits", K);
-    const size_t smem = (size_t)8 * (span + 64) * 2 + 8 * 128 * sizeof(float);
-    launch_pdl(h, (h->pdl & kPdlGemv) != 0, gemv_mma_split_kernel, dim3((rows + 15) / 16, splits), dim3(256), smem, st, W, bias, x,
+    launch_pdl(h, (h->pdl & kPdlGemv) != 0, gemv_mma_split_kernel, dim3((rows + 15) / 16, splits), dim3(256), 0, st, W, bias, x,
                B, rows, K, parts, part_stride);
     return NEON_MOE_OK;
 }

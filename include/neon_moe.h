@@ -196,7 +196,7 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * "fuse_dispatch" (default 0): 1 = at decode-sized passes the router CTA that finishes last also
  * runs the dispatch, saving one launch (identical results; measured no faster than the separate
  * kernel under programmatic dependent launch, 0.1086 vs 0.1078 ms per 64-token pass).
- * "tile_tokens" (default 0 = by batch size: 16 up to 16 tokens, 32 up to 64, else 128): forces the
+ * "tile_tokens" (default 0 = by batch size: 16 up to 16 tokens, 32 up to 384, else 128): forces the
  * token-tile size of the grouped GEMMs (16 and 32 use the stacked-term kernels).
  * "sync_debug": synchronise after every kernel and name the one that failed.
  * "a_tx_bytes": bytes a 128x128 4-bit TMA box reports to its mbarrier (default 8192).

@@ -198,6 +198,10 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * kernel under programmatic dependent launch, 0.1086 vs 0.1078 ms per 64-token pass).
  * "tile_tokens" (default 0 = by batch size: 16 up to 16 tokens, 32 up to 384, else 128): forces the
  * token-tile size of the grouped GEMMs (16 and 32 use the stacked-term kernels).
+ * "router_wide_max" (default 384): passes of up to this many tokens run the router with one CTA per
+ * token, which also produces the per-token maxima the 16/32-token tiles scale by; larger passes use
+ * the router that shares each weight read between 8 tokens.  "graph_max_tokens" (default 64): the
+ * largest pass that is replayed from a captured graph (measured gain above 64 tokens: ~1 us).
  * "sync_debug": synchronise after every kernel and name the one that failed.
  * "a_tx_bytes": bytes a 128x128 4-bit TMA box reports to its mbarrier (default 8192).
  * Others ("n_ctas", "ctas_per_sm", "max_stages", "trace_ptr") are measurement aids.

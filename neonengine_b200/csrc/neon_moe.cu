@@ -54,6 +54,10 @@ struct neon_moe_handle {
     int max_stages = 0, ctas_per_sm = 1;
     int pdl = 1;                  // programmatic dependent launch between the kernels of a pass
     int tile_override = 0;        // 0 = token-tile size chosen from the batch size; 16 / 32 / 128 force it
+    int router_wide_max = 384;    // passes up to this many tokens use the one-CTA-per-token router, which also yields the token
+                                  // maxima the stacked-term tiles need (measured 9-13 us faster than the token-blocked router
+                                  // plus a separate maxima kernel at 96-256 tokens, equal at 384)
+    int graph_max_tokens = 64;    // passes up to this many tokens are replayed from a captured CUDA graph
     int sync_debug = 0;           // synchronise and check after every kernel (slow; names the failing kernel)
     long long* trace = nullptr;
     int trace_which = 0;  // 0 = both products (the down product overwrites), 1 = gate_up only, 2 = down only
@@ -650,7 +654,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
 static void launch_router(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, int32_t* idx, float* w,
                           float* tok_amax, cudaStream_t st) {
     const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k;
-    if (h->path == 2 && T > 64) {  // large batches never need the token maxima (128-token tiles scale per block)
+    if (h->path == 2 && T > h->router_wide_max) {  // token-blocked router: no token maxima (128-token tiles scale per block)
         const size_t smem = (size_t)8 * H * 2 + (size_t)8 * E * sizeof(float);
         static bool configured[kMaxDevicesAttr] = {};
         if (!configured[h->cfg.device]) {
@@ -680,7 +684,7 @@ int neon_moe_forward(neon_moe_handle* h, const void* hidden, int T, const float*
     // Small passes are launch-bound: the second time the same arguments come in, the launch
     // sequence is captured into a CUDA graph (on the handle's own stream) and replayed from then
     // on.  Not while profiling or debugging, and not inside a caller's own stream capture.
-    const bool cacheable = h->use_graphs && h->has_weights && h->cfg.ep_size == 1 && T > 0 && T <= 64 && hidden && out &&
+    const bool cacheable = h->use_graphs && h->has_weights && h->cfg.ep_size == 1 && T > 0 && T <= h->graph_max_tokens && hidden && out &&
                            !h->profiling && !h->sync_debug && !h->trace;
     if (!cacheable) return forward_eager(h, hidden, T, logit_bias, out, topk_idx, topk_w, st);
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -757,7 +761,7 @@ static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const fl
         launch_router(h, hidden, T, logit_bias, h->idx, h->route_w, h->x_amax, st);
     }
     // the token maxima come from the decode routers only (the token-blocked router does not produce them)
-    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, (h->path == 2 && T <= 64) ? h->x_amax : nullptr, out, st, prof,
+    int rc = experts_core(h, hidden, T, k, h->idx, 0, h->route_w, (h->path == 2 && T <= h->router_wide_max) ? h->x_amax : nullptr, out, st, prof,
                           fused);
     if (rc) return rc;
     if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
@@ -1006,6 +1010,11 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     } else if (!strcmp(name, "tile_tokens")) {
         if (value != 0 && value != 16 && value != 32 && value != 128) return fail(h, NEON_MOE_EINVAL, "tile_tokens must be 0, 16, 32 or 128");
         h->tile_override = (int)value;
+    } else if (!strcmp(name, "router_wide_max")) {
+        h->router_wide_max = (int)value;
+    } else if (!strcmp(name, "graph_max_tokens")) {
+        h->graph_max_tokens = (int)value;
+        drop_graphs(h);
     } else if (!strcmp(name, "mx4")) {
         h->mx4 = (int)value;
     } else if (!strcmp(name, "use_graphs")) {

@@ -42,6 +42,11 @@ class NeonWaterConfig(ctypes.Structure):
                 ("collision_substeps", c_int), ("jacobi_iterations", c_int), ("device", c_int)]
 
 
+class NeonSvgfConfig(ctypes.Structure):
+    """Mirror of ``neon_svgf_config`` (include/neon_svgf.h)."""
+    _fields_ = [("width", c_int), ("height", c_int), ("atrous_iterations", c_int), ("device", c_int)]
+
+
 # name -> (restype, argtypes); must list every symbol include/neon_water.h declares
 WATER_SIGNATURES = {
     "neon_water_create": (c_int, [ctypes.POINTER(NeonWaterConfig), c_void_p, c_int, ctypes.POINTER(c_void_p)]),
@@ -57,6 +62,20 @@ WATER_SIGNATURES = {
     "neon_water_profile_step": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), c_void_p]),
     "neon_water_set_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.c_int64]),
     "neon_water_launch_count": (ctypes.c_int64, [c_void_p]),
+}
+
+# name -> (restype, argtypes); must list every symbol include/neon_svgf.h declares
+SVGF_SIGNATURES = {
+    "neon_svgf_create": (c_int, [ctypes.POINTER(NeonSvgfConfig), ctypes.POINTER(c_void_p)]),
+    "neon_svgf_destroy": (c_int, [c_void_p]),
+    "neon_svgf_last_error": (ctypes.c_char_p, [c_void_p]),
+    "neon_svgf_set_history": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "neon_svgf_denoise": (c_int, [c_void_p] + [c_void_p] * 5 + [c_void_p]),
+    "neon_svgf_denoise_host": (c_int, [c_void_p] + [c_void_p] * 5 + [c_void_p]),
+    "neon_svgf_read": (c_int, [c_void_p, ctypes.c_char_p, c_void_p, ctypes.c_uint64]),
+    "neon_svgf_profile_frame": (c_int, [c_void_p] + [c_void_p] * 5 + [ctypes.POINTER(ctypes.c_double), c_void_p]),
+    "neon_svgf_set_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.c_int64]),
+    "neon_svgf_launch_count": (ctypes.c_int64, [c_void_p]),
 }
 
 # name -> (restype, argtypes); must list every symbol include/neon_decoder.h declares
@@ -116,7 +135,7 @@ def load() -> ctypes.CDLL:
         raise ImportError(f"{SO_PATH} is missing: build it with `python -m neonengine_b200.build` "
                           "(there is no CPU fallback)")
     lib = ctypes.CDLL(SO_PATH)
-    for name, (res, args) in {**SIGNATURES, **DECODER_SIGNATURES, **WATER_SIGNATURES}.items():
+    for name, (res, args) in {**SIGNATURES, **DECODER_SIGNATURES, **WATER_SIGNATURES, **SVGF_SIGNATURES}.items():
         fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
         fn.restype = res
         fn.argtypes = args

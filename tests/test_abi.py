@@ -47,6 +47,14 @@ def test_exports_every_declared_water_symbol(lib):
     assert set(names) == set(_lib.WATER_SIGNATURES), "python binding table out of sync with the header"
 
 
+def test_exports_every_declared_svgf_symbol(lib):
+    names = declared_symbols("neon_svgf.h", "neon_svgf_")
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in neon_svgf.h but not exported"
+    assert set(names) == set(_lib.SVGF_SIGNATURES), "python binding table out of sync with the header"
+
+
 def test_water_create_rejects_bad_config(lib):
     h = ctypes.c_void_p()
     cfg = _lib.NeonWaterConfig(8, 1, 4, 4, 0.1, 1.0, 1.0, 0.0, 1.0, 0.002)  # one cell along x

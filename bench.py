@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the gpt-oss-shaped MoE layer (tokens/s) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2|cfg3|cfg4|water] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2|cfg3|cfg4|water|svgf] [--impl reference]
 
 A step is one pass of the MoE layer over one batch of seeded synthetic hidden states.
 Default workload at one GPU is the batched-decode configuration (T=64 tokens, Zipf-skewed
@@ -21,6 +21,8 @@ K/V cache, 201088-token vocabulary; one step = one new token per sequence, token
 `--workload water` runs the reference engine's own FLIP water step (8000 particles, 99x37x44 cells,
 4 separation sub-steps, 50 Jacobi iterations per step) and reports simulation steps/s; its CPU arm
 is the reference shader itself compiled for the host (oracle/_ref) when present, else the restatement.
+`--workload svgf` runs the reference engine's denoiser (temporal accumulation + 3 a-trous passes) on
+1920x1080 frames of a seeded synthetic scene and reports frames/s; CPU arm as for the water step.
 `--impl reference` times the CPU oracle alone (the nominal reference engine has no
 implementation of this path; the oracle is its stand-in on the host cores).
 """
@@ -53,6 +55,8 @@ WORKLOADS = {
                            "vocabulary 201088, random-init weights"),
     "water": (0, 0, False, "NeonEngine FLIP water step: 8000 particles, 99x37x44 cells, 4 separation sub-steps, "
                            "50 pressure Jacobi iterations, dt 1/500"),
+    "svgf": (0, 0, False, "NeonEngine denoiser: temporal accumulation + 3 a-trous passes of one 1920x1080 frame "
+                          "(rgba32f G-buffer, rgba16f history, rgba8 image), seeded synthetic scene"),
     "cfg4": (8192, 128, False, "gpt-oss-120b-shaped MoE layer, 128 experts, T=8192 tokens per GPU, uniform routing, "
                                "experts sharded over the GPUs (expert parallel) when more than one"),
 }
@@ -353,6 +357,135 @@ def run_water(args, local_rank):
         dist.destroy_process_group()
 
 
+SVGF_W, SVGF_H, SVGF_ITERS, SVGF_FRAMES = 1920, 1080, 3, 4
+
+
+def svgf_cpu_frames(n_frames, w=SVGF_W, h=SVGF_H):
+    """Times n_frames of the denoiser on one host core: the reference shaders compiled for the CPU
+    when that library is present, else the restatement.  Returns (frames/s, kind, description)."""
+    from neonengine_b200 import svgf_synth
+    from oracle import svgf
+    st = svgf.State.zeros(w, h)
+    frames = [svgf_synth.make_frame(w, h, i) for i in range(n_frames)]
+    if svgf.have_ref():
+        kind, fn, what = "reference", svgf.ref_frame, "raytracing_pp.comp + raytracing_atrous.comp compiled for the CPU, bodies live"
+        svgf.ref_lib()
+    else:
+        kind, fn, what = "port", lambda g, im, s, it: svgf.frame(g, im, s, it, serial=True), "C restatement of the two shaders"
+        svgf.lib()
+    t0 = time.perf_counter()
+    for g, image in frames:
+        fn(g, image, st, SVGF_ITERS)
+    dt = time.perf_counter() - t0
+    return n_frames / dt, kind, f"{n_frames} frames of the same {w}x{h} sequence ({what}, 1 thread, {dt:.1f} s)"
+
+
+def run_svgf_reference(args):
+    n = max(1, min(args.steps, 4))
+    fps, kind, desc = svgf_cpu_frames(n)
+    line = {"impl": "reference", "metric": "denoised_frames_per_s", "value": fps, "unit": "frames/s", "n_gpus": args.gpus,
+            "steps": n, "warmup": 0, "ms_per_step": 1e3 / fps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "svgf", "description": WORKLOADS["svgf"][3]},
+            "cpu_baseline": {"value": fps, "unit": "frames/s", "cores": 1, "kind": kind, "sample": desc},
+            "e2e": {"value": fps, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    emit(line)
+
+
+def run_svgf(args, local_rank):
+    """Frames are independent jobs per GPU (the history couples consecutive frames of one view):
+    N independent replicas under torchrun."""
+    import torch
+    import torch.distributed as dist
+    from neonengine_b200 import svgf_synth
+    from neonengine_b200.svgf_denoiser import SvgfDenoiser
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    w, h = SVGF_W, SVGF_H
+    px = w * h
+    dn = SvgfDenoiser(w, h, SVGF_ITERS, device=local_rank)
+    frames = [svgf_synth.make_frame(w, h, i) for i in range(SVGF_FRAMES)]
+    d_g = [[torch.from_numpy(a).cuda() for a in g] for g, _ in frames]
+    d_img = [torch.from_numpy(im).cuda() for _, im in frames]
+    d_work = [torch.empty_like(t) for t in d_img]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    st = torch.cuda.current_stream()
+
+    def step(i):
+        k = i % SVGF_FRAMES
+        dn.render(d_g[k], d_work[k], stream=st)
+
+    for k in range(SVGF_FRAMES):
+        d_work[k].copy_(d_img[k])
+    warm = max(args.warmup, 3, 2 * SVGF_FRAMES)   # every (frame, ping-pong parity) pair has its graph before timing
+    for i in range(warm):
+        step(i)
+    barrier()
+    l0 = dn.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for i in range(args.steps):
+            step(i)
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        launches = dn.launch_count() - l0
+        prof = [dn.profile_frame(d_g[i % SVGF_FRAMES], d_work[i % SVGF_FRAMES], stream=st) for i in range(6)][2:]
+        t_ms = sum(p[0] for p in prof) / len(prof)
+        a_ms = sum(p[1] for p in prof) / len(prof)
+        # end to end: the five host images of a frame in, the denoised image out, every frame
+        e2e_steps = max(4, min(args.steps, 40))
+        pin_g = [[torch.from_numpy(a).pin_memory() for a in g] for g, _ in frames]
+        pin_img = [torch.from_numpy(im.copy()).pin_memory() for _, im in frames]
+        for i in range(2):
+            dn.render_host_ptr(*(t.data_ptr() for t in pin_g[i % SVGF_FRAMES]), pin_img[i % SVGF_FRAMES].data_ptr(), stream=st)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            dn.render_host_ptr(*(t.data_ptr() for t in pin_g[i % SVGF_FRAMES]), pin_img[i % SVGF_FRAMES].data_ptr(), stream=st)
+        e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+    peaks, peak_kind = measured_peaks()
+    # one filter pass per pixel: reads normal 16 + position 16 + moments 16 + colour 8, writes image 4 + moments 16
+    pass_bytes = px * 76
+    pass_ms = a_ms / SVGF_ITERS
+    achieved = pass_bytes / (pass_ms * 1e-3) / 1e9
+    gbuf_mb = SVGF_FRAMES * px * 68 / 1e6
+    line = {"metric": "denoised_frames_per_s", "value": world * args.steps / (ms * 1e-3), "unit": "frames/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "svgf", "description": WORKLOADS["svgf"][3], "width": w, "height": h,
+                       "atrous_iterations": SVGF_ITERS,
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (one view per GPU)",
+                       "l2_policy": f"{SVGF_FRAMES} rotating frames; their {gbuf_mb:.0f} MB of G-buffer and image exceed the 126 MB L2"},
+            "e2e": {"value": world * e2e_steps / e2e_s, "unit": "frames/s", "h2d_bytes_per_step": px * 68,
+                    "d2h_bytes_per_step": px * 4, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "k_atrous (one of 3 launches per frame)", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "traffic": None, "algorithmic_bytes_per_launch": pass_bytes, "ms_per_launch": pass_ms,
+                         "eager_group_ms_per_frame": {"temporal": t_ms, "atrous": a_ms},
+                         "note": "25 taps x ~80 unfused float operations per pixel: bound by the FP32 pipe, not by HBM"},
+            "clocks": clocks.summary()}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        fps, kind, desc = svgf_cpu_frames(3)
+        line["cpu_baseline"] = {"value": fps, "unit": "frames/s", "cores": 1, "kind": kind, "sample": desc}
+    if rank == 0:
+        emit(line)
+    dn.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_decoder_reference(args):
     tps, cores, desc = decoder_cpu_sample()
     line = {"impl": "reference", "metric": "decoder_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
@@ -505,7 +638,7 @@ def main():
     if args.workload is None:
         args.workload = "cfg1" if max(world, args.gpus) == 1 else "cfg4"
     if args.steps is None:
-        args.steps = 200 if args.workload == "cfg3" else 500 if args.workload == "water" else 2000 if WORKLOADS[args.workload][0] <= 64 else 50
+        args.steps = 200 if args.workload == "cfg3" else 500 if args.workload == "water" else 200 if args.workload == "svgf" else 2000 if WORKLOADS[args.workload][0] <= 64 else 50
     if args.impl == "reference":
         if args.workload == "cfg3":
             if rank == 0:
@@ -514,6 +647,10 @@ def main():
         if args.workload == "water":
             if rank == 0:
                 run_water_reference(args)
+            return
+        if args.workload == "svgf":
+            if rank == 0:
+                run_svgf_reference(args)
             return
         if args.steps > 64:
             args.steps = 8
@@ -536,6 +673,9 @@ def main():
         return
     if args.workload == "water":
         run_water(args, local_rank)
+        return
+    if args.workload == "svgf":
+        run_svgf(args, local_rank)
         return
 
     T, E, zipf, desc = WORKLOADS[args.workload]

@@ -116,7 +116,7 @@ def test_cpp_wrappers_compile():
     with tempfile.TemporaryDirectory() as d:
         src = os.path.join(d, "check.cpp")
         with open(src, "w") as f:
-            f.write('#include "lve_moe_layer_system.hpp"\n#include "lve_water_physics.hpp"\nint main() { return 0; }\n')
+            f.write('#include "lve_moe_layer_system.hpp"\n#include "lve_water_physics.hpp"\n#include "lve_svgf_denoiser.hpp"\nint main() { return 0; }\n')
         res = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I" + os.path.join(ROOT, "include"), src],
                              capture_output=True, text=True)
         assert res.returncode == 0, res.stderr

@@ -33,12 +33,15 @@ __device__ __forceinline__ float max_glsl(float a, float b) { return a < b ? b :
 __device__ __forceinline__ float min_glsl(float a, float b) { return b < a ? b : a; }
 __device__ __forceinline__ float mixf(float x, float y, float a) { return x * (1.0f - a) + y * a; }
 
-// 2^x: nearest-integer split, degree-7 polynomial of 2^f on [-0.5, 0.5], exact scaling by 2^n
+// 2^x: nearest-integer split, degree-7 polynomial of 2^f on [-0.5, 0.5], exact scaling by 2^n.
+// Inside (-126, 128) the nearest integer (ties to even) comes from adding and subtracting 1.5 * 2^23,
+// whose sum also carries that integer in its low mantissa bits: two additions on the main pipes
+// instead of a rounding and a conversion instruction, same values.
 __device__ __forceinline__ float exp2_poly(float x) {
-    if (x != x) return x;
-    if (x >= 128.0f) return INFINITY;
-    if (!(x > -126.0f)) return 0.0f;
-    const float n = rintf(x), f = x - n;
+    if (!(x > -126.0f && x < 128.0f)) return x != x ? x : (x > 0.0f ? INFINITY : 0.0f);
+    const float magic = 12582912.0f;
+    const float shifted = x + magic;
+    const float n = shifted - magic, f = x - n;
     float p = 1.5252734e-5f;
     p = fmaf(p, f, 1.5403530e-4f);
     p = fmaf(p, f, 1.3333558e-3f);
@@ -47,7 +50,8 @@ __device__ __forceinline__ float exp2_poly(float x) {
     p = fmaf(p, f, 2.4022651e-1f);
     p = fmaf(p, f, 6.9314718e-1f);
     p = fmaf(p, f, 1.0f);
-    return p * __uint_as_float((unsigned)((int)n + 127) << 23);
+    // (n + 127) << 23 with n = bits(shifted) - bits(magic)
+    return p * __uint_as_float((__float_as_uint(shifted) - 0x4B400000u + 127u) << 23);
 }
 
 __device__ __forceinline__ unsigned to_unorm8(float v) {

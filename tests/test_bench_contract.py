@@ -1,6 +1,6 @@
 """CPU checks of bench.py's contract: the reference arm prints exactly one JSON line on stdout with
-the agreed keys, for the MoE layer (CPU oracle) and for the water step (the reference shader compiled
-for the CPU when present, else the restatement)."""
+the agreed keys, for the MoE layer (CPU oracle) and for the water step and the denoiser (the reference shaders
+compiled for the CPU when present, else the restatements)."""
 import json
 import os
 import subprocess
@@ -26,6 +26,13 @@ def test_reference_arm_water():
     assert line["value"] > 0 and line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] == 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
     assert line["config"]["workload"] == "water"
+
+
+def test_reference_arm_denoiser():
+    line = _run(["--workload", "svgf", "--steps", "1"])
+    assert KEYS <= set(line) and line["impl"] == "reference" and line["metric"] == "denoised_frames_per_s"
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] == 1
+    assert line["e2e"]["value"] == line["value"] and line["config"]["workload"] == "svgf"
 
 
 def test_reference_arm_moe_layer_under_torchrun_env():

@@ -152,18 +152,14 @@ __device__ void build_tile_list(const int32_t* __restrict__ idx, int n, int e_lo
 }
 
 __global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
-                                                              DispatchArrays d, int tile_tokens, TileList tl,
-                                                              int tile_tokens2, TileList tl2, unsigned* zero_n) {
+                                                              DispatchArrays d, int tile_tokens, TileList tl) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ int dsmem[];
     __shared__ int s_first[kMaxExperts + 1];
-    if (zero_n)
-        for (int i = threadIdx.x; i < n; i += blockDim.x) zero_n[i] = 0u;
     dispatch_block(idx, n, e_lo, n_local, d, dsmem);
     __syncthreads();  // offsets and counts are in global memory, written by this CTA
     build_tile_list(idx, n, e_lo, n_local, d, tile_tokens, tl, s_first);
-    if (tile_tokens2 > 0) build_tile_list(idx, n, e_lo, n_local, d, tile_tokens2, tl2, s_first);
 }
 
 // The same for at most 1024 entries (decode batches): one entry per thread, four barriers, all

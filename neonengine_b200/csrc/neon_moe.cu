@@ -62,12 +62,11 @@ struct neon_moe_handle {
     long long* trace = nullptr;
     int trace_which = 0;  // 0 = both products (the down product overwrites), 1 = gate_up only, 2 = down only
     uint8_t *gu_wt = nullptr, *gu_sfa = nullptr, *dn_wt = nullptr, *dn_sfa = nullptr;
-    float *x_scale = nullptr, *a_scale = nullptr;  // per-row activation scales (stacked mode)
-    float *x_amax = nullptr, *a_amax = nullptr;    // largest magnitude per source row / per sorted row
+    float* x_scale = nullptr;  // per-row scales of the hidden-state terms (stacked mode; the SwiGLU rows use a fixed bound)
+    float* x_amax = nullptr;   // largest magnitude per token row
     uint8_t *x_act = nullptr, *a_act = nullptr;  // activation blocks (terms + scales) per (tile, chunk)
     float* a_f32 = nullptr;
     int32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_tiles = nullptr, *row_tile = nullptr;
-    int32_t *tile2_expert = nullptr, *tile2_row0 = nullptr, *tile2_rows = nullptr, *n_tiles2 = nullptr, *row_tile2 = nullptr;
     int tile_cap = 0, kp_h = 0, kp_i = 0;
     CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
     CUtensorMap tm4_gu{}, tm4_dn{}, tm4_gu2{}, tm4_dn2{};  // the same boxes left packed (4-bit in shared memory)
@@ -167,8 +166,8 @@ void free_all(neon_moe_handle* h) {
     void* ptrs[] = {h->router_w, h->router_b, h->gu_bias, h->dn_bias, h->gu_wq, h->dn_wq, h->gu_sq, h->dn_sq,
                     h->idx, h->count, h->offset, h->perm, h->inv, h->route_w, h->y, h->a_hi, h->a_lo,
                     h->status, h->st_hidden, h->st_out, h->st_bias, h->st_hidden2, h->st_out2, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
-                    h->x_act, h->a_act, h->x_scale, h->a_scale, h->x_amax, h->a_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
-                    h->n_tiles, h->row_tile, h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
+                    h->x_act, h->a_act, h->x_scale, h->x_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
+                    h->n_tiles, h->row_tile, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
                     h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv};
     for (void* p : ptrs)
         if (p) cudaFree(p);
@@ -476,14 +475,10 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         }
     }
     if ((rc = dev_alloc(h, &h->x_act, x_bytes)) || (rc = dev_alloc(h, &h->a_act, a_bytes)) ||
-        (rc = dev_alloc(h, &h->x_scale, n)) || (rc = dev_alloc(h, &h->a_scale, n)) ||
-        (rc = dev_alloc(h, &h->x_amax, n)) || (rc = dev_alloc(h, &h->a_amax, n)) ||
+        (rc = dev_alloc(h, &h->x_scale, n)) || (rc = dev_alloc(h, &h->x_amax, n)) ||
         (rc = dev_alloc(h, &h->a_f32, n * cfg->inter)) || (rc = dev_alloc(h, &h->tile_expert, (size_t)h->tile_cap)) ||
         (rc = dev_alloc(h, &h->tile_row0, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile_rows, (size_t)h->tile_cap)) ||
-        (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)) ||
-        (rc = dev_alloc(h, &h->tile2_expert, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile2_row0, (size_t)h->tile_cap)) ||
-        (rc = dev_alloc(h, &h->tile2_rows, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->n_tiles2, (size_t)4)) ||
-        (rc = dev_alloc(h, &h->row_tile2, n)))
+        (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
         return bail(rc);
     if (cfg->ep_size > 1) {
         const size_t ns = (size_t)h->n_src, E = (size_t)cfg->n_experts, Hh = (size_t)cfg->hidden;
@@ -554,10 +549,8 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
     const int n = rows * k_eff;
     DispatchArrays d{h->count, h->offset, h->perm, h->inv};
     if (h->path == 2) {
-        const int tt = tile_tokens_for(h, rows), tt2 = 0, tt_dn = tt;  // one tile list serves both products
+        const int tt = tile_tokens_for(h, rows), tt_dn = tt;  // one tile list serves both products
         TileList tl{h->tile_expert, h->tile_row0, h->tile_rows, h->n_tiles, h->row_tile};
-        TileList tl2{h->tile2_expert, h->tile2_row0, h->tile2_rows, h->n_tiles2, h->row_tile2};
-        const TileList& tld = tt2 ? tl2 : tl;
         const bool stacked = tt <= 32;
         if (dispatched) {
             // the router launch already produced the dispatch arrays and the tile list
@@ -566,7 +559,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
                      e_lo, EL, d, tt, tl);
         else
             launch_k(h->pdl != 0, dispatch_tiles_kernel, dim3(1), dim3(1024), (size_t)(33 * EL) * sizeof(int), st, idx, n, e_lo,
-                     EL, d, tt, tl, tt2, tl2, (unsigned*)nullptr);
+                     EL, d, tt, tl);
         if (!dispatched) h->launches++;
         DBG_SYNC(h, st, "dispatch_tiles_kernel");
         const int nch_h = h->kp_h / kChunkK, nch_i = h->kp_i / kChunkK;
@@ -593,13 +586,13 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         // |SwiGLU| <= limit * (limit + 1): a fixed bound replaces the row maximum
         const float a_bound = h->cfg.swiglu_limit * (h->cfg.swiglu_limit + 1.f);
         if (tt_dn > 32)
-            launch_split<kDownTermsPrefill, false>(h, tt_dn, tld, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
+            launch_split<kDownTermsPrefill, false>(h, tt_dn, tl, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
         else
-            launch_split<4, false>(h, tt_dn, tld, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
+            launch_split<4, false>(h, tt_dn, tl, h->a_f32, I, n, k_eff, nullptr, a_bound, h->a_act, nullptr, st);
         const bool mx4_dn = tt_dn <= 32 && h->mx4;
         DBG_SYNC(h, st, "split_rows (activation)");
         // down: rows H, K = I
-        g.tile_expert = tld.expert; g.tile_row0 = tld.row0; g.tile_rows = tld.rows; g.n_tiles = tld.n_tiles;
+        g.tile_expert = tl.expert; g.tile_row0 = tl.row0; g.tile_rows = tl.rows; g.n_tiles = tl.n_tiles;
         g.sfa = h->dn_sfa; g.act = h->a_act; g.row_scale = nullptr; g.bias = h->dn_bias;
         {   // the scale split_rows derives from the bound: 2^(floor(log2 bound) - 7), same clamps
             uint32_t bits; memcpy(&bits, &a_bound, 4);

@@ -844,11 +844,19 @@ def main():
             gu_flops = T * k * gu_flops_per_pair
             achieved = gu_flops / (gu_ms * 1e-3) / 1e12
             peak = peaks.get("bf16_tflops", 1590.0)
+            # measured ceiling of the instruction kinds themselves (operands resident in shared memory)
+            from neonengine_b200 import mma_rate
+            ceil8 = mma_rate.measure("mxf8f6f4", 128, 4096, device=local_rank)["tflops"]
+            ceil4 = mma_rate.measure("mxf4", 256, 4096, device=local_rank)["tflops"]
             roofline = {"bound": "tensor", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peak,
                         "peak_kind": peak_kind + " bf16 burst", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                         "algorithmic_flops_per_launch": gu_flops, "ms_per_launch": gu_ms,
                         "layer_tflops": T * k * shape.flops_per_pair / step_s / 1e12,
-                        "layer_frac_of_mxfp4_nominal_9000": T * k * shape.flops_per_pair / step_s / 1e12 / 9000.0}
+                        "layer_frac_of_mxfp4_nominal_9000": T * k * shape.flops_per_pair / step_s / 1e12 / 9000.0,
+                        "mma_issue_ceiling_tflops": {"mxf8f6f4_128x128": ceil8, "mxf4_128x256": ceil4},
+                        # the launch executes two e4m3 terms per activation: twice the algorithmic flops
+                        "executed_tflops": 2 * achieved, "frac_of_mxf8f6f4_ceiling": 2 * achieved / ceil8,
+                        "layer_frac_of_mxf4_ceiling": T * k * shape.flops_per_pair / step_s / 1e12 / ceil4}
         roofline.update({"stage_ms_per_step": per_step, "layer_bytes_per_step": layer_bytes,
                          "layer_gbs": layer_bytes / step_s / 1e9,
                          "layer_frac_of_peak": layer_bytes / step_s / 1e9 / peaks["hbm_gbs"],

@@ -233,6 +233,16 @@ int neon_moe_destroy(neon_moe_handle* h);
 /* Library version string. */
 const char* neon_moe_version(void);
 
+/* Measures the issue rate of the block-scaled tensor-core instruction the grouped GEMM uses, with
+ * the operands resident in shared memory (no global traffic): every SM issues `chunks` groups of
+ * accumulating 128 x n MMAs (kind 0: tcgen05.mma.kind::mxf8f6f4, 4 instructions of K = 32 per group;
+ * kind 1: kind::mxf4, 2 instructions of K = 64 per group) back to back.  n: 16..256, multiple of 16.
+ * ms receives the duration of the launch (CUDA events), cycles the SM clocks one SM needed from the
+ * first issue to the completion of the last instruction.  Work per SM = chunks * 2 * 128 * n * 128
+ * floating-point operations.  The measured ceiling of the prefill roofline (no library has one for
+ * these instruction kinds); the engine has no counterpart. */
+int neon_moe_mma_rate(int device, int kind, int n, int chunks, double* ms, int64_t* cycles);
+
 #ifdef __cplusplus
 }
 #endif

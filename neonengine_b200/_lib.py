@@ -120,6 +120,7 @@ SIGNATURES = {
     "neon_moe_last_error": (ctypes.c_char_p, [c_void_p]),
     "neon_moe_destroy": (c_int, [c_void_p]),
     "neon_moe_version": (ctypes.c_char_p, []),
+    "neon_moe_mma_rate": (c_int, [c_int, c_int, c_int, c_int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int64)]),
 }
 
 _lib = None

@@ -15,6 +15,7 @@
 #include "moe_kernels.cuh"
 #include "gmm_sm100.cuh"
 #include "ep.cuh"
+#include "mma_rate.cuh"
 
 using namespace neon;
 
@@ -403,6 +404,47 @@ void launch_expert(neon_moe_handle* h, const ExpertParams& p, int T, cudaStream_
 extern "C" {
 
 const char* neon_moe_version(void) { return "neon_moe 0.1 (sm_100a)"; }
+
+int neon_moe_mma_rate(int device, int kind, int n, int chunks, double* ms, int64_t* cycles) {
+    if (!ms || !cycles || (kind != 0 && kind != 1) || n < 16 || n > 256 || n % 16 || chunks < 1 || chunks > (1 << 20))
+        return NEON_MOE_EINVAL;
+    int n_dev = 0, sms = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev || cudaSetDevice(device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+        cudaGetLastError();
+        return NEON_MOE_ECUDA;
+    }
+    const size_t smem = 16384 + 32768 + 512 + 1024;
+    MmaRateOut* d_out = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = NEON_MOE_ECUDA;
+    MmaRateOut host{};
+    float elapsed = 0.f;
+    if (cudaMalloc(&d_out, sizeof(MmaRateOut)) != cudaSuccess || cudaMemset(d_out, 0, sizeof(MmaRateOut)) != cudaSuccess ||
+        cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess ||
+        cudaFuncSetAttribute(mma_rate_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(mma_rate_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        goto out;
+    for (int rep = 0; rep < 2; ++rep) {  // the first launch warms up
+        cudaEventRecord(e0, nullptr);
+        if (kind == 1) mma_rate_kernel<true><<<sms, 128, smem>>>(n, chunks, d_out);
+        else mma_rate_kernel<false><<<sms, 128, smem>>>(n, chunks, d_out);
+        cudaEventRecord(e1, nullptr);
+        if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) goto out;
+    }
+    if (cudaEventElapsedTime(&elapsed, e0, e1) != cudaSuccess ||
+        cudaMemcpy(&host, d_out, sizeof host, cudaMemcpyDeviceToHost) != cudaSuccess)
+        goto out;
+    *ms = elapsed;
+    *cycles = host.cycles;
+    rc = host.status ? NEON_MOE_EDEVICE : NEON_MOE_OK;
+out:
+    cudaGetLastError();
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(d_out);
+    return rc;
+}
 
 const char* neon_moe_last_error(const neon_moe_handle* h) { return h ? h->err.c_str() : g_create_error.c_str(); }
 

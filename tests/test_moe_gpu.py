@@ -271,3 +271,19 @@ def test_pipelined_host_batches_equal_blocking_calls(full20b):
         ref = ref[0] if isinstance(ref, tuple) else ref
         np.testing.assert_array_equal(o.numpy(), ref)
     assert layer.status() == 0
+
+
+def test_mma_rate_measurement():
+    """The in-library ceiling of the block-scaled MMA instructions: plausible and monotone in N."""
+    from neonengine_b200 import mma_rate
+    r64 = mma_rate.measure("mxf8f6f4", 64, 2048)
+    r256 = mma_rate.measure("mxf8f6f4", 256, 2048)
+    r4 = mma_rate.measure("mxf4", 256, 2048)
+    for r in (r64, r256, r4):
+        assert r["cycles_per_mma"] > 8 and 50.0 < r["tflops"] < 20000.0
+    assert r256["tflops"] > r64["tflops"]          # larger N amortises the weight-operand read
+    assert r4["tflops"] > 0.9 * r256["tflops"]     # packed 4-bit operands are at least as fast
+    lib = __import__("neonengine_b200._lib", fromlist=["load"]).load()
+    import ctypes
+    ms, cyc = ctypes.c_double(), ctypes.c_int64()
+    assert lib.neon_moe_mma_rate(0, 0, 100, 16, ctypes.byref(ms), ctypes.byref(cyc)) == 1   # n not a multiple of 16

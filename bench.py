@@ -846,8 +846,8 @@ def main():
             peak = peaks.get("bf16_tflops", 1590.0)
             # measured ceiling of the instruction kinds themselves (operands resident in shared memory)
             from neonengine_b200 import mma_rate
-            ceil8 = mma_rate.measure("mxf8f6f4", 128, 4096, device=local_rank)["tflops"]
-            ceil4 = mma_rate.measure("mxf4", 256, 4096, device=local_rank)["tflops"]
+            ceil8 = mma_rate.measure("mxf8f6f4", 128, 8192, device=local_rank)["tflops"]
+            ceil4 = mma_rate.measure("mxf4", 256, 8192, device=local_rank)["tflops"]
             roofline = {"bound": "tensor", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peak,
                         "peak_kind": peak_kind + " bf16 burst", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                         "algorithmic_flops_per_launch": gu_flops, "ms_per_launch": gu_ms,

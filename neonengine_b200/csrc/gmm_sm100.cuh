@@ -313,6 +313,9 @@ __host__ __device__ inline size_t act_block_bytes(int terms, int tile_tokens, bo
     return (size_t)act_header_bytes(terms) + (size_t)(tile_tokens / 8) * terms * 1024;
 }
 
+// Chunks one warp of split_rows_kernel handles (all their loads are issued before any arithmetic).
+constexpr int kSplitChunksPerWarp = 4;
+
 template <int TERMS, bool FROM_BF16, bool STACK>
 __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm,
                                                          int top_k, int K, int n_rows, const int32_t* __restrict__ row_tile,
@@ -321,56 +324,72 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const void* __restrict_
                                                          uint8_t* __restrict__ act) {
     pdl_launch_dependents();
     pdl_wait();
-    const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
+    constexpr int U = kSplitChunksPerWarp;
+    const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK, groups = (n_chunks + U - 1) / U;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= n_rows * n_chunks) return;
-    const int p = warp / n_chunks, c = warp % n_chunks;
-    const int k0 = c * kChunkK + 4 * lane;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (k0 < K) {
-        if (FROM_BF16) {
-            const uint16_t* row = static_cast<const uint16_t*>(src) + (size_t)(perm[p] / top_k) * K;
-            uint2 raw = *reinterpret_cast<const uint2*>(row + k0);
-            v[0] = __uint_as_float(raw.x << 16);
-            v[1] = __uint_as_float(raw.x & 0xffff0000u);
-            v[2] = __uint_as_float(raw.y << 16);
-            v[3] = __uint_as_float(raw.y & 0xffff0000u);
-        } else {
-            float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)p * K + k0);
-            v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+    if (warp >= n_rows * groups) return;
+    const int p = warp / groups, c0 = (warp % groups) * U;
+    float vv[U][4];
+    {
+        const uint16_t* row16 = nullptr;
+        const float* row32 = nullptr;
+        if (FROM_BF16) row16 = static_cast<const uint16_t*>(src) + (size_t)(perm[p] / top_k) * K;
+        else row32 = static_cast<const float*>(src) + (size_t)p * K;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k0 = (c0 + u) * kChunkK + 4 * lane;
+            vv[u][0] = vv[u][1] = vv[u][2] = vv[u][3] = 0.f;
+            if (c0 + u < n_chunks && k0 < K) {
+                if (FROM_BF16) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(row16 + k0);
+                    vv[u][0] = __uint_as_float(raw.x << 16);
+                    vv[u][1] = __uint_as_float(raw.x & 0xffff0000u);
+                    vv[u][2] = __uint_as_float(raw.y << 16);
+                    vv[u][3] = __uint_as_float(raw.y & 0xffff0000u);
+                } else {
+                    const float4 raw = *reinterpret_cast<const float4*>(row32 + k0);
+                    vv[u][0] = raw.x; vv[u][1] = raw.y; vv[u][2] = raw.z; vv[u][3] = raw.w;
+                }
+            }
         }
     }
     const int tile = row_tile[p], j = p - tile_row0[tile];
     const int npad = (tile_rows[tile] + 7) & ~7;
-    uint8_t* blk = act + ((size_t)tile * n_chunks + c) * act_block_bytes(TERMS, tile_tokens, STACK);
 #pragma unroll
-    for (int t = 0; t < TERMS; ++t) {
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu);
-        int sb = amax > 0.f ? max(ef - 7, 0) : 127;           // E8M0 byte: amax / scale in [128, 256)
-        float inv = __uint_as_float((uint32_t)(254 - sb) << 23);
-        float scale = sb > 0 ? __uint_as_float((uint32_t)sb << 23) : __uint_as_float(0x00400000u);
-        __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
-        __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
-        // row of this term inside the block and the place of its scale word
-        const int n = STACK ? t * npad + j : j;
-        uint8_t* row_ptr = STACK ? blk + 1024 + (size_t)(n >> 3) * 1024
-                                 : blk + act_header_bytes(TERMS) + ((size_t)(n >> 3) * TERMS + t) * 1024;
-        *reinterpret_cast<uint32_t*>(row_ptr + (n & 7) * 128 + (((lane >> 2) ^ (n & 7)) << 4) + ((lane & 3) << 2)) =
-            (uint32_t)lo | ((uint32_t)hi << 16);
-        if (t + 1 < TERMS) {
-            __half2_raw blo = __nv_cvt_fp8x2_to_halfraw2(lo, __NV_E4M3), bhi = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
-            float2 flo = __half22float2(*reinterpret_cast<__half2*>(&blo)), fhi = __half22float2(*reinterpret_cast<__half2*>(&bhi));
-            v[0] -= flo.x * scale; v[1] -= flo.y * scale; v[2] -= fhi.x * scale; v[3] -= fhi.y * scale;
+    for (int u = 0; u < U; ++u) {
+        const int c = c0 + u;
+        if (c >= n_chunks) break;
+        float* v = vv[u];
+        uint8_t* blk = act + ((size_t)tile * n_chunks + c) * act_block_bytes(TERMS, tile_tokens, STACK);
+#pragma unroll
+        for (int t = 0; t < TERMS; ++t) {
+            float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+            int sb = amax > 0.f ? max(ef - 7, 0) : 127;           // E8M0 byte: amax / scale in [128, 256)
+            float inv = __uint_as_float((uint32_t)(254 - sb) << 23);
+            float scale = sb > 0 ? __uint_as_float((uint32_t)sb << 23) : __uint_as_float(0x00400000u);
+            __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
+            __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+            // row of this term inside the block and the place of its scale word
+            const int n = STACK ? t * npad + j : j;
+            uint8_t* row_ptr = STACK ? blk + 1024 + (size_t)(n >> 3) * 1024
+                                     : blk + act_header_bytes(TERMS) + ((size_t)(n >> 3) * TERMS + t) * 1024;
+            *reinterpret_cast<uint32_t*>(row_ptr + (n & 7) * 128 + (((lane >> 2) ^ (n & 7)) << 4) + ((lane & 3) << 2)) =
+                (uint32_t)lo | ((uint32_t)hi << 16);
+            if (t + 1 < TERMS) {
+                __half2_raw blo = __nv_cvt_fp8x2_to_halfraw2(lo, __NV_E4M3), bhi = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
+                float2 flo = __half22float2(*reinterpret_cast<__half2*>(&blo)), fhi = __half22float2(*reinterpret_cast<__half2*>(&bhi));
+                v[0] -= flo.x * scale; v[1] -= flo.y * scale; v[2] -= fhi.x * scale; v[3] -= fhi.y * scale;
+            }
+            uint32_t w = (uint32_t)sb;
+            w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 8) << 8;
+            w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 16) << 16;
+            w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 24) << 24;
+            if (lane == 0) *reinterpret_cast<uint32_t*>(blk + (STACK ? 0 : t * 512) + (n & 31) * 16 + (n >> 5) * 4) = w;
         }
-        uint32_t w = (uint32_t)sb;
-        w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 8) << 8;
-        w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 16) << 16;
-        w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 24) << 24;
-        if (lane == 0) *reinterpret_cast<uint32_t*>(blk + (STACK ? 0 : t * 512) + (n & 31) * 16 + (n >> 5) * 4) = w;
     }
 }
 

@@ -383,7 +383,8 @@ void launch_split(neon_moe_handle* h, int tile_tokens, const TileList& tl, const
         launch_k(h->pdl != 0, split_rows_stacked_kernel<TERMS, FROM_BF16>, dim3((n * n_chunks + 7) / 8), dim3(256), 0, st, src,
                  h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
     else
-        launch_k(h->pdl != 0, split_rows_kernel<TERMS, FROM_BF16, false>, dim3((n * n_chunks + 7) / 8), dim3(256), 0, st, src,
+        launch_k(h->pdl != 0, split_rows_kernel<TERMS, FROM_BF16, false>,
+                 dim3((n * ((n_chunks + kSplitChunksPerWarp - 1) / kSplitChunksPerWarp) + 7) / 8), dim3(256), 0, st, src,
                  h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, act);
     h->launches++;
 }

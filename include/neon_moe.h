@@ -202,6 +202,9 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * token, which also produces the per-token maxima the 16/32-token tiles scale by; larger passes use
  * the router that shares each weight read between 8 tokens.  "graph_max_tokens" (default 64): the
  * largest pass that is replayed from a captured graph (measured gain above 64 tokens: ~1 us).
+ * "router_mma" (default 1): passes above router_wide_max tokens compute the router logits on tensor
+ * cores (mma.sync, 16 tokens per CTA; 32 or 128 experts); 0 = the CUDA-core router that shares each
+ * weight read between 8 tokens.  Same routing; logits differ in summation order only.
  * "sync_debug": synchronise after every kernel and name the one that failed.
  * "a_tx_bytes": bytes a 128x128 4-bit TMA box reports to its mbarrier (default 8192).
  * Others ("n_ctas", "ctas_per_sm", "max_stages", "trace_ptr") are measurement aids.

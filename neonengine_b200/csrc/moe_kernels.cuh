@@ -611,6 +611,117 @@ router_topk_block8_kernel(const uint16_t* __restrict__ x, const uint16_t* __rest
     }
 }
 
+// Router for large batches on tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate): one CTA
+// per 16 tokens, its four warps each take every fourth 32-wide window of the hidden dimension and
+// hold the 16 x E logits of that share in registers; the shares are added in shared memory in warp
+// order, then bias, top-k and softmax as in the other routers.  A lane's 16-byte load (8 consecutive
+// bf16 of one row) feeds two MMAs: the order of the 16 k-slots inside an MMA is free as long as both
+// operands use the same one.  Products of bf16 values are exact in fp32, so only the summation order
+// differs from the other routers (logits agree to ~1e-6; the synthetic inputs keep the top-k gaps
+// above 1e-4).  NT = E / 8 expert tiles.
+template <int NT>
+__global__ void __launch_bounds__(128)
+router_topk_mma_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wr, const uint16_t* __restrict__ br,
+                       const float* __restrict__ logit_bias, int T, int H, int k, int32_t* __restrict__ idx,
+                       float* __restrict__ w) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int E = NT * 8, TOK = 16;
+    extern __shared__ __align__(16) unsigned char rsmem[];
+    float* part = reinterpret_cast<float*>(rsmem);  // [4 warps][TOK][E], then reused: [TOK][E] logits in part[0]
+    const int t0 = blockIdx.x * TOK, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int ra_t = min(t0 + g, T - 1), rb_t = min(t0 + g + 8, T - 1);  // rows beyond T repeat the last token (never stored)
+    const uint16_t* xa = x + (size_t)ra_t * H + c * 8;
+    const uint16_t* xb = x + (size_t)rb_t * H + c * 8;
+    const uint16_t* wrow = wr + (size_t)g * H + c * 8;
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const int n_win = H / 32;
+    uint4 va = make_uint4(0, 0, 0, 0), vb = va;
+    if (warp < n_win) {
+        va = *reinterpret_cast<const uint4*>(xa + warp * 32);
+        vb = *reinterpret_cast<const uint4*>(xb + warp * 32);
+    }
+    for (int win = warp; win < n_win; win += 4) {
+        const uint32_t a0[4] = {va.x, vb.x, va.y, vb.y}, a1[4] = {va.z, vb.z, va.w, vb.w};
+        if (win + 4 < n_win) {  // the next window's token rows are in flight during this window's MMAs
+            va = *reinterpret_cast<const uint4*>(xa + (win + 4) * 32);
+            vb = *reinterpret_cast<const uint4*>(xb + (win + 4) * 32);
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + (size_t)j * 8 * H + win * 32));
+            mma_bf16_16816(acc[j], a0, wv.x, wv.y);
+            mma_bf16_16816(acc[j], a1, wv.z, wv.w);
+        }
+    }
+    // accumulator layout: c0, c1 = token g, experts 8j + 2c, + 1; c2, c3 = token g + 8
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        float* p0 = part + ((size_t)warp * TOK + g) * E + 8 * j + 2 * c;
+        p0[0] = acc[j][0]; p0[1] = acc[j][1];
+        p0[8 * E] = acc[j][2]; p0[8 * E + 1] = acc[j][3];
+    }
+    __syncthreads();
+    for (int i = tid; i < TOK * E; i += 128) {
+        const int e = i % E;
+        float v = ((part[i] + part[TOK * E + i]) + part[2 * TOK * E + i]) + part[3 * TOK * E + i];
+        v += bf16_bits_to_float(br[e]);
+        if (logit_bias) v += logit_bias[e];
+        part[i] = v;  // element i of share 0 is read by this thread only
+    }
+    __syncthreads();
+    for (int tt = warp; tt < TOK; tt += 4) {  // each warp selects for four tokens
+        const int t = t0 + tt;
+        if (t >= T) break;
+        const float* lgt = part + tt * E;
+        unsigned long long keys[kMaxExperts / 32];
+#pragma unroll
+        for (int j = 0; j < kMaxExperts / 32; ++j) {
+            int e = lane + 32 * j;
+            keys[j] = (e < E) ? logit_key(lgt[e], e) : 0ull;
+        }
+        float sel[kMaxTopK];
+        int seli[kMaxTopK];
+#pragma unroll
+        for (int s = 0; s < kMaxTopK; ++s) {
+            if (s < k) {
+                unsigned long long best = 0ull;
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j) best = keys[j] > best ? keys[j] : best;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                    best = other > best ? other : best;
+                }
+                int e = 0x7fffffff - (int)(uint32_t)(best & 0xffffffffull);
+                seli[s] = e;
+                sel[s] = lgt[e];
+#pragma unroll
+                for (int j = 0; j < kMaxExperts / 32; ++j)
+                    if (lane + 32 * j == e) keys[j] = 0ull;
+            }
+        }
+        if (lane == 0) {
+            float m = sel[0], den = 0.f, pr[kMaxTopK];
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    pr[s] = expf(sel[s] - m);
+                    den += pr[s];
+                }
+#pragma unroll
+            for (int s = 0; s < kMaxTopK; ++s)
+                if (s < k) {
+                    idx[t * k + s] = seli[s];
+                    w[t * k + s] = pr[s] / den;
+                }
+        }
+    }
+}
+
 // combine_kernel for the main path (programmatic dependent launch aware).
 __global__ void combine_main_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, int T, int H, int k,
                                     float* __restrict__ out) {

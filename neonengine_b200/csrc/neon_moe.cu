@@ -59,6 +59,7 @@ struct neon_moe_handle {
                                   // maxima the stacked-term tiles need (measured 9-13 us faster than the token-blocked router
                                   // plus a separate maxima kernel at 96-256 tokens, equal at 384)
     int graph_max_tokens = 64;    // passes up to this many tokens are replayed from a captured CUDA graph
+    int router_mma = 1;           // larger passes route on tensor cores (32 or 128 experts); 0 = the token-blocked CUDA-core router
     int sync_debug = 0;           // synchronise and check after every kernel (slow; names the failing kernel)
     long long* trace = nullptr;
     int trace_which = 0;  // 0 = both products (the down product overwrites), 1 = gate_up only, 2 = down only
@@ -690,7 +691,18 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
 static void launch_router(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, int32_t* idx, float* w,
                           float* tok_amax, cudaStream_t st) {
     const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k;
-    if (h->path == 2 && T > h->router_wide_max) {  // token-blocked router: no token maxima (128-token tiles scale per block)
+    if (h->path == 2 && T > h->router_wide_max && h->router_mma && (E == 32 || E == 128) && H % 32 == 0) {
+        // tensor-core router, 16 tokens per CTA: no token maxima (128-token tiles scale per block)
+        const size_t smem = (size_t)4 * 16 * E * sizeof(float);
+        if (E == 32)
+            launch_k(h->pdl != 0, router_topk_mma_kernel<4>, dim3((T + 15) / 16), dim3(128), smem, st,
+                     static_cast<const uint16_t*>(hidden), (const uint16_t*)h->router_w, (const uint16_t*)h->router_b, logit_bias, T,
+                     H, k, idx, w);
+        else
+            launch_k(h->pdl != 0, router_topk_mma_kernel<16>, dim3((T + 15) / 16), dim3(128), smem, st,
+                     static_cast<const uint16_t*>(hidden), (const uint16_t*)h->router_w, (const uint16_t*)h->router_b, logit_bias, T,
+                     H, k, idx, w);
+    } else if (h->path == 2 && T > h->router_wide_max) {  // token-blocked router: no token maxima either
         const size_t smem = (size_t)8 * H * 2 + (size_t)8 * E * sizeof(float);
         static bool configured[kMaxDevicesAttr] = {};
         if (!configured[h->cfg.device]) {
@@ -1048,6 +1060,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->tile_override = (int)value;
     } else if (!strcmp(name, "router_wide_max")) {
         h->router_wide_max = (int)value;
+    } else if (!strcmp(name, "router_mma")) {
+        h->router_mma = (int)value;
     } else if (!strcmp(name, "graph_max_tokens")) {
         h->graph_max_tokens = (int)value;
         drop_graphs(h);

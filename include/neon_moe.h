@@ -68,7 +68,10 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out);
 
 /* Copies (and re-tiles for the kernels) the weights; the caller may free its arrays
  * afterwards.  Expert tensors hold this rank's n_experts/ep_size experts; the router is
- * replicated.  on_device != 0: pointers are device memory on cfg->device.
+ * replicated.  on_device != 0: pointers are device memory on cfg->device.  Any E8M0 scale byte
+ * is accepted.  Only the tensor-core layout is kept (4 bits + 1/32 byte per weight, padded to
+ * 128); the second layout that "path" 1 and neon_moe_forward_static read is built from it when
+ * option "mma16_layout" (or "path" 1) asks for it.
  * Follows: initial data handed to the constructor and uploaded once,
  * NeonEngine/src/water_physics.cpp:41-123 (staging upload of particle data). */
 int neon_moe_set_weights(neon_moe_handle* h, const void* router_w_bf16, const void* router_b_bf16,
@@ -81,8 +84,7 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w_bf16, const vo
  * n_sections}, a table of {name[16], offset, bytes} sections and the sections' bytes on 256-byte
  * boundaries.  Layout 0 ("raw") holds the eight tensors exactly as neon_moe_set_weights takes them
  * and is re-tiled on the GPU at load; layout 1 ("tiled") holds the tensor-core layout byte for byte
- * as it sits in HBM, so loading is a straight copy - but it does not hold the mma.sync layout, so
- * "path" 1 and neon_moe_forward_static refuse to run on a handle loaded from it.
+ * as it sits in HBM, so loading is a straight copy.
  * neon_moe_save_weights writes layout 1 from a handle that has weights; raw files are written by
  * the host (neonengine_b200/weight_file.py).  neon_moe_load_weights_file checks the header against
  * the handle's configuration and every section's size against the file before it touches the GPU.
@@ -129,8 +131,12 @@ int neon_moe_ep_init(neon_moe_handle* h, const void* id128);
  * local grouped expert products, all-to-all-v of the outputs (fp32) back, routing-weighted
  * combine.  Arguments as neon_moe_forward.  The call synchronises the stream once in the
  * middle (the exchange sizes are needed on the host) and returns with the rest enqueued.
- * A rank may receive at most 2*max_tokens*top_k rows per pass (twice the average); beyond
- * that the call fails with NEON_MOE_EINVAL before any exchange is posted. */
+ * A rank has room for 2*max_tokens*top_k received rows (twice the average).  Whether a pass
+ * fits is decided from the gathered histograms, which are the same on every rank, so all ranks
+ * reach the same verdict before any row travels: when some rank would overflow, every rank
+ * halves its token range and the halves run as passes of their own (skewed routing costs
+ * extra exchanges, not a failure); only if single-token passes still overflow does the call
+ * fail, with NEON_MOE_EINVAL on every rank alike. */
 int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
                         float* out_f32, int32_t* topk_idx, float* topk_w, void* cuda_stream);
 
@@ -146,6 +152,11 @@ int neon_moe_ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int 
                      int32_t* send_off, int32_t* recv_rows, int32_t* recv_off, int32_t* row_expert,
                      int row_expert_cap, int* n_recv);
 
+/* The collective capacity verdict neon_moe_forward_ep uses, host-only: *first_rank = the lowest
+ * rank whose receive total under all_counts[ep_size][n_experts] exceeds caps[rank], or -1 when
+ * every rank fits. */
+int neon_moe_ep_overflow(const int32_t* all_counts, int ep_size, int n_experts, const int32_t* caps, int* first_rank);
+
 /* The layer pass for callers that must not allocate device memory.  It has no counterpart
  * in the reference engine.
  *
@@ -158,7 +169,11 @@ int neon_moe_ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int 
  * cudaMalloc; this variant keeps them in a 2 MiB array built into the library image (each
  * GPU that loads the library holds those 2 MiB until the process exits) and calls neither
  * cudaMalloc/cudaFree nor any allocating library routine.  `h` is only read: it supplies
- * the weights and the layer description.
+ * the weights and the layer description.  It reads the mma.sync weight layout, which is built
+ * on request: whoever sets the handle up calls neon_moe_set_option(h, "mma16_layout", 1) once
+ * (that call allocates); without it this entry point fails with NEON_MOE_ESTATE.  The calling
+ * thread's current device is the same after the call as before; the handle's device status
+ * word is neither read nor cleared (these kernels have no bounded waits).
  *
  * Arguments are those of neon_moe_forward (all device pointers, stream-ordered).  Limit: the
  * intermediates of T tokens must fit the array - T*top_k*(4*inter + 4*hidden + 16) bytes plus
@@ -187,7 +202,10 @@ int neon_moe_read_dispatch(neon_moe_handle* h, int32_t* count, int32_t* offset, 
 int neon_moe_status(neon_moe_handle* h, int* device_status_word);
 
 /* Tuning / test switches.  "path": 2 (default on sm_100) = TMA + tcgen05 block-scaled
- * grouped GEMM, 1 = the mma.sync kernels.  "use_graphs" (default 1): passes of up to 64
+ * grouped GEMM, 1 = the mma.sync kernels (builds their weight layout on first use; that layout
+ * cannot hold scale bytes above 128 and the switch fails with NEON_MOE_EINVAL then).
+ * "mma16_layout": 1 builds that layout now (allocates ~the size of the expert weights again),
+ * 0 frees it.  "use_graphs" (default 1): passes of up to 64
  * tokens are captured into a CUDA graph the second time the same arguments are seen and
  * replayed afterwards (the analogue of the engine re-submitting a recorded command buffer).
  * "mx4" (default 0): 1 runs decode-sized passes on tcgen05.mma.kind::mxf4 (weights stay packed
@@ -205,9 +223,14 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * "router_mma" (default 1): passes above router_wide_max tokens compute the router logits on tensor
  * cores (mma.sync, 16 tokens per CTA; 32 or 128 experts); 0 = the CUDA-core router that shares each
  * weight read between 8 tokens.  Same routing; logits differ in summation order only.
- * "sync_debug": synchronise after every kernel and name the one that failed.
- * "a_tx_bytes": bytes a 128x128 4-bit TMA box reports to its mbarrier (default 8192).
- * Others ("n_ctas", "ctas_per_sm", "max_stages", "trace_ptr") are measurement aids.
+ * "n_ctas", "ctas_per_sm": grid size of the grouped GEMMs (default: one CTA per SM).
+ * Routing is deterministic for a given router kernel, but the three routers (one CTA per token,
+ * tensor-core, and the one neon_moe_forward_static uses) add the 2880 products in different
+ * orders; logits agree to ~1e-6, so two experts whose logits are closer than that may swap
+ * between a pass of 384 and one of 385 tokens, or between forward and forward_static.  Exact
+ * ties (equal logits) go to the lower expert id in every router.
+ * Builds with -DNEON_MOE_INSTRUMENT add measurement aids ("trace_ptr", "trace_which",
+ * "a_tx_bytes", "max_stages", "sync_debug"); the shipped library has none of them.
  * Follows: the literal knobs the engine's apps set before running a system,
  * NeonEngine/src/raytracing_app.cpp:605-631. */
 int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value);

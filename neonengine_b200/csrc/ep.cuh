@@ -85,6 +85,21 @@ inline int ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int ra
     return ro;
 }
 
+// The receive-capacity verdict of a pass, computed from the gathered histograms alone so that
+// every rank reaches the same answer before any row travels: returns the lowest rank whose
+// receive total exceeds its capacity caps[r], or -1 when every rank fits.  A rank that decided
+// on its own total only would leave its peers waiting in the exchange for rows that never come.
+inline int ep_first_overflow(const int32_t* all_counts, int ep_size, int n_experts, const int32_t* caps) {
+    const int nl = n_experts / ep_size;
+    for (int r = 0; r < ep_size; ++r) {
+        long long total = 0;
+        for (int src = 0; src < ep_size; ++src)
+            for (int e = 0; e < nl; ++e) total += all_counts[(size_t)src * n_experts + r * nl + e];
+        if (total > caps[r]) return r;
+    }
+    return -1;
+}
+
 // xsend[p, :] = hidden[perm[p] / k, :] for the n sorted entries (16-byte vectors).
 __global__ void pack_rows_kernel(const uint16_t* __restrict__ hidden, const int32_t* __restrict__ perm, int k, int H, int n,
                                  uint16_t* __restrict__ xsend) {

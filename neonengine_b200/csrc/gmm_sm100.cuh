@@ -79,6 +79,55 @@ __global__ void repack_tc_kernel(const uint8_t* __restrict__ blocks, const uint8
     }
 }
 
+// Inverse of tc_source_row: the tile row that holds matrix row `row`.
+__device__ __forceinline__ int tc_tile_row(int row, int gate_up) {
+    if (!gate_up) return row;
+    const int ch = row >> 1, half = row & 1;
+    return 128 * (ch >> 6) + 32 * ((ch & 63) >> 4) + (ch & 15) + 16 * half;
+}
+
+// The mma16 layout (moe_common.cuh) rebuilt from the "tc" layout, so that the mma.sync kernels can
+// be served from a handle that keeps only the tensor-core format (the caller's arrays are gone by
+// then).  Same output as repack_mma16_kernel on the original tensors; *bad_scale is set when a scale
+// byte exceeds 128, which the mma16 scale encoding cannot hold.
+__global__ void repack_mma16_from_tc_kernel(const uint8_t* __restrict__ wt, const uint8_t* __restrict__ sfa, int n_experts,
+                                            int rows, int K, int gate_up, uint4* __restrict__ wq, uint32_t* __restrict__ sq,
+                                            int* bad_scale) {
+    const int tiles = rows / 16, nbp = K / 64;
+    const int Kp = round_up_int(K, kChunkK), m_tiles = (rows + 127) / 128, n_chunks = Kp / kChunkK;
+    const long long total = (long long)n_experts * tiles * nbp * 32;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int lane = (int)(i % 32);
+        long long r = i / 32;
+        const int bp = (int)(r % nbp);
+        r /= nbp;
+        const int tl = (int)(r % tiles), e = (int)(r / tiles);
+        const int g = lane >> 2, t = lane & 3;
+        const int row_lo = gate_up ? 2 * (8 * tl + g) : 16 * tl + g;
+        const int row_hi = gate_up ? row_lo + 1 : row_lo + 8;
+        uint32_t words[4], sword = 0;
+        for (int part = 0; part < 4; ++part) {
+            const int row = (part & 1) ? row_hi : row_lo, blk = 2 * bp + (part >> 1);
+            const int tr = tc_tile_row(row, gate_up), m = tr >> 7, rr = tr & 127;
+            const int byte0 = blk * 16 + 4 * t, c = byte0 >> 6;
+            const uint8_t* src = wt + ((((size_t)e * m_tiles + m) * n_chunks + c) * 128 + rr) * 64 + (byte0 & 63);
+            uint32_t cds[8];
+            for (int b = 0; b < 4; ++b) {
+                cds[2 * b] = src[b] & 15u;
+                cds[2 * b + 1] = src[b] >> 4;
+            }
+            words[part] = pack8(cds);
+            if (t == 0) {
+                const uint32_t byte = sfa[(((size_t)e * m_tiles + m) * n_chunks + (blk >> 2)) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (blk & 3)];
+                if (byte > 128u) *bad_scale = 1;
+                sword |= ((byte + 126u) & 255u) << (8 * part);
+            }
+        }
+        wq[i] = make_uint4(words[0], words[1], words[2], words[3]);
+        if (t == 0) sq[(((size_t)e * tiles + tl) * nbp + bp) * 8 + g] = sword;
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Token tiles: each expert's run of sorted rows is cut into tiles of at most `tile_tokens`
 // rows.  One CTA; writes the tile list, *n_tiles and the tile of every sorted row.
@@ -569,7 +618,9 @@ struct GmmParams {
     uint32_t a_tx_bytes;   // bytes one 128 x 128 4-bit box reports to its mbarrier
     int tmem_cols;         // TMEM columns to allocate (power of two)
     int stages;            // pipeline stages in use (<= GmmSmem::kStages)
-    long long* trace;      // optional [2 roles][512 stages][2] clock stamps of CTA 0
+#ifdef NEON_MOE_INSTRUMENT
+    long long* trace;      // optional [2 roles][512 stages][2] clock stamps of CTA 0 (instrumented builds only)
+#endif
     const uint16_t* bias;  // [E][rows_total], original row order
     // gate_up epilogue
     float* a_out;          // [n][inter] fp32
@@ -667,7 +718,10 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         // datapath; all lanes poll the barrier, one elected lane arms it and issues the
         // stage's three copies.  Stage index, phase and global addresses are carried
         // incrementally: every extra instruction in this loop costs ~10 cycles per stage.
-        int s = 0, ph = 0, tr = 0;
+        int s = 0, ph = 0;
+#ifdef NEON_MOE_INSTRUMENT
+        int tr = 0;
+#endif
         // the next item's tile record is fetched one item ahead, off the critical path
         int next_e = 0, next_rows = 0;
         if ((int)blockIdx.x < n_items) {
@@ -693,7 +747,9 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 const bool whole = left >= KC;
                 int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
                 if (!__all_sync(0xffffffffu, ok)) goto done;
+#ifdef NEON_MOE_INSTRUMENT
                 if (p.trace && blockIdx.x == 0 && lane == 0 && tr < 512) p.trace[(0 * 512 + tr) * 2] = clock64();
+#endif
                 uint8_t* st = smem + s * L::kStage;
                 if (elect_one()) {
                     if (whole) {
@@ -709,8 +765,10 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     }
                 }
                 __syncwarp();
+#ifdef NEON_MOE_INSTRUMENT
                 if (p.trace && blockIdx.x == 0 && lane == 0 && tr < 512) p.trace[(0 * 512 + tr) * 2 + 1] = clock64();
                 ++tr;
+#endif
                 box_row += KC * 128;
                 sfa_src += KC * 512;
                 act_src += KC * act_stride;
@@ -730,7 +788,10 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         // MMA issuer.  Same shape as the producer: converged warp, all lanes poll, one elected
         // lane issues the tcgen05 instructions.
         {
-            int s = 0, ph = 0, iter = 0, ctr = 0;
+            int s = 0, ph = 0, iter = 0;
+#ifdef NEON_MOE_INSTRUMENT
+            int ctr = 0;
+#endif
             bool ready = false;  // the current stage's barrier was already seen complete
             const uint32_t smem_base = smem_u32(smem);
             if (STACK) {
@@ -755,14 +816,18 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 const uint32_t d_tmem = tmem_base + b * L::kAccCols;
                 uint32_t first = 0;  // becomes non-zero after the item's first stage
                 for (int left = p.n_chunks; left > 0; left -= KC) {
+#ifdef NEON_MOE_INSTRUMENT
                     const bool tracing = p.trace && blockIdx.x == 0 && lane == 0 && ctr < 512;
                     if (tracing) p.trace[(1 * 512 + ctr) * 2] = clock64();  // about to wait for the stage's data
+#endif
                     if (!ready) {
                         ok = mbar_wait(&full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);
                         if (!__all_sync(0xffffffffu, ok)) goto done;
                     }
+#ifdef NEON_MOE_INSTRUMENT
                     if (tracing) p.trace[(1 * 512 + ctr) * 2 + 1] = clock64();  // data present
                     ++ctr;
+#endif
                     tc_fence_after();
                     const uint32_t st = smem_base + s * L::kStage;
                     const uint32_t sf_stage = tmem_base + SF_BASE + s * SF_COLS;

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <new>
 #include <algorithm>
+#include <atomic>
 #include <string>
 #include <vector>
 
@@ -83,6 +84,8 @@ struct neon_moe_handle {
     cudaEvent_t ep_ev[6] = {};
     bool ep_timed = false;
     int ep_last_recv = 0;
+    int ep_subpasses = 0;              // exchanges the last expert-parallel call needed (1 unless a rank's capacity was exceeded)
+    std::vector<int32_t> ep_caps;      // receive capacity (rows) of every rank, gathered by ep_init
     // replay cache: a forward with the same arguments is captured once into a CUDA graph
     struct CachedGraph {
         const void *hidden, *bias, *out, *idx, *w;
@@ -202,38 +205,51 @@ void mark(neon_moe_handle* h, cudaStream_t st, bool active) {
     cudaEventRecord(h->events[h->events_used++], st);
 }
 
-// Upload (when needed) and re-tile one MXFP4 matrix set.
-int load_matrix(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* scales, int rows, int K, int gate_up,
-                int on_device, uint4** wq, uint32_t** sq) {
-    const int E = h->n_local;
-    const size_t nb = (size_t)E * rows * (K / 2), ns = (size_t)E * rows * (K / 32);
-    const uint8_t *d_blocks = blocks, *d_scales = scales;
-    uint8_t *tmp_b = nullptr, *tmp_s = nullptr;
-    if (!on_device) {
-        CU(h, cudaMalloc(&tmp_b, nb));
-        CU(h, cudaMalloc(&tmp_s, ns));
-        CU(h, cudaMemcpy(tmp_b, blocks, nb, cudaMemcpyHostToDevice));
-        CU(h, cudaMemcpy(tmp_s, scales, ns, cudaMemcpyHostToDevice));
-        d_blocks = tmp_b;
-        d_scales = tmp_s;
+// Frees device buffers on scope exit (temporaries of the loaders, also on their error returns).
+struct ScopedDeviceFree {
+    void* p[2] = {nullptr, nullptr};
+    ~ScopedDeviceFree() {
+        for (void* q : p)
+            if (q) cudaFree(q);
     }
-    const int tiles = rows / 16, nbp = K / 64;
-    if (!*wq) {
-        int rc = dev_alloc(h, wq, (size_t)E * tiles * nbp * 32);
-        if (rc) return rc;
-        rc = dev_alloc(h, sq, (size_t)E * tiles * nbp * 8);
-        if (rc) return rc;
+};
+
+void free_mma16(neon_moe_handle* h) {
+    for (void** p : {(void**)&h->gu_wq, (void**)&h->dn_wq, (void**)&h->gu_sq, (void**)&h->dn_sq}) {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
     }
-    CU(h, cudaMemset(h->status, 0, sizeof(int)));
-    repack_mma16_kernel<<<148 * 8, 256>>>(d_blocks, d_scales, E, rows, K, gate_up, *wq, *sq, h->status);
-    h->launches++;
-    CU(h, cudaGetLastError());
+}
+
+// Builds the mma.sync kernels' weight layout from the tensor-core layout the handle holds (only
+// "path" 1 and neon_moe_forward_static read it, so it is not built - and takes no memory - until
+// one of them is asked for).  Allocates; scale bytes above 128 are refused here and only here.
+int ensure_mma16(neon_moe_handle* h) {
+    if (h->gu_wq) return NEON_MOE_OK;
+    if (!h->gu_wt || !h->dn_wt) return fail(h, NEON_MOE_ESTATE, "no weights loaded");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const int E = h->n_local, H = h->cfg.hidden, I = h->cfg.inter;
+    struct Job { const uint8_t *wt, *sfa; int rows, K, gate_up; uint4** wq; uint32_t** sq; };
+    const Job jobs[2] = {{h->gu_wt, h->gu_sfa, 2 * I, H, 1, &h->gu_wq, &h->gu_sq}, {h->dn_wt, h->dn_sfa, H, I, 0, &h->dn_wq, &h->dn_sq}};
+    int* flag = h->status + 3;  // fourth word of the status block
+    CU(h, cudaMemset(flag, 0, sizeof(int)));
+    for (const Job& j : jobs) {
+        const int tiles = j.rows / 16, nbp = j.K / 64;
+        int rc = dev_alloc(h, j.wq, (size_t)E * tiles * nbp * 32);
+        if (!rc) rc = dev_alloc(h, j.sq, (size_t)E * tiles * nbp * 8);
+        if (rc) { free_mma16(h); return rc; }
+        repack_mma16_from_tc_kernel<<<148 * 8, 256>>>(j.wt, j.sfa, E, j.rows, j.K, j.gate_up, *j.wq, *j.sq, flag);
+        h->launches++;
+    }
     int bad = 0;
-    CU(h, cudaMemcpy(&bad, h->status, sizeof(int), cudaMemcpyDeviceToHost));
-    CU(h, cudaMemset(h->status, 0, sizeof(int)));
-    if (tmp_b) cudaFree(tmp_b);
-    if (tmp_s) cudaFree(tmp_s);
-    if (bad) return fail(h, NEON_MOE_EINVAL, "MXFP4 scale byte above 128 (scale > 2) is not supported");
+    cudaError_t ce = cudaMemcpy(&bad, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (ce == cudaSuccess) ce = cudaGetLastError();
+    if (ce != cudaSuccess) { free_mma16(h); return fail(h, NEON_MOE_ECUDA, "building the mma.sync weight layout failed: %s", cudaGetErrorString(ce)); }
+    if (bad) {
+        free_mma16(h);
+        return fail(h, NEON_MOE_EINVAL, "the mma.sync kernels (path 1, neon_moe_forward_static) do not support MXFP4 scale bytes above 128 "
+                                        "(scale > 2); the tensor-core path has no such limit");
+    }
     return NEON_MOE_OK;
 }
 
@@ -289,14 +305,14 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
     const int E = h->n_local;
     const size_t nb = (size_t)E * rows * (K / 2), ns = (size_t)E * rows * (K / 32);
     const uint8_t *d_blocks = blocks, *d_scales = scales;
-    uint8_t *tmp_b = nullptr, *tmp_s = nullptr;
+    ScopedDeviceFree tmp;
     if (!on_device) {
-        CU(h, cudaMalloc(&tmp_b, nb));
-        CU(h, cudaMalloc(&tmp_s, ns));
-        CU(h, cudaMemcpy(tmp_b, blocks, nb, cudaMemcpyHostToDevice));
-        CU(h, cudaMemcpy(tmp_s, scales, ns, cudaMemcpyHostToDevice));
-        d_blocks = tmp_b;
-        d_scales = tmp_s;
+        CU(h, cudaMalloc(&tmp.p[0], nb));
+        CU(h, cudaMalloc(&tmp.p[1], ns));
+        CU(h, cudaMemcpy(tmp.p[0], blocks, nb, cudaMemcpyHostToDevice));
+        CU(h, cudaMemcpy(tmp.p[1], scales, ns, cudaMemcpyHostToDevice));
+        d_blocks = static_cast<const uint8_t*>(tmp.p[0]);
+        d_scales = static_cast<const uint8_t*>(tmp.p[1]);
     }
     const int Kp = round_up_int(K, kChunkK), m_tiles = (rows + 127) / 128, n_chunks = Kp / kChunkK;
     if (!*wt) {
@@ -309,8 +325,6 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
     h->launches++;
     CU(h, cudaGetLastError());
     CU(h, cudaDeviceSynchronize());
-    if (tmp_b) cudaFree(tmp_b);
-    if (tmp_s) cudaFree(tmp_s);
     const uint64_t nrows = (uint64_t)E * m_tiles * n_chunks * 128;
     int rc;
     if ((rc = make_weight_map(h, map, *wt, nrows, 128, false)) || (rc = make_weight_map(h, map2, *wt, nrows, 256, false)) ||
@@ -572,11 +586,11 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
     if ((rc = copy_in(h, &h->router_b, router_b, (size_t)E, on_device))) return rc;
     if ((rc = copy_in(h, &h->gu_bias, gu_bias, (size_t)EL * 2 * I, on_device))) return rc;
     if ((rc = copy_in(h, &h->dn_bias, dn_bias, (size_t)EL * H, on_device))) return rc;
-    if ((rc = load_matrix(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wq, &h->gu_sq))) return rc;
-    if ((rc = load_matrix(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wq, &h->dn_sq))) return rc;
+    free_mma16(h);  // the mma.sync layout of the previous weights, if it was built
     if ((rc = load_matrix_tc(h, gu_blocks, gu_scales, 2 * I, H, 1, on_device, &h->gu_wt, &h->gu_sfa, &h->tm_gu, &h->tm_gu2, &h->tm4_gu, &h->tm4_gu2))) return rc;
     if ((rc = load_matrix_tc(h, dn_blocks, dn_scales, H, I, 0, on_device, &h->dn_wt, &h->dn_sfa, &h->tm_dn, &h->tm_dn2, &h->tm4_dn, &h->tm4_dn2))) return rc;
     CU(h, cudaDeviceSynchronize());
+    if (h->path == 1 && (rc = ensure_mma16(h))) return rc;  // a handle already on the mma.sync kernels keeps working
     h->has_weights = true;
     return NEON_MOE_OK;
 }
@@ -615,7 +629,10 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         launch_split<2, true>(h, tt, tl, hidden, H, n, k_eff, hidden_amax, 0.f, h->x_act, h->x_scale, st);
         DBG_SYNC(h, st, "split_rows (hidden)");
         GmmParams g{};
-        g.a_tx_bytes = h->a_tx_bytes; g.trace = h->trace_which == 2 ? nullptr : h->trace;
+        g.a_tx_bytes = h->a_tx_bytes;
+#ifdef NEON_MOE_INSTRUMENT
+        g.trace = h->trace_which == 2 ? nullptr : h->trace;
+#endif
         g.a_out = h->a_f32; g.inter = I; g.limit = h->cfg.swiglu_limit; g.alpha = h->cfg.swiglu_alpha;
         g.perm = h->perm; g.route_w = route_w; g.y = h->y; g.hidden = H; g.status = h->status;
         // gate_up: rows 2I, K = H
@@ -645,7 +662,9 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
             if (mx4_dn) g.row_scale_const = a_bound * (1.f / 6.f);  // split_rows_fp4_kernel's first-term scale
         }
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
+#ifdef NEON_MOE_INSTRUMENT
         g.trace = h->trace_which == 1 ? nullptr : h->trace;
+#endif
         rc = tt_dn > 32 ? launch_gmm<kDownTermsPrefill, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st)
                         : launch_gmm<4, false>(h, tt_dn, h->tm_dn, h->tm_dn2, g, st);
         if (rc) return rc;
@@ -845,6 +864,14 @@ int neon_moe_ep_init(neon_moe_handle* h, const void* id128) {
     ncclUniqueId id;
     memcpy(id.internal, id128, NCCL_UNIQUE_ID_BYTES);
     NC(h, nccl_api().CommInitRank(&h->comm, h->cfg.ep_size, id, h->cfg.ep_rank));
+    // every rank learns every rank's receive capacity, so that the overflow verdict of a pass is
+    // the same everywhere (ranks may have been created with different max_tokens)
+    const int G = h->cfg.ep_size;
+    CU(h, cudaMemcpy(h->s_count, &h->n_cap, sizeof(int32_t), cudaMemcpyHostToDevice));
+    NC(h, nccl_api().AllGather(h->s_count, h->all_counts_d, 1, ncclInt32, h->comm, h->own_stream));
+    h->ep_caps.assign((size_t)G, 0);
+    CU(h, cudaMemcpyAsync(h->ep_caps.data(), h->all_counts_d, (size_t)G * 4, cudaMemcpyDeviceToHost, h->own_stream));
+    CU(h, cudaStreamSynchronize(h->own_stream));
     return NEON_MOE_OK;
 }
 
@@ -858,16 +885,31 @@ int neon_moe_ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int 
     return *n_recv < 0 ? NEON_MOE_EINVAL : NEON_MOE_OK;
 }
 
-int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
-                        int32_t* topk_idx, float* topk_w, void* cuda_stream) {
-    if (!h) return NEON_MOE_EINVAL;
-    if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "forward_ep before set_weights");
-    if (!h->comm) return fail(h, NEON_MOE_ESTATE, "forward_ep before ep_init");
-    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
-    if (T > 0 && (!hidden || !out)) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
-    CU(h, cudaSetDevice(h->cfg.device));
+int neon_moe_ep_overflow(const int32_t* all_counts, int ep_size, int n_experts, const int32_t* caps, int* first_rank) {
+    if (!all_counts || !caps || !first_rank || ep_size <= 0 || n_experts <= 0 || n_experts % ep_size) return NEON_MOE_EINVAL;
+    *first_rank = ep_first_overflow(all_counts, ep_size, n_experts, caps);
+    return NEON_MOE_OK;
+}
+
+// NCCL call inside an open group: on failure the group is closed before the error is returned,
+// so the communicator is not left with a half-built group.
+#define NCG(h, call)                                                                                 \
+    do {                                                                                             \
+        ncclResult_t r_ = (call);                                                                    \
+        if (r_ != ncclSuccess) {                                                                     \
+            nccl_api().GroupEnd();                                                                   \
+            return fail(h, NEON_MOE_ENCCL, "%s failed: %s", #call, nccl_api().GetErrorString(r_)); \
+        }                                                                                            \
+    } while (0)
+
+// One exchange + local expert pass + exchange back over `T` of this rank's tokens.  When the
+// gathered histograms show that some rank would receive more rows than it has room for, EVERY
+// rank sees that from the same data and the token range is cut in two halves that run as passes
+// of their own (each rank halves its own range; the verdict is collective, so the ranks stay in
+// step).  Only when no rank has more than one token left does the call fail - on every rank.
+static int ep_pass(neon_moe_handle* h, const uint16_t* hidden, int T, const float* logit_bias, float* out,
+                   int32_t* topk_idx, float* topk_w, cudaStream_t st, int depth) {
     NcclApi& nc = nccl_api();
-    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k, G = h->cfg.ep_size, me = h->cfg.ep_rank;
     const int n = T * k;
     // 1. route own tokens, sort entries by global expert (= by destination rank, then expert), pack rows
@@ -876,28 +918,45 @@ int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const flo
     if (T > 0) launch_router(h, hidden, T, logit_bias, h->s_idx, h->s_w, nullptr, st);
     dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->s_idx, n, 0, E, sd);
     h->launches++;
-    if (n > 0) {
-        pack_rows_kernel<<<n, 128, 0, st>>>(static_cast<const uint16_t*>(hidden), h->s_perm, k, H, n, h->xsend);
-        h->launches++;
-    }
-    CU(h, cudaEventRecord(h->ep_ev[1], st));
     // 2. every rank learns every histogram; sizes are needed on the host to post the exchange
     NC(h, nc.AllGather(h->s_count, h->all_counts_d, (size_t)E, ncclInt32, h->comm, st));
     int32_t* all_counts = h->host_pinned;
     int32_t* row_expert_h = h->host_pinned + (size_t)E * G;
     CU(h, cudaMemcpyAsync(all_counts, h->all_counts_d, (size_t)E * G * 4, cudaMemcpyDeviceToHost, st));
+    if (n > 0) {  // runs while the histograms travel
+        pack_rows_kernel<<<n, 128, 0, st>>>(hidden, h->s_perm, k, H, n, h->xsend);
+        h->launches++;
+    }
+    CU(h, cudaEventRecord(h->ep_ev[1], st));
     CU(h, cudaStreamSynchronize(st));
+    const int over = ep_first_overflow(all_counts, G, E, h->ep_caps.data());
+    if (over >= 0) {
+        long long most = 0;  // entries of the rank with the most tokens in this pass
+        for (int r = 0; r < G; ++r) {
+            long long nr = 0;
+            for (int e = 0; e < E; ++e) nr += all_counts[(size_t)r * E + e];
+            most = std::max(most, nr);
+        }
+        if (most <= k || depth >= 16)
+            return fail(h, NEON_MOE_EINVAL, "rank %d would receive more than its %d rows even from single-token passes", over,
+                        (int)h->ep_caps[over]);
+        const int T0 = T / 2;  // every rank halves its own range; a rank with T <= 1 runs an empty first half
+        int rc = ep_pass(h, hidden, T0, logit_bias, out, topk_idx, topk_w, st, depth + 1);
+        if (rc) return rc;
+        return ep_pass(h, hidden + (size_t)T0 * H, T - T0, logit_bias, out + (size_t)T0 * H, topk_idx ? topk_idx + (size_t)T0 * k : nullptr,
+                       topk_w ? topk_w + (size_t)T0 * k : nullptr, st, depth + 1);
+    }
     int32_t send_rows[64], send_off[64], recv_rows[64], recv_off[64];
-    if (G > 64) return fail(h, NEON_MOE_EINVAL, "ep_size above 64");
     const int R = ep_plan(all_counts, G, E, me, send_rows, send_off, recv_rows, recv_off, row_expert_h, h->n_cap);
-    if (R < 0) return fail(h, NEON_MOE_EINVAL, "this rank would receive more than %d rows (2x the per-rank average)", h->n_cap);
+    if (R < 0) return fail(h, NEON_MOE_EINVAL, "exchange plan disagrees with the capacity verdict");  // cannot happen: same data
     h->ep_last_recv = R;
+    h->ep_subpasses++;
     if (R > 0) CU(h, cudaMemcpyAsync(h->row_expert, row_expert_h, (size_t)R * 4, cudaMemcpyHostToDevice, st));
     // 3. token rows to the owners of their experts
     NC(h, nc.GroupStart());
     for (int r = 0; r < G; ++r) {
-        if (send_rows[r]) NC(h, nc.Send(h->xsend + (size_t)send_off[r] * H, (size_t)send_rows[r] * H, ncclBfloat16, r, h->comm, st));
-        if (recv_rows[r]) NC(h, nc.Recv(h->xrecv + (size_t)recv_off[r] * H, (size_t)recv_rows[r] * H, ncclBfloat16, r, h->comm, st));
+        if (send_rows[r]) NCG(h, nc.Send(h->xsend + (size_t)send_off[r] * H, (size_t)send_rows[r] * H, ncclBfloat16, r, h->comm, st));
+        if (recv_rows[r]) NCG(h, nc.Recv(h->xrecv + (size_t)recv_off[r] * H, (size_t)recv_rows[r] * H, ncclBfloat16, r, h->comm, st));
     }
     NC(h, nc.GroupEnd());
     CU(h, cudaEventRecord(h->ep_ev[2], st));
@@ -910,8 +969,8 @@ int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const flo
     // 5. outputs back to the token owners, in the order the rows were sent
     NC(h, nc.GroupStart());
     for (int r = 0; r < G; ++r) {
-        if (recv_rows[r]) NC(h, nc.Send(h->yback + (size_t)recv_off[r] * H, (size_t)recv_rows[r] * H, ncclFloat32, r, h->comm, st));
-        if (send_rows[r]) NC(h, nc.Recv(h->yrecv + (size_t)send_off[r] * H, (size_t)send_rows[r] * H, ncclFloat32, r, h->comm, st));
+        if (recv_rows[r]) NCG(h, nc.Send(h->yback + (size_t)recv_off[r] * H, (size_t)recv_rows[r] * H, ncclFloat32, r, h->comm, st));
+        if (send_rows[r]) NCG(h, nc.Recv(h->yrecv + (size_t)send_off[r] * H, (size_t)send_rows[r] * H, ncclFloat32, r, h->comm, st));
     }
     NC(h, nc.GroupEnd());
     CU(h, cudaEventRecord(h->ep_ev[4], st));
@@ -929,6 +988,19 @@ int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const flo
     h->last_stream = st;
     h->last_n = R;
     return NEON_MOE_OK;
+}
+
+int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out,
+                        int32_t* topk_idx, float* topk_w, void* cuda_stream) {
+    if (!h) return NEON_MOE_EINVAL;
+    if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "forward_ep before set_weights");
+    if (!h->comm) return fail(h, NEON_MOE_ESTATE, "forward_ep before ep_init");
+    if (h->cfg.ep_size > 64) return fail(h, NEON_MOE_EINVAL, "ep_size above 64");
+    if (T < 0 || T > h->cfg.max_tokens) return fail(h, NEON_MOE_EINVAL, "T=%d outside [0, max_tokens=%d]", T, h->cfg.max_tokens);
+    if (T > 0 && (!hidden || !out)) return fail(h, NEON_MOE_EINVAL, "null hidden/out");
+    CU(h, cudaSetDevice(h->cfg.device));
+    h->ep_subpasses = 0;
+    return ep_pass(h, static_cast<const uint16_t*>(hidden), T, logit_bias, out, topk_idx, topk_w, static_cast<cudaStream_t>(cuda_stream), 0);
 }
 
 int neon_moe_ep_times(neon_moe_handle* h, double* ms5, int* rows_received) {
@@ -1038,15 +1110,33 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     drop_graphs(h);
     if (!strcmp(name, "path")) {
         if (value != 1 && value != 2) return fail(h, NEON_MOE_EINVAL, "path must be 1 (mma.sync) or 2 (tcgen05)");
-        if (value == 1 && !h->gu_wq && h->has_weights)
-            return fail(h, NEON_MOE_ESTATE, "path 1 needs the mma.sync weight layout, which a tiled weight file does not hold");
+        if (value == 1 && h->has_weights) {
+            int rc = ensure_mma16(h);
+            if (rc) return rc;
+        }
         h->path = (int)value;
+    } else if (!strcmp(name, "mma16_layout")) {
+        if (value) {
+            if (!h->has_weights) return fail(h, NEON_MOE_ESTATE, "mma16_layout before set_weights");
+            int rc = ensure_mma16(h);
+            if (rc) return rc;
+        } else if (h->path != 1) {
+            CU(h, cudaSetDevice(h->cfg.device));
+            CU(h, cudaDeviceSynchronize());
+            free_mma16(h);
+        }
+#ifdef NEON_MOE_INSTRUMENT
     } else if (!strcmp(name, "a_tx_bytes")) {
         h->a_tx_bytes = (uint32_t)value;
     } else if (!strcmp(name, "trace_ptr")) {
         h->trace = reinterpret_cast<long long*>(value);
     } else if (!strcmp(name, "trace_which")) {
         h->trace_which = (int)value;
+    } else if (!strcmp(name, "sync_debug")) {
+        h->sync_debug = (int)value;
+    } else if (!strcmp(name, "max_stages")) {
+        h->max_stages = (int)value;
+#endif
     } else if (!strcmp(name, "ctas_per_sm")) {
         h->ctas_per_sm = (int)value;
     } else if (!strcmp(name, "n_ctas")) {
@@ -1069,10 +1159,6 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->mx4 = (int)value;
     } else if (!strcmp(name, "use_graphs")) {
         h->use_graphs = (int)value;
-    } else if (!strcmp(name, "sync_debug")) {
-        h->sync_debug = (int)value;
-    } else if (!strcmp(name, "max_stages")) {
-        h->max_stages = (int)value;
     } else {
         return fail(h, NEON_MOE_EINVAL, "unknown option '%s'", name);
     }
@@ -1243,11 +1329,8 @@ int neon_moe_load_weights_file(neon_moe_handle* h, const char* path) {
         (rc = make_weight_map(h, &h->tm_dn, h->dn_wt, rows_dn, 128, false)) || (rc = make_weight_map(h, &h->tm_dn2, h->dn_wt, rows_dn, 256, false)) ||
         (rc = make_weight_map(h, &h->tm4_dn, h->dn_wt, rows_dn, 128, true)) || (rc = make_weight_map(h, &h->tm4_dn2, h->dn_wt, rows_dn, 256, true)))
         return rc;
-    // the mma.sync kernels' layout was not loaded: those paths refuse to run until set_weights is called
-    for (void** p : {(void**)&h->gu_wq, (void**)&h->dn_wq, (void**)&h->gu_sq, (void**)&h->dn_sq}) {
-        if (*p) cudaFree(*p);
-        *p = nullptr;
-    }
+    // the mma.sync kernels' layout is rebuilt from these tiles when "path" 1 or "mma16_layout" asks for it
+    free_mma16(h);
     h->path = 2;
     h->has_weights = true;
     return NEON_MOE_OK;
@@ -1279,7 +1362,21 @@ constexpr size_t kStaticScratchBytes = 2u << 20;  // 2 MiB, held by every GPU th
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device
+std::atomic<void*> g_static_scratch_addr[kMaxDevices];  // device address of g_static_scratch, per device (zero-initialised)
+
+// Makes `dev` current for the scope and puts the caller's device back afterwards.
+struct ScopedDevice {
+    int prev = -1;
+    cudaError_t err;
+    explicit ScopedDevice(int dev) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != dev) err = cudaSetDevice(dev);
+        else if (err == cudaSuccess) prev = -1;  // nothing to restore
+    }
+    ~ScopedDevice() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
@@ -1290,7 +1387,9 @@ extern "C" int neon_moe_forward_static(const neon_moe_handle* h, const void* hid
                                        void* cuda_stream) {
     if (!h) return fail(nullptr, NEON_MOE_EINVAL, "null handle");
     if (!h->has_weights) return fail(nullptr, NEON_MOE_ESTATE, "forward_static before set_weights");
-    if (!h->gu_wq) return fail(nullptr, NEON_MOE_ESTATE, "forward_static needs the mma.sync weight layout, which a tiled weight file does not hold");
+    if (!h->gu_wq)
+        return fail(nullptr, NEON_MOE_ESTATE, "forward_static reads the mma.sync weight layout, which is built on request: call "
+                                              "neon_moe_set_option(h, \"mma16_layout\", 1) once at set-up, where allocating is allowed");
     if (h->cfg.ep_size != 1) return fail(nullptr, NEON_MOE_ESTATE, "forward_static needs ep_size == 1");
     if (T < 0) return fail(nullptr, NEON_MOE_EINVAL, "negative T");
     if (T == 0) return NEON_MOE_OK;
@@ -1309,18 +1408,20 @@ extern "C" int neon_moe_forward_static(const neon_moe_handle* h, const void* hid
                     "use neon_moe_forward for larger batches", T, off, kStaticScratchBytes);
     const int dev = h->cfg.device;
     if (dev < 0 || dev >= kMaxDevices) return fail(nullptr, NEON_MOE_EINVAL, "device ordinal beyond %d", kMaxDevices);
-    cudaError_t ce = cudaSetDevice(dev);
+    ScopedDevice on_dev(dev);  // the caller's current device is restored on return
+    cudaError_t ce = on_dev.err;
     if (ce != cudaSuccess) return fail(nullptr, NEON_MOE_ECUDA, "cudaSetDevice failed: %s", cudaGetErrorString(ce));
-    if (!g_static_scratch_addr[dev]) {
+    void* scratch = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
         // The array's name is only a host-side stand-in; kernels need its device address,
-        // looked up once per device with that device current.
-        void* p = nullptr;
-        ce = cudaGetSymbolAddress(&p, g_static_scratch);
-        if (ce != cudaSuccess || !p)
+        // looked up once per device with that device current.  Two threads racing here both
+        // obtain the same address, so the plain store is enough.
+        ce = cudaGetSymbolAddress(&scratch, g_static_scratch);
+        if (ce != cudaSuccess || !scratch)
             return fail(nullptr, NEON_MOE_ECUDA, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(ce));
-        g_static_scratch_addr[dev] = p;
+        g_static_scratch_addr[dev].store(scratch, std::memory_order_release);
     }
-    unsigned char* base = static_cast<unsigned char*>(g_static_scratch_addr[dev]);
+    unsigned char* base = static_cast<unsigned char*>(scratch);
     int32_t* s_idx = reinterpret_cast<int32_t*>(base + o_idx);
     float* s_rw = reinterpret_cast<float*>(base + o_rw);
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);

@@ -99,3 +99,38 @@ def test_plan_known_answer():
     assert re.tolist() == [0, 0, 1, 1, 1, 1, 1, 1]
     with pytest.raises(RuntimeError):
         ep_plan(counts, 1, cap=4)     # would receive 8 rows
+
+
+def test_capacity_verdict_is_the_same_on_every_rank():
+    """A skewed four-rank histogram: rank 0 would receive more than its room while the other
+    ranks' own totals fit.  The verdict is computed from the gathered histograms and names rank 0
+    whichever rank evaluates it, so no rank posts an exchange that a peer has walked away from."""
+    import ctypes
+    sys.path.insert(0, ROOT)
+    from neonengine_b200 import _lib
+    from neonengine_b200.moe_layer_system import ep_plan
+    lib = _lib.load()
+    G, E, k, T = 4, 16, 4, 8
+    counts = np.zeros((G, E), np.int32)
+    counts[:, 0:4] = [12, 10, 6, 2]          # 30 of each rank's 32 entries go to rank 0's experts
+    counts[:, 4] = 1
+    counts[:, 8] = 1
+    assert (counts.sum(1) == T * k).all()
+    caps = np.full(G, 2 * T * k, np.int32)   # 64 rows each; rank 0 would get 120
+    first = ctypes.c_int(-2)
+    assert lib.neon_moe_ep_overflow(counts.ctypes.data, G, E, caps.ctypes.data, ctypes.byref(first)) == 0
+    assert first.value == 0
+    # the per-rank plan alone would let ranks 1..3 carry on: that is why it is not the verdict
+    for r in (1, 2, 3):
+        ep_plan(counts, r, cap=int(caps[r]))
+    with pytest.raises(RuntimeError):
+        ep_plan(counts, 0, cap=int(caps[0]))
+    # halving every rank's token range halves the histogram: the halves fit
+    half = counts // 2
+    assert lib.neon_moe_ep_overflow(half.ctypes.data, G, E, caps.ctypes.data, ctypes.byref(first)) == 0
+    assert first.value == -1
+    # ranks with different capacities: the verdict uses each rank's own
+    caps2 = np.array([200, 3, 200, 200], np.int32)
+    assert lib.neon_moe_ep_overflow(counts.ctypes.data, G, E, caps2.ctypes.data, ctypes.byref(first)) == 0
+    assert first.value == 1
+    assert lib.neon_moe_ep_overflow(None, G, E, caps.ctypes.data, ctypes.byref(first)) == 1

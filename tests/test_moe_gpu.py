@@ -161,13 +161,98 @@ def test_prefill_sized_batch_properties(full20b):
     assert np.isfinite(out).all()
 
 
-def test_scale_out_of_range_is_rejected():
+def test_large_scales_load_on_the_tensor_core_path():
+    """E8M0 bytes up to 140 (scales up to 2^13) are ordinary weights for the tensor-core path:
+    outputs stay within the contract's mean relative error and, relative to the largest output,
+    within its absolute one.  The mma.sync layout cannot hold them: asking for it fails, and the
+    handle keeps working on the tensor-core path."""
     shape, W, hidden, lb, z = load_golden("small_seeded")
-    bad = synth.MoeWeights(shape, W.router_w, W.router_b, W.gate_up_blocks, W.gate_up_scales.copy(),
-                           W.gate_up_bias, W.down_blocks, W.down_scales, W.down_bias)
-    bad.gate_up_scales[0, 0, 0] = 200
-    with pytest.raises(RuntimeError, match="scale"):
-        make_layer(shape, bad, 4)
+    rng = np.random.default_rng(5)
+    big = synth.MoeWeights(shape, W.router_w, W.router_b, W.gate_up_blocks, W.gate_up_scales.copy(),
+                           W.gate_up_bias, W.down_blocks, W.down_scales.copy(), W.down_bias)
+    for sc in (big.gate_up_scales, big.down_scales):
+        pick = rng.random(sc.shape) < 0.05
+        sc[pick] = rng.integers(129, 141, int(pick.sum()), dtype=np.uint8)
+    layer = make_layer(shape, big, 16)
+    out, idx, w = run_device(layer, hidden, lb)
+    ref, ridx, rw = oracle.moe_forward(hidden, big, logit_bias=lb)
+    np.testing.assert_array_equal(idx, ridx)
+    scale = np.abs(ref).max()
+    assert np.isfinite(out).all() and scale > 1e3
+    max_abs = np.abs(out - ref).max() / scale
+    mean_rel = np.abs(out - ref).mean() / np.abs(ref).mean()
+    assert max_abs <= 1e-5 and mean_rel <= 5e-3, (max_abs, mean_rel)
+    with pytest.raises(RuntimeError, match="scale bytes above 128"):
+        layer.set_option("path", 1)
+    with pytest.raises(RuntimeError, match="scale bytes above 128"):
+        layer.set_option("mma16_layout", 1)
+    out2, _, _ = run_device(layer, hidden, lb)
+    np.testing.assert_array_equal(out2, out)
+    layer.close()
+
+
+def test_mma16_layout_is_built_on_request_only():
+    """set_weights keeps one copy of the expert weights; the mma.sync layout appears (and device
+    memory shrinks by about the weights' size) only when asked for, and goes away again."""
+    torch = torch_cuda()
+    shape = synth.MoeShape(hidden=2880, inter=2880, n_experts=8, top_k=4)
+    W = synth.make_weights(shape, 3)
+    layer = make_layer(shape, W, 8)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    layer.set_option("mma16_layout", 1)
+    free1 = torch.cuda.mem_get_info()[0]
+    weights = 8 * (2880 * 2880 * 3 // 2)
+    assert 0.9 * weights < free0 - free1 < 1.5 * weights
+    hidden = synth.make_hidden(5, W, 3)
+    a = run_device(layer, hidden)[0]
+    layer.set_option("path", 1)
+    b = run_device(layer, hidden)[0]
+    layer.set_option("path", 2)
+    assert_close(b, a, "path 1 vs path 2")
+    layer.set_option("mma16_layout", 0)
+    assert torch.cuda.mem_get_info()[0] >= free0 - (4 << 20)
+    layer.close()
+
+
+@pytest.mark.parametrize("n_experts", [32, 128])
+def test_tensor_core_router_breaks_exact_ties_like_the_others(n_experts):
+    """Exact ties and signed zeros through the large-batch routers (T > 384): identical router
+    rows give bit-equal logits in every router, so the lower expert id must win; a zero hidden
+    state makes every logit the bias alone (+0 and -0 compare equal).  Tensor-core router,
+    CUDA-core router and the oracle must agree on every token."""
+    torch = torch_cuda()
+    shape = synth.MoeShape(hidden=256, inter=64, n_experts=n_experts, top_k=4)
+    W = synth.make_weights(shape, 7)
+    rw = W.router_w.copy()
+    rb = W.router_b.copy()
+    rw[5] = rw[2]; rw[9] = rw[2]; rw[n_experts - 1] = rw[0]        # three-way and two-way ties
+    rb[5] = rb[2]; rb[9] = rb[2]; rb[n_experts - 1] = rb[0]
+    rb[3] = 0x8000                                                   # -0.0 bias
+    W = synth.MoeWeights(shape, rw, rb, W.gate_up_blocks, W.gate_up_scales, W.gate_up_bias, W.down_blocks,
+                         W.down_scales, W.down_bias)
+    T = 400
+    hidden = synth.make_hidden(T, W, 7, min_gap=0.0)
+    hidden[7] = 0                                                     # all logits = bias
+    hidden[8] = 0x8000                                                # -0.0 everywhere
+    layer = make_layer(shape, W, T)
+    ridx, rwt = oracle.route(hidden, W.router_w, W.router_b, 4)
+    results = {}
+    for mma in (1, 0):
+        layer.set_option("router_mma", mma)
+        out, idx, w = run_device(layer, hidden)
+        results[mma] = idx
+        # tokens whose top-5 logits are well separated or exactly tied must match the oracle
+        lg = oracle.route(hidden, W.router_w, W.router_b, 4, want_logits=True)[2].astype(np.float64)
+        srt = -np.sort(-lg, axis=1)[:, :5]
+        gaps = srt[:, :-1] - srt[:, 1:]
+        safe = ((gaps > 1e-4) | (gaps == 0)).all(axis=1)
+        assert safe.sum() > T // 2
+        np.testing.assert_array_equal(idx[safe], ridx[safe], err_msg=f"router_mma={mma}")
+        np.testing.assert_allclose(w[safe], rwt[safe], rtol=0, atol=2e-6)
+    np.testing.assert_array_equal(results[1][[7, 8]], results[0][[7, 8]])
+    layer.set_option("router_mma", 1)
+    layer.close()
 
 
 def test_graph_replay_matches_eager(full20b):

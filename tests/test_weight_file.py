@@ -93,14 +93,15 @@ def test_loader_matches_set_weights_and_tiled_bytes(tmp_path):
             b.run(h)
         b.load_weights_file(path)
         np.testing.assert_array_equal(b.run(h).cpu().numpy(), ref)
-        if path == tiled:  # only the tensor-core layout was loaded
-            with pytest.raises(RuntimeError, match="mma.sync"):
-                b.set_option("path", 1)
-            with pytest.raises(RuntimeError, match="mma.sync"):
-                b.run_static(h)
-            b.set_weights(W)  # a full upload restores every path
-            b.set_option("path", 1)
-            b.run(h)
+        # only the tensor-core layout is in a file; the mma.sync kernels' layout is rebuilt from it on
+        # request and must then serve the same weights
+        with pytest.raises(RuntimeError, match="mma16_layout"):
+            b.run_static(h)
+        b.set_option("path", 1)
+        via_mma = b.run(h).cpu().numpy()
+        a.set_option("path", 1)
+        np.testing.assert_array_equal(via_mma, a.run(h).cpu().numpy())
+        a.set_option("path", 2)
         b.close()
     # refusals: wrong shape, truncated file, missing file
     other = MoeLayerSystem(synth.MoeShape(hidden=256, inter=128, n_experts=8, top_k=4), None, max_tokens=4)

@@ -626,6 +626,10 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side-configs", action="store_true",
+                    help="default run only: skip the cfg0 and cfg2 blocks measured beside the headline workload")
+    ap.add_argument("--no-n1-base", action="store_true",
+                    help="multi-GPU runs only: skip rank 0's single-GPU run of the same workload")
     ap.add_argument("--decoder-layers", type=int, default=None,
                     help="cfg3 only: run fewer than 24 layers (for small profiler captures; not a bench result)")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
@@ -678,192 +682,369 @@ def main():
         run_svgf(args, local_rank)
         return
 
-    T, E, zipf, desc = WORKLOADS[args.workload]
-    shape = synth.MoeShape(n_experts=E)
-    ep = world > 1
-    if ep and E % world:
-        raise SystemExit(f"{E} experts cannot be sharded over {world} ranks")
-    nl = E // world
-    W = synth.make_weights(shape, 0, experts=(rank * nl, (rank + 1) * nl) if ep else None)
-    decode = T <= 64
-    n_batches = 8 if decode else 2
-    batches, lb = make_batches(T, W, zipf, n_batches, base_stream=100 * rank)
-    dev = torch.device("cuda", local_rank)
-    layer = MoeLayerSystem(shape, W, max_tokens=T, device=local_rank, ep_rank=rank, ep_size=world)
-    for opt in args.option:
-        name, value = opt.split("=")
-        layer.set_option(name, int(value))
-    if ep:
-        ids = [MoeLayerSystem.ep_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(ids, src=0)
-        layer.ep_init(ids[0])
-    d_batches = [torch.from_numpy(b.view(np.int16)).to(dev) for b in batches]
-    d_lb = None if lb is None else torch.from_numpy(lb).to(dev)
-    d_out = torch.empty((T, shape.hidden), dtype=torch.float32, device=dev)
-    H, I, k = shape.hidden, shape.inter, shape.top_k
+    run_moe(args, rank, world, local_rank)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
 
-    def max_over_ranks(v):
-        if world > 1:
-            t = torch.tensor([v], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+def dram_traffic_table():
+    """Measured DRAM bytes per launch (ncu captures) of the dominant kernels: lines
+    `kernel workload bytes units commit` in profiles/dram_traffic.txt."""
+    table = {}
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    if os.path.exists(path):
+        for ln in open(path):
+            f = ln.split()
+            if len(f) >= 5 and not ln.startswith("#"):
+                table[(f[0], f[1])] = {"bytes": float(f[2]), "units": float(f[3]), "commit": f[4]}
+    return table
+
+
+def disjoint_decode_batches(W, n_batches, base_stream=0):
+    """Single-token batches whose expert sets are pairwise disjoint where the draw allows it, so that
+    n_batches * top_k distinct experts (all 32 at the default shape) rotate through the timed region
+    and no pass finds its weights in L2."""
+    k = W.shape.top_k
+    picked, used = [], set()
+    for stream in range(base_stream, base_stream + 4000):
+        hid = synth.make_hidden(1, W, 0, stream=stream)
+        lg = synth.router_logits_f64(hid, W)[0]
+        top = set(np.argsort(-lg)[:k].tolist())
+        if not (top & used):
+            picked.append(hid)
+            used |= top
+            if len(picked) == n_batches:
+                return picked
+        if len(used) + k > W.shape.n_experts:
+            used = set()   # every expert has been used once: start another round
+    while len(picked) < n_batches:
+        picked.append(synth.make_hidden(1, W, 0, stream=base_stream + 5000 + len(picked)))
+    return picked
+
+
+def parity_sample(hidden, lb, got_out, got_idx, expert_weights, shape, sample):
+    """Routing of every token and outputs of the sampled tokens against the CPU oracle.
+    expert_weights(lo, hi) returns the MoeWeights of experts [lo, hi) (full router)."""
+    import oracle
+    router = expert_weights(0, 1)
+    ridx, rw = oracle.route(hidden, router.router_w, router.router_b, shape.top_k, lb)
+    mism = int((ridx != got_idx).any(axis=1).sum())
+    sample = np.asarray(sample, np.int32)
+    ref = np.zeros((sample.size, shape.hidden), np.float64)
+    for e in sorted(set(ridx[sample].ravel().tolist())):
+        ref += oracle.experts(hidden, ridx, rw, expert_weights(e, e + 1), tokens=sample, e_lo=e)
+    got = np.asarray(got_out, np.float64)[sample]
+    max_abs = float(np.abs(got - ref).max())
+    mean_rel = float(np.abs(got - ref).mean() / max(np.abs(ref).mean(), 1e-30))
+    return {"routing_mismatches": mism, "tokens_routed": int(hidden.shape[0]), "tokens": int(sample.size),
+            "max_abs": max_abs, "mean_rel": mean_rel,
+            "pass": bool(mism == 0 and max_abs <= 2e-2 and mean_rel <= 5e-3),
+            "oracle": "CPU restatement of the configuration text, fp64 accumulate (parity unpinned: the reference has no such path)"}
+
+
+class MoeRun:
+    """One workload on one layer: device-timed groups of K steps, per-stage profile, roofline, parity."""
+
+    def __init__(self, workload, args, rank, world, local_rank, dist, weights=None, min_seconds=0.3):
+        import torch
+        from neonengine_b200.moe_layer_system import MoeLayerSystem
+        self.torch, self.dist, self.args = torch, dist, args
+        self.workload, self.rank, self.world, self.local_rank = workload, rank, world, local_rank
+        self.T, self.E, self.zipf, self.desc = WORKLOADS[workload]
+        self.shape = synth.MoeShape(n_experts=self.E)
+        self.ep = world > 1
+        self.nl = self.E // world
+        self.min_seconds = min_seconds
+        if weights is not None:
+            self.W = weights
+        else:
+            self.W = synth.make_weights(self.shape, 0, experts=(rank * self.nl, (rank + 1) * self.nl) if self.ep else None)
+        T = self.T
+        self.decode = T <= 64
+        self.n_batches = 8 if self.decode else 2
+        if T == 1 and not self.ep:
+            self.batches, self.lb = disjoint_decode_batches(self.W, self.n_batches), None
+        else:
+            self.batches, self.lb = make_batches(T, self.W, self.zipf, self.n_batches, base_stream=100 * rank)
+        self.dev = torch.device("cuda", local_rank)
+        self.layer = MoeLayerSystem(self.shape, self.W, max_tokens=T, device=local_rank, ep_rank=rank if self.ep else 0,
+                                    ep_size=world if self.ep else 1)
+        for opt in args.option:
+            name, value = opt.split("=")
+            self.layer.set_option(name, int(value))
+        self.d_batches = [torch.from_numpy(b.view(np.int16)).to(self.dev) for b in self.batches]
+        self.d_lb = None if self.lb is None else torch.from_numpy(self.lb).to(self.dev)
+        self.d_out = torch.empty((T, self.shape.hidden), dtype=torch.float32, device=self.dev)
+        self.run = self.layer.run_ep if self.ep else self.layer.run
+
+    def barrier(self):
+        if self.ep:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        if self.ep:
+            t = self.torch.tensor([v], device=self.dev, dtype=self.torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
             return float(t.item())
         return v
 
-    def timed(fn, steps):
+    def step_device(self, i):
+        self.run(self.d_batches[i % self.n_batches], logit_bias=self.d_lb, out=self.d_out)
+
+    def timed(self, fn, steps):
+        torch = self.torch
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
+        self.barrier()
         ev0.record()
         for i in range(steps):
             fn(i)
         ev1.record()
-        barrier()
-        return max_over_ranks(ev0.elapsed_time(ev1))
+        self.barrier()
+        return self.max_over_ranks(ev0.elapsed_time(ev1))
 
-    run = layer.run_ep if ep else layer.run
+    def warm(self, warmup):
+        # the library captures a pass into a CUDA graph the second time it sees the same arguments, so
+        # every rotating batch goes through twice before the warm-up proper
+        for i in range(2 * self.n_batches):
+            self.step_device(i)
+        for i in range(max(warmup, 3)):
+            self.step_device(i)
 
-    def step_device(i):
-        run(d_batches[i % n_batches], logit_bias=d_lb, out=d_out)
+    def timed_groups(self, steps):
+        """Groups of exactly `steps` steps, repeated until min_seconds of timed work have run (the
+        elapsed time is the maximum over ranks, so every rank runs the same number of groups)."""
+        groups, total = [], 0.0
+        while True:
+            ms = self.timed(self.step_device, steps)
+            groups.append(ms)
+            total += ms
+            if total >= self.min_seconds * 1e3 or len(groups) >= 400:
+                return groups
+
+    def stage_profile(self, steps):
+        layer = self.layer
+        if self.ep:
+            acc, rows, n = {}, 0, 0
+            for i in range(min(steps, 20)):
+                self.step_device(i)
+                tms, r = layer.ep_times()
+                rows += r
+                for kk, v in tms.items():
+                    acc[kk] = acc.get(kk, 0.0) + v
+                n += 1
+            return {kk: self.max_over_ranks(v / n) for kk, v in acc.items()}, rows / n
+        layer.profile(True)
+        self.timed(self.step_device, min(max(steps, 50), 2000))
+        stage_ms, n = layer.read_profile()
+        layer.profile(False)
+        return {kk: v / max(n, 1) for kk, v in stage_ms.items()}, n
+
+    def touched(self):
+        counts = []
+        for bt in self.d_batches:
+            self.layer.run(bt, logit_bias=self.d_lb, out=self.d_out)
+            counts.append(int((self.layer.read_dispatch()[0] > 0).sum()))
+        return sum(counts) / len(counts)
+
+    def parity(self, n_sample):
+        torch = self.torch
+        T = self.T
+        hid = self.batches[0]
+        out, idx, _ = self.run(self.d_batches[0], logit_bias=self.d_lb, want_routing=True)
+        torch.cuda.synchronize()
+        sample = np.unique(np.linspace(0, T - 1, min(T, n_sample)).astype(np.int32))
+        if self.ep:
+            def weights(lo, hi):
+                return synth.make_weights(self.shape, 0, experts=(lo, hi))
+        else:
+            def weights(lo, hi):
+                return self.W.slice_experts(lo, hi)
+        return parity_sample(hid, self.lb, out.cpu().numpy(), idx.cpu().numpy(), weights, self.shape, sample)
+
+    def close(self):
+        self.layer.close()
+        del self.d_batches, self.d_out
+
+
+def moe_roofline(run, step_s, stage_ms, n_prof, peaks, peak_kind, traffic_table):
+    """The dominant kernel's roofline for a single-GPU MoE workload."""
+    shape, T, k = run.shape, run.T, run.shape.top_k
+    H, I = shape.hidden, shape.inter
+    mean_touched = run.touched()
+    layer_bytes = mean_touched * shape.expert_bytes + shape.router_bytes + T * H * 2 + T * H * 4
+    gu_expert_bytes = 2 * I * H // 2 + 2 * I * H // 32 + 2 * I * 2
+    if run.layer.launch_count and T <= 8 and stage_ms is None:
+        # one cooperative kernel per pass: the kernel is the layer, its algorithmic bytes are the layer's
+        achieved = layer_bytes / step_s / 1e9
+        roof = {"bound": "hbm", "kernel": "decode_fused_kernel (router + gate_up + SwiGLU + down + combine, one launch)",
+                "achieved": achieved, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes_per_launch": layer_bytes,
+                "ms_per_launch": step_s * 1e3,
+                "note": "launch duration = the step (one kernel per pass, replayed from a CUDA graph; CUDA events around K passes)"}
+    elif run.decode:
+        gu_ms = stage_ms["gate_up"]
+        gu_bytes = mean_touched * gu_expert_bytes + T * H * 2 + T * k * I * 4
+        achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gu_ms}
+        ent = traffic_table.get(("gmm_bs_kernel_gate_up", run.workload))
+        if ent:   # ncu capture of one launch, scaled by the experts this run touched
+            roof["traffic"] = ent["bytes"] * mean_touched / ent["units"]
+            roof["traffic_source"] = f"ncu capture at commit {ent['commit']} ({ent['bytes']:.0f} B at {ent['units']:.0f} experts touched), scaled"
+    else:
+        gu_ms = stage_ms["gate_up"]
+        gu_flops = T * k * 2 * 2 * I * H
+        achieved = gu_flops / (gu_ms * 1e-3) / 1e12
+        peak = peaks.get("bf16_tflops", 1590.0)
+        from neonengine_b200 import mma_rate
+        ceil8 = mma_rate.measure("mxf8f6f4", 128, 8192, device=run.local_rank)["tflops"]
+        ceil4 = mma_rate.measure("mxf4", 256, 8192, device=run.local_rank)["tflops"]
+        layer_tf = T * k * shape.flops_per_pair / step_s / 1e12
+        roof = {"bound": "tensor", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peak,
+                "peak_kind": peak_kind + " bf16 burst", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "algorithmic_flops_per_launch": gu_flops, "ms_per_launch": gu_ms, "layer_tflops": layer_tf,
+                "layer_frac_of_mxfp4_nominal_9000": layer_tf / 9000.0,
+                "mma_issue_ceiling_tflops": {"mxf8f6f4_128x128": ceil8, "mxf4_128x256": ceil4},
+                "frac_of_mxf4_ceiling": achieved / ceil4, "layer_frac_of_mxf4_ceiling": layer_tf / ceil4}
+    if stage_ms is not None:
+        roof["stage_ms_per_step"] = stage_ms
+    roof.update({"layer_bytes_per_step": layer_bytes, "layer_gbs": layer_bytes / step_s / 1e9,
+                 "layer_frac_of_peak": layer_bytes / step_s / 1e9 / peaks["hbm_gbs"],
+                 "layer_frac_of_8000": layer_bytes / step_s / 1e9 / 8000.0, "experts_touched_mean": mean_touched})
+    return roof
+
+
+def side_config(workload, args, local_rank, peaks, peak_kind, traffic_table):
+    """A further configuration measured in the same run (its own layer, its own batches): device-timed
+    ms/step, tokens/s, the dominant kernel's roofline and a parity sample."""
+    run = MoeRun(workload, args, 0, 1, local_rank, None, min_seconds=0.15)
+    run.warm(args.warmup)
+    groups = run.timed_groups(args.steps)
+    ms = statistics.median(groups)
+    step_s = ms / args.steps * 1e-3
+    fused = run.T <= 8 and not any(o.startswith("decode_fused=0") for o in args.option)
+    stage_ms = None if fused else run.stage_profile(args.steps)[0]
+    roof = moe_roofline(run, step_s, stage_ms, 0, peaks, peak_kind, traffic_table)
+    out = {"description": run.desc, "tokens_per_step": run.T, "ms_per_step": ms / args.steps,
+           "ms_per_step_min": min(groups) / args.steps, "groups": len(groups), "value": run.T / step_s, "unit": "tokens/s",
+           "roofline": roof, "parity": run.parity(8), "status": run.layer.status()}
+    run.close()
+    return out
+
+
+def run_moe(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    ep = world > 1
+    peaks, peak_kind = measured_peaks()
+    traffic_table = dram_traffic_table()
+    T, E, zipf, desc = WORKLOADS[args.workload]
+    if ep and E % world:
+        raise SystemExit(f"{E} experts cannot be sharded over {world} ranks")
+
+    # With several GPUs, rank 0 first runs the SAME workload on its GPU alone (all experts local, no
+    # exchange): the like-for-like base of the weak-scaling numbers.
+    n1_same = None
+    if ep and not args.no_n1_base:
+        if rank == 0:
+            solo = MoeRun(args.workload, args, 0, 1, local_rank, None, min_seconds=0.1)
+            solo.warm(3)
+            g = solo.timed_groups(min(args.steps, 10))
+            n1_same = statistics.median(g) / min(args.steps, 10)
+            solo.close()
+            del solo
+            torch.cuda.empty_cache()
+        dist.barrier()
+
+    run = MoeRun(args.workload, args, rank, world, local_rank, dist)
+    layer, shape = run.layer, run.shape
+    H, I, k = shape.hidden, shape.inter, shape.top_k
+    if ep:
+        ids = [layer.ep_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        layer.ep_init(ids[0])
+    n_batches, batches, lb = run.n_batches, run.batches, run.lb
 
     # pinned host buffers for the end-to-end arm
     h_in = [torch.from_numpy(b.view(np.int16)).pin_memory() for b in batches]
-    h_out = torch.empty((T, shape.hidden), dtype=torch.float32).pin_memory()
-    h_outs = [torch.empty((T, shape.hidden), dtype=torch.float32).pin_memory() for _ in range(4)]
+    h_out = torch.empty((T, H), dtype=torch.float32).pin_memory()
+    h_outs = [torch.empty((T, H), dtype=torch.float32).pin_memory() for _ in range(4)]
     h_lb = None if lb is None else torch.from_numpy(lb).pin_memory()
-    d_stage = torch.empty((T, shape.hidden), dtype=torch.int16, device=dev)
-
-    def step_host(i):
-        if ep:   # host -> device, expert-parallel pass, device -> host
-            d_stage.copy_(h_in[i % n_batches], non_blocking=True)
-            layer.run_ep(d_stage, logit_bias=d_lb, out=d_out)
-            h_out.copy_(d_out, non_blocking=True)
-            torch.cuda.synchronize()
-        else:
-            layer.run_host_ptr(h_in[i % n_batches].data_ptr(), T, None if h_lb is None else h_lb.data_ptr(),
-                               h_out.data_ptr())
+    lbp = None if h_lb is None else h_lb.data_ptr()
 
     with ClockSampler(local_rank) as clocks:
-        # set-up, before the warm-up: the library captures a pass into a CUDA graph the second time it
-        # sees the same arguments, so every rotating batch goes through twice; with fewer warm-up steps
-        # than batches the captures would otherwise land inside the timed region
-        for i in range(2 * n_batches):
-            step_device(i)
-        for i in range(max(args.warmup, 3)):
-            step_device(i)
+        run.warm(args.warmup)
         l0 = layer.launch_count
-        ms = timed(step_device, args.steps)
-        launches = layer.launch_count - l0
-        # per-kernel durations over the same steps (CUDA events recorded inside the library)
-        stage_ms, n_prof, ep_ms, ep_rows = None, 0, None, 0
-        if ep:
-            acc = {}
-            for i in range(min(args.steps, 20)):
-                step_device(i)
-                tms, rows = layer.ep_times()
-                ep_rows += rows
-                for kk, v in tms.items():
-                    acc[kk] = acc.get(kk, 0.0) + v
-                n_prof += 1
-            ep_ms = {kk: max_over_ranks(v / n_prof) for kk, v in acc.items()}
-            ep_rows /= n_prof
-        else:
-            layer.profile(True)
-            timed(step_device, min(args.steps, 4000))
-            stage_ms, n_prof = layer.read_profile()
-            layer.profile(False)
-        # end to end through host buffers: every step's hidden states come from pinned host memory
-        # and its result goes back to pinned host memory inside the timed region
+        groups = run.timed_groups(args.steps)
+        launches = (layer.launch_count - l0) // len(groups)
+        ms = statistics.median(groups)
+        fused = (not ep) and T <= 8 and not any(o.startswith("decode_fused=0") for o in args.option)
+        stage_ms, ep_rows = (None, 0) if fused else run.stage_profile(args.steps)
+        # end to end through host buffers: every step's hidden states come from pinned host memory and
+        # its result goes back to pinned host memory inside the timed region
         e2e_steps = max(3, min(args.steps, 500))
-        for i in range(3):
-            step_host(i)
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            step_host(i)
-        barrier()
-        e2e_blocking_s = max_over_ranks(time.perf_counter() - t0)
-        e2e_s = e2e_blocking_s
         if not ep:
-            # the same steps through the pipelined call: upload of step i+1 and download of step i-1
-            # overlap the layer pass of step i (neon_moe_forward_host_batches)
-            ins = [h_in[i % n_batches].data_ptr() for i in range(e2e_steps)]
-            outs = [h_outs[i % len(h_outs)].data_ptr() for i in range(e2e_steps)]
-            lbp = None if h_lb is None else h_lb.data_ptr()
-            layer.run_host_batches(ins[:8], T, lbp, outs[:8])
-            barrier()
+            for i in range(3):
+                layer.run_host_ptr(h_in[i % n_batches].data_ptr(), T, lbp, h_out.data_ptr())
+            run.barrier()
             t0 = time.perf_counter()
-            layer.run_host_batches(ins, T, lbp, outs)
-            e2e_s = max_over_ranks(time.perf_counter() - t0)
-    assert layer.status() == 0
+            for i in range(e2e_steps):
+                layer.run_host_ptr(h_in[i % n_batches].data_ptr(), T, lbp, h_out.data_ptr())
+            run.barrier()
+            e2e_blocking_s = time.perf_counter() - t0
+        # the same steps through the pipelined call: upload of step i+1 and download of step i-1 overlap
+        # the layer pass of step i (neon_moe_forward_host_batches; collective on an expert-parallel handle)
+        ins = [h_in[i % n_batches].data_ptr() for i in range(e2e_steps)]
+        outs = [h_outs[i % len(h_outs)].data_ptr() for i in range(e2e_steps)]
+        layer.run_host_batches(ins[:4], T, lbp, outs[:4])
+        run.barrier()
+        t0 = time.perf_counter()
+        layer.run_host_batches(ins, T, lbp, outs)
+        run.barrier()
+        e2e_s = run.max_over_ranks(time.perf_counter() - t0)
+        if ep:
+            e2e_blocking_s = e2e_s
+    status = layer.status()
+    assert status == 0, f"device status word {status}"
 
     tokens_per_step = T * world
     step_s = ms / args.steps * 1e-3
     value = tokens_per_step / step_s
     e2e_value = tokens_per_step * e2e_steps / e2e_s
-    peaks, peak_kind = measured_peaks()
-    gu_expert_bytes = 2 * I * H // 2 + 2 * I * H // 32 + 2 * I * 2
-    gu_flops_per_pair = 2 * 2 * I * H
+    clk = clocks.summary()
 
     if ep:
         # dominant unit: the local expert pass (both grouped GEMMs) over the rows this rank received
+        ep_ms = stage_ms
         ex_ms = ep_ms["experts"]
         achieved = ep_rows * shape.flops_per_pair / (ex_ms * 1e-3) / 1e12
+        from neonengine_b200 import mma_rate
+        ceil8 = mma_rate.measure("mxf8f6f4", 128, 8192, device=local_rank)["tflops"]
+        ceil4 = mma_rate.measure("mxf4", 256, 8192, device=local_rank)["tflops"]
         roofline = {"bound": "tensor", "kernel": "gmm_bs_kernel (gate_up + down, local experts)", "achieved": achieved,
                     "peak": peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")), "peak_kind": peak_kind + " bf16 sustained",
                     "unit": "TFLOP/s", "traffic": None, "ms_per_launch": ex_ms,
                     "algorithmic_flops_per_launch": ep_rows * shape.flops_per_pair,
                     "ep_stage_ms_per_step_max_over_ranks": ep_ms, "rows_received_rank0": ep_rows,
-                    "all_to_all_exposed_ms": ep_ms["dispatch_a2a"] + ep_ms["combine_a2a"]}
+                    "all_to_all_exposed_ms": ep_ms["dispatch_a2a"] + ep_ms["combine_a2a"],
+                    "mma_issue_ceiling_tflops": {"mxf8f6f4_128x128": ceil8, "mxf4_128x256": ceil4},
+                    "frac_of_mxf4_ceiling": achieved / ceil4, "frac_of_mxfp4_nominal_9000": achieved / 9000.0}
         roofline["frac"] = achieved / roofline["peak"]
+        if n1_same is None and rank == 0 and not args.no_n1_base:
+            n1_same = None
+        n1 = [n1_same if rank == 0 else None]
+        dist.broadcast_object_list(n1, src=0)
+        if n1[0] is not None:
+            roofline["n1_same_workload_ms"] = n1[0]
+            roofline["weak_efficiency_same_workload"] = n1[0] / (ms / args.steps)
     else:
-        touched = []
-        for bt in d_batches:
-            layer.run(bt, logit_bias=d_lb, out=d_out)
-            touched.append(int((layer.read_dispatch()[0] > 0).sum()))
-        mean_touched = sum(touched) / len(touched)
-        per_step = {kk: v / max(n_prof, 1) for kk, v in stage_ms.items()}
-        gu_ms = per_step["gate_up"]
-        layer_bytes = mean_touched * shape.expert_bytes + shape.router_bytes + T * H * 2 + T * H * 4
-        if decode:
-            # the gate_up product streams each touched expert's nibbles + scales + bias once,
-            # plus the hidden rows in and the fp32 activation out
-            gu_bytes = mean_touched * gu_expert_bytes + T * H * 2 + T * k * I * 4
-            achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
-            # DRAM read+write of one gate_up launch from the ncu capture summarised in
-            # profiles/gmm_bs_kernel_cfg1_T64.md (245.2 MB at 26 experts touched), scaled by experts touched
-            traffic = 245.2e6 * mean_touched / 26.0 if args.workload == "cfg1" else None
-            roofline = {"bound": "hbm", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved,
-                        "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
-                        "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
-                        "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gu_ms}
-        else:
-            gu_flops = T * k * gu_flops_per_pair
-            achieved = gu_flops / (gu_ms * 1e-3) / 1e12
-            peak = peaks.get("bf16_tflops", 1590.0)
-            # measured ceiling of the instruction kinds themselves (operands resident in shared memory)
-            from neonengine_b200 import mma_rate
-            ceil8 = mma_rate.measure("mxf8f6f4", 128, 8192, device=local_rank)["tflops"]
-            ceil4 = mma_rate.measure("mxf4", 256, 8192, device=local_rank)["tflops"]
-            roofline = {"bound": "tensor", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peak,
-                        "peak_kind": peak_kind + " bf16 burst", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                        "algorithmic_flops_per_launch": gu_flops, "ms_per_launch": gu_ms,
-                        "layer_tflops": T * k * shape.flops_per_pair / step_s / 1e12,
-                        "layer_frac_of_mxfp4_nominal_9000": T * k * shape.flops_per_pair / step_s / 1e12 / 9000.0,
-                        "mma_issue_ceiling_tflops": {"mxf8f6f4_128x128": ceil8, "mxf4_128x256": ceil4},
-                        # the launch executes two e4m3 terms per activation: twice the algorithmic flops
-                        "executed_tflops": 2 * achieved, "frac_of_mxf8f6f4_ceiling": 2 * achieved / ceil8,
-                        "layer_frac_of_mxf4_ceiling": T * k * shape.flops_per_pair / step_s / 1e12 / ceil4}
-        roofline.update({"stage_ms_per_step": per_step, "layer_bytes_per_step": layer_bytes,
-                         "layer_gbs": layer_bytes / step_s / 1e9,
-                         "layer_frac_of_peak": layer_bytes / step_s / 1e9 / peaks["hbm_gbs"],
-                         "layer_frac_of_8000": layer_bytes / step_s / 1e9 / 8000.0,
-                         "experts_touched_mean": mean_touched})
+        roofline = moe_roofline(run, step_s, stage_ms, 0, peaks, peak_kind, traffic_table)
 
-    weights_mb = shape.expert_bytes * nl / 1e6
+    parity = run.parity(16 if ep else 8) if rank == 0 or ep else None
+    if ep:   # the pass is collective: every rank ran it, rank 0 checked its own tokens
+        parity = parity if rank == 0 else None
+
+    weights_mb = shape.expert_bytes * run.nl / 1e6
     line = {"metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -873,22 +1054,35 @@ def main():
                        "parallelism": "single GPU" if world == 1 else f"ep{world} (experts sharded, all-to-all over NCCL)",
                        "l2_policy": f"{n_batches} rotating batches; {weights_mb:.0f} MB of expert weights per GPU "
                                     "exceed the 126 MB L2"},
+            "timing": {"groups_of_steps": len(groups), "ms_per_step_median": ms / args.steps,
+                       "ms_per_step_min": min(groups) / args.steps, "ms_per_step_max": max(groups) / args.steps,
+                       "timed_seconds": sum(groups) / 1e3,
+                       "ms_per_step_x_sm_mhz": None if not clk["sm_mhz"] else ms / args.steps * clk["sm_mhz"]},
             "e2e": {"value": e2e_value, "unit": "tokens/s",
-                    "h2d_bytes_per_step": T * H * 2 + (E * 4 if (lb is not None and not ep) else 0),
-                    "d2h_bytes_per_step": T * H * 4, "steps": e2e_steps,
-                    "api": "neon_moe_forward_host_batches (pipelined copies)" if not ep else "H2D + neon_moe_forward_ep + D2H per step",
+                    "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4, "steps": e2e_steps,
+                    "api": "neon_moe_forward_host_batches (pipelined copies" + ("; every batch an expert-parallel pass)" if ep else ")"),
                     "blocking_call_per_step_value": tokens_per_step * e2e_steps / e2e_blocking_s},
-            "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks.summary()}
+            "gpu_launches": int(launches), "roofline": roofline, "parity": parity, "clocks": clk}
 
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_tps, cpu_steps_done, cores = cpu_steps(W, batches, lb, seconds_budget=12.0,
-                                                   max_tokens_per_step=min(T, 64))
+    if rank == 0 and world == 1 and args.workload == "cfg1" and not args.no_side_configs:
+        run.close()
+        torch.cuda.empty_cache()
+        line["configs"] = {w: side_config(w, args, local_rank, peaks, peak_kind, traffic_table) for w in ("cfg0", "cfg2")}
+    if rank == 0 and not args.no_cpu_baseline:
+        cpu_tps, cpu_steps_done, cores = cpu_steps(run.W if not ep else synth.make_weights(synth.MoeShape(n_experts=32), 0),
+                                                   batches if not ep else make_batches(64, synth.make_weights(synth.MoeShape(n_experts=32), 0), False, 2)[0],
+                                                   lb, seconds_budget=12.0 if not ep else 6.0, max_tokens_per_step=min(T, 64))
         line["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                "sample": f"{cpu_steps_done} steps of {min(T, 64)} tokens of the same batches "
-                                          "(CPU oracle, OpenMP, fp64 accumulate)"}
+                                "sample": f"{cpu_steps_done} steps of {min(T, 64)} tokens "
+                                          + ("of the same batches" if not ep else "of the 32-expert layer (the 128-expert weights of "
+                                             "all ranks are not on one host; per-token work is the same)")
+                                          + " (CPU oracle, OpenMP, fp64 accumulate)"}
     if rank == 0:
         emit(line)
-    layer.close()
+    try:
+        run.close()
+    except Exception:
+        pass
     if world > 1:
         dist.destroy_process_group()
 

@@ -112,7 +112,9 @@ int neon_moe_forward_host(neon_moe_handle* h, const void* hidden_bf16, int T, co
  * [T,H] out; the same optional logit_bias for all), pipelined: the upload of batch i+1 and the
  * download of batch i-1 overlap the layer pass of batch i on separate copy streams with two
  * staging sets, so with pinned host buffers the run proceeds at the device's pace.  Returns when
- * every result is in host memory.  Results equal n_batches calls of neon_moe_forward_host. */
+ * every result is in host memory.  Results equal n_batches calls of neon_moe_forward_host.
+ * On an expert-parallel handle (after neon_moe_ep_init) every batch runs as neon_moe_forward_ep:
+ * the call is then collective - every rank calls it with the same n_batches. */
 int neon_moe_forward_host_batches(neon_moe_handle* h, const void* const* hidden_bf16, int n_batches, int T,
                                   const float* logit_bias, float* const* out_f32);
 

@@ -18,6 +18,8 @@ SOURCES = ["neon_moe.cu", "neon_decoder.cu", "neon_water.cu", "neon_svgf.cu"]
 SOURCE_FLAGS = {"neon_water.cu": ["-fmad=false"], "neon_svgf.cu": ["-fmad=false"]}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-cudart", "static"]
+if os.environ.get("NEON_MOE_INSTRUMENT"):   # measurement aids (clock stamps, debug options); never in the shipped library
+    NVCC_FLAGS.append("-DNEON_MOE_INSTRUMENT")
 
 
 def _newest_source() -> float:

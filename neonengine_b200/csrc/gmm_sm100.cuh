@@ -593,6 +593,60 @@ __global__ void __launch_bounds__(256) split_rows_fp4_kernel(const void* __restr
     }
 }
 
+// MXFP4 quantisation of activation rows for tcgen05.mma.kind::mxf4 at prefill (both operands 4-bit):
+// per block of 32 along K the E8M0 scale is 2^(floor(log2 amax) - 2), so amax lands in [4, 8) and
+// clips to 6; every value is rounded to the nearest e2m1 magnitude, ties to the even code.  One warp
+// per (sorted row p, 128-wide chunk), lane l owns 4 elements.  Block per (token tile, chunk):
+// [512 B scale atom: byte (n % 32) * 16 + (n / 32) * 4 + kb for tile row n, k-block kb]
+// [16 row groups x 512 B: rows of 64 bytes (128 codes, low nibble = even column) in the
+// 64-byte-swizzled K-major layout, 16-byte unit u of row n at u ^ ((n >> 1) & 3)].
+constexpr int kQuant4BlockBytes = 512 + 128 * 64;
+
+template <bool FROM_BF16>
+__global__ void __launch_bounds__(256) quant_rows_mxfp4_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm,
+                                                               int top_k, int K, int n_rows, const int32_t* __restrict__ row_tile,
+                                                               const int32_t* __restrict__ tile_row0, uint8_t* __restrict__ act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows * n_chunks) return;
+    const int p = warp / n_chunks, c = warp - p * n_chunks;
+    const int src_row = FROM_BF16 ? perm[p] / top_k : p;
+    const int k0 = c * kChunkK + 4 * lane;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k0 < K) {
+        if (FROM_BF16) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(src) + (size_t)src_row * K + k0);
+            v[0] = __uint_as_float(raw.x << 16);
+            v[1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[2] = __uint_as_float(raw.y << 16);
+            v[3] = __uint_as_float(raw.y & 0xffff0000u);
+        } else {
+            const float4 raw = *reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)src_row * K + k0);
+            v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+        }
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+    const int sb = amax > 0.f ? min(max(ef - 2, 1), 254) : 127;       // E8M0 byte of the block scale
+    const float inv = __uint_as_float((uint32_t)(254 - sb) << 23);     // 1 / scale, exact
+    const __nv_fp4x2_storage_t lo = __nv_cvt_float2_to_fp4x2(make_float2(v[0] * inv, v[1] * inv), __NV_E2M1, cudaRoundNearest);
+    const __nv_fp4x2_storage_t hi = __nv_cvt_float2_to_fp4x2(make_float2(v[2] * inv, v[3] * inv), __NV_E2M1, cudaRoundNearest);
+    const int tile = row_tile[p], n = p - tile_row0[tile];
+    uint8_t* blk = act + ((size_t)tile * n_chunks + c) * kQuant4BlockBytes;
+    *reinterpret_cast<uint16_t*>(blk + 512 + (size_t)(n >> 3) * 512 + (n & 7) * 64 + (((lane >> 3) ^ ((n >> 1) & 3)) << 4) +
+                                 ((lane & 7) << 1)) = (uint16_t)((uint32_t)lo | ((uint32_t)hi << 8));
+    uint32_t w = (uint32_t)sb;
+    w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 8) << 8;
+    w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 16) << 16;
+    w |= __shfl_sync(0xffffffffu, (uint32_t)sb, 24) << 24;
+    if (lane == 0) *reinterpret_cast<uint32_t*>(blk + (n & 31) * 16 + (n >> 5) * 4) = w;
+}
+
 // ---------------------------------------------------------------------------------------
 // The GEMM.  Persistent CTAs walk items = (token tile, 128-row weight tile), item index =
 // blockIdx.x + i*gridDim.x, weight tile fastest so that concurrent CTAs share a token tile's
@@ -635,11 +689,13 @@ struct GmmParams {
 };
 
 // MX4: packed 4-bit operands (kind::mxf4): a weight box is 8 KB in shared memory, rows are 64 B.
+// Stacked: the activations are TERMS e2m1 terms with unit block scales (decode).  Not stacked
+// (TERMS == 1): the activations are MXFP4-quantised, one scale atom + 64-byte rows per block.
 template <int BN_MAX, int TERMS, bool STACK, int KC, bool MX4 = false>
 struct GmmSmem {
-    static_assert(!MX4 || STACK, "packed 4-bit operands are a stacked-mode feature");
+    static_assert(!MX4 || STACK || TERMS == 1, "quantised 4-bit activations are a single term");
     static constexpr int kABytes = MX4 ? 8192 : 16384;  // one 128 x 128 weight box in shared memory
-    static constexpr int kActBytes = MX4 ? TERMS * BN_MAX * 64
+    static constexpr int kActBytes = MX4 ? (STACK ? TERMS * BN_MAX * 64 : 512 + BN_MAX * 64)
                                          : (STACK ? TERMS * BN_MAX * 128 : act_header_bytes(TERMS) + (BN_MAX / 8) * TERMS * 1024);
     static constexpr int kStage = (KC * (kABytes + kActBytes + 512) + 1023) / 1024 * 1024;
     static constexpr int kSfCols = KC * (STACK ? 4 : 4 * (1 + TERMS));  // TMEM columns of scales per stage
@@ -736,8 +792,9 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 next_e = p.tile_expert[nt];
                 next_rows = p.tile_rows[nt];
             }
-            const uint32_t act_bytes = MX4 ? TERMS * ((rows + 7) >> 3) * 512 : STACK ? TERMS * ((rows + 7) >> 3) * 1024
-                                             : act_header_bytes(TERMS) + ((rows + 7) >> 3) * TERMS * 1024;
+            const uint32_t act_bytes = MX4 ? (STACK ? TERMS * ((rows + 7) >> 3) * 512 : 512 + ((rows + 7) >> 3) * 512)
+                                           : STACK ? TERMS * ((rows + 7) >> 3) * 1024
+                                                   : act_header_bytes(TERMS) + ((rows + 7) >> 3) * TERMS * 1024;
             const uint32_t box = (uint32_t)((e * p.m_tiles + m) * p.n_chunks);
             int box_row = (int)(box * 128);
             const uint8_t* sfa_src = p.sfa + (size_t)box * 512;
@@ -836,6 +893,17 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         const uint32_t sf_tmem = sf_stage + k * (SF_COLS / KC);
                         const uint32_t act_smem = st + ACT_OFF + k * L::kActBytes;
                         tc_copy_sf(sf_tmem, make_sf_desc(st + SFA_OFF + k * 512));
+                        if (MX4 && !STACK) {
+                            // packed e2m1 x e2m1 with the activations' own block scales: K = 64 per instruction,
+                            // two scales per row and instruction for both operands (scale ids 0 and 2)
+                            tc_copy_sf(sf_tmem + 4, make_sf_desc(act_smem));
+                            const uint64_t a4 = make_sw64_desc(st + k * L::kABytes), b4 = make_sw64_desc(act_smem + 512);
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+                                mma_mxf4(d_tmem, a4 + 2 * j, b4 + 2 * j, idesc0 + j * ((2u << 29) | (2u << 4)), sf_tmem, sf_tmem + 4,
+                                         first | (uint32_t)(k | j));
+                            return;
+                        }
                         if (MX4) {
                             // packed e2m1 x e2m1, K = 64 per instruction, two weight scales each
                             // (scale ids 0 and 2); activation scales are the unit atom

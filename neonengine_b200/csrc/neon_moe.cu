@@ -16,6 +16,7 @@
 #include "moe_kernels.cuh"
 #include "gmm_sm100.cuh"
 #include "ep.cuh"
+#include "decode_fused.cuh"
 #include "mma_rate.cuh"
 
 using namespace neon;
@@ -73,6 +74,15 @@ struct neon_moe_handle {
     int tile_cap = 0, kp_h = 0, kp_i = 0;
     CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
     CUtensorMap tm4_gu{}, tm4_dn{}, tm4_gu2{}, tm4_dn2{};  // the same boxes left packed (4-bit in shared memory)
+    // one-launch decode pass (T <= 8): router partial sums, partial sums of both products, counters
+    int decode_fused = 1;         // 1 = passes of at most decode_max_tokens tokens run as one cooperative kernel
+    int decode_max_tokens = 0;    // largest pass the one-launch kernel serves on this handle (0 = not available)
+    int decode_stall_test = 0;    // test hook: the kernel's first wait expects one arrival too many and must time out
+    long long decode_wait_limit = kWaitLimitCycles;
+    float *dec_router_part = nullptr, *dec_gu_part = nullptr, *dec_dn_part = nullptr;
+    unsigned* dec_counters = nullptr;
+    int dec_gu_items_cap = 0, dec_counter_words = 0;
+    int mxf4_prefill = 0;         // 128-token tiles: 1 = activations quantised to MXFP4, tcgen05.mma.kind::mxf4 (outside the accuracy contract)
     int mx4 = 0;                  // decode tiles: 1 = kind::mxf4 with e2m1 activation terms, 0 = kind::mxf8f6f4 with e4m3 terms
     // expert parallelism: source-side routing/dispatch over all experts, exchange buffers
     ncclComm_t comm = nullptr;
@@ -173,7 +183,8 @@ void free_all(neon_moe_handle* h) {
                     h->status, h->st_hidden, h->st_out, h->st_bias, h->st_hidden2, h->st_out2, h->gu_wt, h->gu_sfa, h->dn_wt, h->dn_sfa,
                     h->x_act, h->a_act, h->x_scale, h->x_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
                     h->n_tiles, h->row_tile, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
-                    h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv};
+                    h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv,
+                    h->dec_router_part, h->dec_gu_part, h->dec_dn_part, h->dec_counters};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (h->host_pinned) cudaFreeHost(h->host_pinned);
@@ -384,6 +395,8 @@ int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, cons
     }
     if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
     if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
+    if (h->mxf4_prefill)  // MXFP4-quantised activations, both operands packed 4-bit, two chunks per stage
+        return launch_gmm_one<128, 1, GATE_UP, false, 2, true>(h, GATE_UP ? h->tm4_gu : h->tm4_dn, GATE_UP ? h->tm4_gu2 : h->tm4_dn2, p, st);
     return launch_gmm_one<128, TERMS, GATE_UP, false, 1>(h, tm1, tm2, p, st);
 }
 
@@ -391,7 +404,10 @@ template <int TERMS, bool FROM_BF16>
 void launch_split(neon_moe_handle* h, int tile_tokens, const TileList& tl, const void* src, int K, int n, int top_k,
                   const float* amax, float amax_const, uint8_t* act, float* row_scale, cudaStream_t st) {
     const int n_chunks = round_up_int(K, kChunkK) / kChunkK;
-    if (tile_tokens <= 32 && h->mx4)
+    if (tile_tokens > 32 && h->mxf4_prefill)
+        launch_k(h->pdl != 0, quant_rows_mxfp4_kernel<FROM_BF16>, dim3((n * n_chunks + 7) / 8), dim3(256), 0, st, src, h->perm, top_k, K, n,
+                 tl.row_tile, tl.row0, act);
+    else if (tile_tokens <= 32 && h->mx4)
         launch_k(h->pdl != 0, split_rows_fp4_kernel<kMx4Terms, FROM_BF16>, dim3((n * n_chunks + 7) / 8), dim3(256), 0, st, src,
                  h->perm, top_k, K, n, tl.row_tile, tl.row0, tl.rows, tile_tokens, amax, amax_const, act, row_scale);
     else if (tile_tokens <= 32)
@@ -538,6 +554,25 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         (rc = dev_alloc(h, &h->tile_row0, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile_rows, (size_t)h->tile_cap)) ||
         (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
         return bail(rc);
+    // one-launch decode pass: needs sm_100, one GPU holding all experts, at most 32 (token, slot) entries
+    if (h->path == 2 && cfg->ep_size == 1 && cfg->n_experts <= h->n_sms && cfg->top_k <= kDecMaxEntries &&
+        h->kp_h / kChunkK <= kDecCacheChunks && h->kp_i / kChunkK <= kDecCacheChunks) {
+        const int t_dec = std::min({cfg->max_tokens, kDecMaxTok, kDecMaxEntries / cfg->top_k});
+        const int exp_max = std::min(cfg->n_experts, t_dec * cfg->top_k);
+        const int gu_tiles = 2 * cfg->inter / 128, dn_tiles = (cfg->hidden + 127) / 128;
+        h->dec_gu_items_cap = exp_max * gu_tiles;
+        h->dec_counter_words = 4 + h->dec_gu_items_cap + dn_tiles;
+        if ((rc = dev_alloc(h, &h->dec_router_part, (size_t)kDecMaxTok * cfg->n_experts * kDecMaxSlices)) ||
+            (rc = dev_alloc(h, &h->dec_gu_part, (size_t)h->dec_gu_items_cap * kDecParts * 1024)) ||
+            (rc = dev_alloc(h, &h->dec_dn_part, (size_t)exp_max * dn_tiles * kDecParts * 1024)) ||
+            (rc = dev_alloc(h, &h->dec_counters, (size_t)h->dec_counter_words)))
+            return bail(rc);
+        if (cudaMemset(h->dec_counters, 0, (size_t)h->dec_counter_words * 4) != cudaSuccess)
+            return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
+        int coop = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, cfg->device);
+        h->decode_max_tokens = coop ? t_dec : 0;
+    }
     if (cfg->ep_size > 1) {
         const size_t ns = (size_t)h->n_src, E = (size_t)cfg->n_experts, Hh = (size_t)cfg->hidden;
         if ((rc = dev_alloc(h, &h->s_idx, ns)) || (rc = dev_alloc(h, &h->s_w, ns)) || (rc = dev_alloc(h, &h->s_count, E)) ||
@@ -707,6 +742,52 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
     return NEON_MOE_OK;
 }
 
+// Shared memory of decode_fused_kernel: the stage ring, barriers, routing tables and logits (+ alignment slack).
+constexpr int kDecodeSmemBytes = 227 * 1024;  // everything an SM has: what the token-operand tiles leave goes to weight stages
+
+// The whole pass as one cooperative launch (decode_fused.cuh).  The caller has checked T.
+static int launch_decode_fused(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out, cudaStream_t st) {
+    static bool configured[kMaxDevicesAttr] = {};
+    if (!configured[h->cfg.device]) {
+        CU(h, cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmemBytes));
+        configured[h->cfg.device] = true;
+    }
+    const int H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts;
+    DecodeParams p{};
+    p.x = static_cast<const uint16_t*>(hidden); p.wr = h->router_w; p.br = h->router_b; p.logit_bias = logit_bias;
+    p.T = T; p.H = H; p.I = I; p.E = E; p.k = h->cfg.top_k;
+    p.limit = h->cfg.swiglu_limit; p.alpha = h->cfg.swiglu_alpha;
+    p.gu_sfa = h->gu_sfa; p.dn_sfa = h->dn_sfa; p.gu_bias = h->gu_bias; p.dn_bias = h->dn_bias;
+    p.gu_m_tiles = 2 * I / 128; p.dn_m_tiles = (H + 127) / 128; p.nch_h = h->kp_h / kChunkK; p.nch_i = h->kp_i / kChunkK;
+    const int grid = h->n_sms;
+    p.n_slices = std::max(1, std::min(kDecMaxSlices, grid / E));
+    p.rows_dn = T <= 4 ? 4 : 8;
+    p.stages = dec_stages(p.rows_dn, kDecodeSmemBytes);
+    p.a_tx_bytes = h->a_tx_bytes;
+    p.router_part = h->dec_router_part; p.gu_part = h->dec_gu_part; p.dn_part = h->dec_dn_part;
+    p.counters = h->dec_counters; p.gu_items_cap = h->dec_gu_items_cap;
+    p.router_expected_extra = h->decode_stall_test ? 1u : 0u;
+    p.wait_limit = h->decode_wait_limit;
+    p.status = h->status; p.out = out; p.idx = h->idx; p.route_w = h->route_w;
+    p.d = DispatchArrays{h->count, h->offset, h->perm, h->inv};
+#ifdef NEON_MOE_INSTRUMENT
+    p.trace = h->trace;
+#endif
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = kDecodeSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident at once: they wait on one another's counters
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CU(h, cudaLaunchKernelEx(&cfg, decode_fused_kernel, h->tm_gu, h->tm_dn, p));
+    h->launches++;
+    return NEON_MOE_OK;
+}
+
 static void launch_router(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, int32_t* idx, float* w,
                           float* tok_amax, cudaStream_t st) {
     const int H = h->cfg.hidden, E = h->cfg.n_experts, k = h->cfg.top_k;
@@ -812,6 +893,15 @@ static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const fl
     CU(h, cudaSetDevice(h->cfg.device));
     const int k = h->cfg.top_k, n = T * k;
     const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
+    if (h->path == 2 && h->decode_fused && T <= h->decode_max_tokens && !prof && h->tile_override == 0 && !h->mx4 && !h->fuse_dispatch) {
+        int rc = launch_decode_fused(h, hidden, T, logit_bias, out, st);
+        if (rc) return rc;
+        if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
+        if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
+        h->last_stream = st;
+        h->last_n = n;
+        return NEON_MOE_OK;
+    }
     mark(h, st, prof);
     // decode passes on the main path: the last router CTA also runs the dispatch
     const bool fused = h->path == 2 && h->fuse_dispatch && T <= 64 && n <= 1024 && h->n_local == h->cfg.n_experts;
@@ -1078,7 +1168,8 @@ int neon_moe_forward_host_batches(neon_moe_handle* h, const void* const* hidden,
         CU(h, cudaEventRecord(h->ev_in[b], h->s_in));
         CU(h, cudaStreamWaitEvent(sc, h->ev_in[b], 0));
         if (i >= 2) CU(h, cudaStreamWaitEvent(sc, h->ev_out[b], 0));  // batch i-2's result has left the output buffer
-        int rc = neon_moe_forward(h, in_buf[b], T, logit_bias ? h->st_bias : nullptr, out_buf[b], nullptr, nullptr, sc);
+        int rc = h->cfg.ep_size > 1 ? neon_moe_forward_ep(h, in_buf[b], T, logit_bias ? h->st_bias : nullptr, out_buf[b], nullptr, nullptr, sc)
+                                    : neon_moe_forward(h, in_buf[b], T, logit_bias ? h->st_bias : nullptr, out_buf[b], nullptr, nullptr, sc);
         if (rc) return rc;
         CU(h, cudaEventRecord(h->ev_comp[b], sc));
         CU(h, cudaStreamWaitEvent(h->s_out, h->ev_comp[b], 0));
@@ -1155,6 +1246,15 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     } else if (!strcmp(name, "graph_max_tokens")) {
         h->graph_max_tokens = (int)value;
         drop_graphs(h);
+    } else if (!strcmp(name, "decode_fused")) {
+        h->decode_fused = (int)value;
+    } else if (!strcmp(name, "decode_stall_test")) {
+        h->decode_stall_test = (int)value;
+    } else if (!strcmp(name, "decode_wait_limit")) {
+        if (value < 1000) return fail(h, NEON_MOE_EINVAL, "decode_wait_limit is in SM clocks, at least 1000");
+        h->decode_wait_limit = (long long)value;
+    } else if (!strcmp(name, "mxf4_prefill")) {
+        h->mxf4_prefill = (int)value;
     } else if (!strcmp(name, "mx4")) {
         h->mx4 = (int)value;
     } else if (!strcmp(name, "use_graphs")) {
@@ -1342,6 +1442,8 @@ int neon_moe_status(neon_moe_handle* h, int* word) {
     CU(h, cudaStreamSynchronize(h->last_stream));
     CU(h, cudaMemcpy(word, h->status, sizeof(int), cudaMemcpyDeviceToHost));
     CU(h, cudaMemset(h->status, 0, sizeof(int)));
+    // a pass that gave up on a wait leaves the one-launch kernel's counters mid-way: start them afresh
+    if (*word && h->dec_counters) CU(h, cudaMemset(h->dec_counters, 0, (size_t)h->dec_counter_words * 4));
     return *word ? NEON_MOE_EDEVICE : NEON_MOE_OK;
 }
 

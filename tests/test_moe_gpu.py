@@ -327,6 +327,7 @@ def test_fused_router_dispatch_equals_separate_kernels(full20b):
     dispatch arrays and outputs (bit for bit) as the separate dispatch kernel."""
     shape, W, layer = full20b
     lb = synth.zipf_logit_bias(shape.n_experts)
+    layer.set_option("decode_fused", 0)     # both arms on the multi-kernel path (the one-launch decode pass has no dispatch kernel)
     try:
         for T, seed in ((64, 41), (8, 42), (1, 43), (17, 44)):
             hidden = synth.make_hidden(T, W, seed, logit_bias=lb)
@@ -341,6 +342,7 @@ def test_fused_router_dispatch_equals_separate_kernels(full20b):
                 np.testing.assert_array_equal(a, b)
     finally:
         layer.set_option("fuse_dispatch", 0)
+        layer.set_option("decode_fused", 1)
 
 
 def test_pipelined_host_batches_equal_blocking_calls(full20b):
@@ -372,3 +374,84 @@ def test_mma_rate_measurement():
     import ctypes
     ms, cyc = ctypes.c_double(), ctypes.c_int64()
     assert lib.neon_moe_mma_rate(0, 0, 100, 16, ctypes.byref(ms), ctypes.byref(cyc)) == 1   # n not a multiple of 16
+
+
+@pytest.mark.parametrize("T", [1, 2, 4, 7, 8])
+def test_one_launch_decode_pass(full20b, T):
+    """Passes of at most 8 tokens run as ONE cooperative kernel (router, both expert products,
+    SwiGLU and combine; no dispatch pass).  Routing and the dispatch arrays it reports are
+    bit-exact against the oracle, outputs within the contract; it launches exactly one kernel;
+    two runs give the same bits; and the multi-kernel path agrees within the contract."""
+    shape, W, layer = full20b
+    lb = synth.zipf_logit_bias(shape.n_experts) if T in (4, 8) else None
+    hidden = synth.make_hidden(T, W, 70 + T, logit_bias=lb)
+    layer.set_option("use_graphs", 0)
+    try:
+        before = layer.launch_count
+        out, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, what=f"one-launch T={T}")
+        assert layer.launch_count - before == 1
+        again = run_device(layer, hidden, lb)[0]
+        np.testing.assert_array_equal(again, out)
+        layer.set_option("decode_fused", 0)
+        before = layer.launch_count
+        multi = run_device(layer, hidden, lb)[0]
+        assert layer.launch_count - before > 1
+        assert_close(out, multi, f"one-launch vs multi-kernel T={T}")
+    finally:
+        layer.set_option("decode_fused", 1)
+        layer.set_option("use_graphs", 1)
+
+
+def test_one_launch_decode_bounded_wait_reports_and_recovers(full20b):
+    """Failure detection without a GPU fault: a test hook makes the kernel's first wait expect one
+    arrival more than the grid can deliver.  Every CTA gives up after the (shortened) limit, the
+    pass returns, the status word names the wait, and the next pass is correct again."""
+    shape, W, layer = full20b
+    hidden = synth.make_hidden(2, W, 90)
+    layer.set_option("use_graphs", 0)
+    try:
+        layer.set_option("decode_wait_limit", 100_000_000)   # ~50 ms of SM clocks
+        layer.set_option("decode_stall_test", 1)
+        run_device(layer, hidden)
+        assert layer.status() == 7                            # code of the router-completion wait
+        layer.set_option("decode_stall_test", 0)
+        layer.set_option("decode_wait_limit", 400_000_000)
+        check_against_oracle(layer, W, hidden, what="after a timed-out pass")
+    finally:
+        layer.set_option("decode_stall_test", 0)
+        layer.set_option("use_graphs", 1)
+
+
+def test_mxf4_prefill_against_the_quantisation_aware_oracle(full20b, capsys):
+    """Option mxf4_prefill: 128-token tiles on tcgen05.mma.kind::mxf4 with the activations quantised to
+    MXFP4 (blocks of 32, E8M0 scale 2^(floor(log2 amax) - 2), nearest e2m1, ties to even) - the rule
+    of the oracle's quant_act mode.  Routing stays exact.  Against the quantisation-aware oracle the
+    outputs agree to accumulation noise except where a SwiGLU value sits within float rounding of
+    a quantisation boundary and the two sides round it to different codes (one code step of one
+    activation moves an output by up to ~0.5): so the mean relative error must meet the contract,
+    and at most 1 output in 1000 may miss the absolute bound.  Against the plain oracle this path
+    is, by construction, far outside the contract (4-bit activations): that error is printed."""
+    shape, W, _ = full20b
+    T = 1024
+    layer = make_layer(shape, W, max_tokens=T)
+    layer.set_option("mxf4_prefill", 1)
+    hidden = synth.make_hidden(T, W, 8)
+    out, idx, w = run_device(layer, hidden)
+    ridx, rw = oracle.route(hidden, W.router_w, W.router_b, shape.top_k)
+    np.testing.assert_array_equal(idx, ridx)
+    toks = np.arange(7, T, 97, dtype=np.int32)
+    ref_q = oracle.experts(hidden, ridx, rw, W, tokens=toks, quant_act=True)
+    ref = oracle.experts(hidden, ridx, rw, W, tokens=toks)
+    got = out[toks].astype(np.float64)
+    err_q = np.abs(got - ref_q)
+    mean_rel_q = err_q.mean() / np.abs(ref_q).mean()
+    frac_over = (err_q > 2e-2).mean()
+    mean_rel_plain = np.abs(got - ref).mean() / np.abs(ref).mean()
+    with capsys.disabled():
+        print(f"\n[mxf4 prefill] vs quantisation-aware oracle: mean_rel {mean_rel_q:.3e}, max_abs {err_q.max():.3e}, "
+              f"outputs over 2e-2: {frac_over:.2e}; vs plain oracle: mean_rel {mean_rel_plain:.3e}, "
+              f"max_abs {np.abs(got - ref).max():.3e}")
+    assert layer.status() == 0
+    assert mean_rel_q <= 5e-3 and frac_over <= 1e-3, (mean_rel_q, frac_over)
+    assert mean_rel_plain > 5e-3          # 4-bit activations cannot meet the contract against the unquantised result
+    layer.close()

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the gpt-oss-shaped MoE layer (tokens/s) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2|cfg3|cfg4|water|svgf] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0|cfg1|cfg2|cfg3|cfg4|water|svgf|pt] [--impl reference]
 
 A step is one pass of the MoE layer over one batch of seeded synthetic hidden states.
 Default workload at one GPU is the batched-decode configuration (T=64 tokens, Zipf-skewed
@@ -57,6 +57,8 @@ WORKLOADS = {
                            "50 pressure Jacobi iterations, dt 1/500"),
     "svgf": (0, 0, False, "NeonEngine denoiser: temporal accumulation + 3 a-trous passes of one 1920x1080 frame "
                           "(rgba32f G-buffer, rgba16f history, rgba8 image), seeded synthetic scene"),
+    "pt": (0, 0, False, "NeonEngine path tracer: Cornell box with 50 sphere lights (11248 triangles), 800x600, one sample per "
+                        "pixel, at most 3 bounces with next-event estimation (raygen.rgen + closesthit.rchit + miss shaders)"),
     "cfg4": (8192, 128, False, "gpt-oss-120b-shaped MoE layer, 128 experts, T=8192 tokens per GPU, uniform routing, "
                                "experts sharded over the GPUs (expert parallel) when more than one"),
 }
@@ -486,6 +488,120 @@ def run_svgf(args, local_rank):
         dist.destroy_process_group()
 
 
+PT_W, PT_H = 800, 600
+
+
+def pt_cpu_frames(n_frames):
+    """Times n_frames of the path tracer on one host core: the reference shaders compiled for the CPU when
+    that library is present, else the restatement.  Returns (Mrays/s, kind, description)."""
+    from neonengine_b200 import pt_synth
+    from oracle import pt
+    sc = pt_synth.cornell_box(0)
+    ip, iv = pt_synth.camera(PT_W, PT_H)
+    if pt.have_ref():
+        kind, fn, what = "reference", pt.ref_render, "raygen.rgen + closesthit.rchit + miss shaders compiled for the CPU"
+    else:
+        kind, fn, what = "port", pt.render, "C restatement of the four shaders"
+    rays, t0 = 0, time.perf_counter()
+    for i in range(n_frames):
+        rays += fn(sc, ip, iv, float(i), PT_W, PT_H)[1]
+    dt = time.perf_counter() - t0
+    return rays / dt / 1e6, kind, f"{n_frames} frames of the same scene and camera ({what}, own CPU hierarchy, 1 thread, {dt:.1f} s)"
+
+
+def run_pt_reference(args):
+    n = max(1, min(args.steps, 3))
+    mr, kind, desc = pt_cpu_frames(n)
+    line = {"impl": "reference", "metric": "path_tracer_mrays_per_s", "value": mr, "unit": "Mrays/s", "n_gpus": args.gpus,
+            "steps": n, "warmup": 0, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": "pt", "description": WORKLOADS["pt"][3]},
+            "cpu_baseline": {"value": mr, "unit": "Mrays/s", "cores": 1, "kind": kind, "sample": desc},
+            "e2e": {"value": mr, "unit": "Mrays/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    emit(line)
+
+
+def run_pt(args, local_rank):
+    """Frames are independent: N independent replicas under torchrun (one view per GPU)."""
+    import torch
+    import torch.distributed as dist
+    from neonengine_b200 import pt_synth
+    from neonengine_b200.path_tracer import PathTracer
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    sc = pt_synth.cornell_box(0)
+    ip, iv = pt_synth.camera(PT_W, PT_H)
+    tr = PathTracer(sc, PT_W, PT_H, device=local_rank)
+    img = torch.empty((PT_H, PT_W, 4), dtype=torch.uint8, device=f"cuda:{local_rank}")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    st = torch.cuda.current_stream()
+    warm = max(args.warmup, 3)
+    for i in range(warm):
+        tr.render(ip, iv, float(i), image=img, stream=st)
+    barrier()
+    tr.rays()
+    l0 = tr.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for i in range(args.steps):
+            tr.render(ip, iv, float(100 + i), image=img, stream=st)   # a new sample of the scene every frame
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        rays = tr.rays()
+        launches = tr.launch_count() - l0
+        e2e_steps = max(5, min(args.steps, 200))
+        h_img = torch.empty((PT_H, PT_W, 4), dtype=torch.uint8).pin_memory()
+        for i in range(3):
+            tr.render_host_ptr(ip, iv, float(i), h_img.data_ptr())
+        barrier()
+        tr.rays()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            tr.render_host_ptr(ip, iv, float(500 + i), h_img.data_ptr())
+        e2e_s = time.perf_counter() - t0
+        e2e_rays = tr.rays()
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+    peaks, peak_kind = measured_peaks()
+    nodes, depth = tr.bvh_info()
+    # algorithmic bytes of a frame: the rgba8 image out; the scene (0.9 MB of hierarchy, triangles, vertices) stays in L2
+    frame_bytes = PT_W * PT_H * 4
+    achieved = frame_bytes / (ms / args.steps * 1e-3) / 1e9
+    line = {"metric": "path_tracer_mrays_per_s", "value": world * rays / (ms * 1e-3) / 1e6, "unit": "Mrays/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "pt", "description": WORKLOADS["pt"][3], "width": PT_W, "height": PT_H,
+                       "rays_per_frame": rays / max(args.steps, 1), "bvh_nodes": nodes, "bvh_depth": depth,
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (one view per GPU)",
+                       "l2_policy": "the scene (under 1 MB) is L2-resident by the workload's own size; every frame is a new sample "
+                                    "(new frame id), nothing repeats"},
+            "e2e": {"value": world * e2e_rays / e2e_s / 1e6, "unit": "Mrays/s", "h2d_bytes_per_step": 2 * 64 + 4,
+                    "d2h_bytes_per_step": frame_bytes, "steps": e2e_steps, "frames_per_s": world * e2e_steps / e2e_s},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "pt_frame_kernel (one launch per frame)", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "algorithmic_bytes_per_launch": frame_bytes, "ms_per_launch": ms / args.steps,
+                         "note": "latency- and divergence-bound traversal over an L2-resident scene: the HBM roofline does not bind; "
+                                 "Mrays/s is the figure of merit"},
+            "clocks": clocks.summary()}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        mr, kind, desc = pt_cpu_frames(2)
+        line["cpu_baseline"] = {"value": mr, "unit": "Mrays/s", "cores": 1, "kind": kind, "sample": desc}
+    if rank == 0:
+        emit(line)
+    tr.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_decoder_reference(args):
     tps, cores, desc = decoder_cpu_sample()
     line = {"impl": "reference", "metric": "decoder_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
@@ -642,7 +758,7 @@ def main():
     if args.workload is None:
         args.workload = "cfg1" if max(world, args.gpus) == 1 else "cfg4"
     if args.steps is None:
-        args.steps = 200 if args.workload == "cfg3" else 500 if args.workload == "water" else 200 if args.workload == "svgf" else 2000 if WORKLOADS[args.workload][0] <= 64 else 50
+        args.steps = 200 if args.workload == "cfg3" else 500 if args.workload == "water" else 200 if args.workload in ("svgf", "pt") else 2000 if WORKLOADS[args.workload][0] <= 64 else 50
     if args.impl == "reference":
         if args.workload == "cfg3":
             if rank == 0:
@@ -655,6 +771,10 @@ def main():
         if args.workload == "svgf":
             if rank == 0:
                 run_svgf_reference(args)
+            return
+        if args.workload == "pt":
+            if rank == 0:
+                run_pt_reference(args)
             return
         if args.steps > 64:
             args.steps = 8
@@ -680,6 +800,9 @@ def main():
         return
     if args.workload == "svgf":
         run_svgf(args, local_rank)
+        return
+    if args.workload == "pt":
+        run_pt(args, local_rank)
         return
 
     run_moe(args, rank, world, local_rank)

@@ -47,6 +47,24 @@ class NeonSvgfConfig(ctypes.Structure):
     _fields_ = [("width", c_int), ("height", c_int), ("atrous_iterations", c_int), ("device", c_int)]
 
 
+class NeonPtConfig(ctypes.Structure):
+    """Mirror of ``neon_pt_config`` (include/neon_pt.h)."""
+    _fields_ = [("width", c_int), ("height", c_int), ("n_lights", c_int), ("device", c_int)]
+
+
+# name -> (restype, argtypes); must list every symbol include/neon_pt.h declares
+PT_SIGNATURES = {
+    "neon_pt_create": (c_int, [ctypes.POINTER(NeonPtConfig), c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "neon_pt_render": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_float, c_void_p, c_void_p]),
+    "neon_pt_render_host": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_float, c_void_p]),
+    "neon_pt_rays": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint64)]),
+    "neon_pt_bvh_info": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
+    "neon_pt_status": (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    "neon_pt_launch_count": (ctypes.c_int64, [c_void_p]),
+    "neon_pt_last_error": (ctypes.c_char_p, [c_void_p]),
+    "neon_pt_destroy": (c_int, [c_void_p]),
+}
+
 # name -> (restype, argtypes); must list every symbol include/neon_water.h declares
 WATER_SIGNATURES = {
     "neon_water_create": (c_int, [ctypes.POINTER(NeonWaterConfig), c_void_p, c_int, ctypes.POINTER(c_void_p)]),
@@ -137,7 +155,7 @@ def load() -> ctypes.CDLL:
         raise ImportError(f"{SO_PATH} is missing: build it with `python -m neonengine_b200.build` "
                           "(there is no CPU fallback)")
     lib = ctypes.CDLL(SO_PATH)
-    for name, (res, args) in {**SIGNATURES, **DECODER_SIGNATURES, **WATER_SIGNATURES, **SVGF_SIGNATURES}.items():
+    for name, (res, args) in {**SIGNATURES, **DECODER_SIGNATURES, **WATER_SIGNATURES, **SVGF_SIGNATURES, **PT_SIGNATURES}.items():
         fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
         fn.restype = res
         fn.argtypes = args

@@ -13,9 +13,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libneon_moe.so")
 APP = os.path.join(HERE, "moe_app")
-SOURCES = ["neon_moe.cu", "neon_decoder.cu", "neon_water.cu", "neon_svgf.cu"]
+SOURCES = ["neon_moe.cu", "neon_decoder.cu", "neon_water.cu", "neon_svgf.cu", "neon_pt.cu"]
 # the water step reproduces the reference shader's float arithmetic bit for bit: no fused multiply-add there
-SOURCE_FLAGS = {"neon_water.cu": ["-fmad=false"], "neon_svgf.cu": ["-fmad=false"]}
+SOURCE_FLAGS = {"neon_water.cu": ["-fmad=false"], "neon_svgf.cu": ["-fmad=false"], "neon_pt.cu": ["-fmad=false"]}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-cudart", "static"]
 if os.environ.get("NEON_MOE_INSTRUMENT"):   # measurement aids (clock stamps, debug options); never in the shipped library

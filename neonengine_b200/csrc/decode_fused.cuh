@@ -27,9 +27,13 @@
 //              token, the k slots in slot order (parts in order inside a slot): fixed order, no
 //              float atomics.
 //
-// Every wait (mbarrier, counter in global memory) is bounded; on a timeout the CTA records a
-// code in *status, every role leaves its loops and the kernel returns.  The counters are reset
-// by the CTA that exits last, so a pass leaves them ready for the next one.
+// CTAs signal one another through words in global memory tied to the number of the pass (a
+// counter CTA 0 advances at the end of every pass): the router shares are counted by a counter
+// that is never reset (it must reach pass x shares), "part p of item i is written" is a flag
+// equal to the pass number, the arrival counters of the output tiles wrap to zero by themselves.
+// Nothing has to be reset between passes, and the host clears all of it when it reads a
+// non-zero status word.  Every wait (mbarrier, flag) is bounded; on a timeout the CTA records a code in
+// *status, every role leaves its loops and the kernel returns.
 #pragma once
 #include "gmm_sm100.cuh"
 
@@ -38,7 +42,7 @@ namespace neon {
 constexpr int kDecMaxTok = 8;        // tokens per pass (token operand rows per term)
 constexpr int kDecMaxEntries = 32;   // T * top_k
 constexpr int kDecParts = 4;         // partial sums an item can have at most
-constexpr int kDecStagesMax = 10;        // weight stages (16 KB in shared memory = 8 KB of nibbles from HBM, + a 512 B scale atom)
+constexpr int kDecStagesMax = 5;         // weight stages of TWO chunks (32 KB in shared memory = 16 KB of nibbles from HBM, + two 512 B scale atoms)
 constexpr int kDecBuilderThreads = 384;  // 12 builder warps
 constexpr int kDecThreads = 64 + 128 + kDecBuilderThreads;
 constexpr int kDecCacheChunks = 24;      // K chunks of a product at most: one token-operand tile each
@@ -49,7 +53,7 @@ constexpr int kDecMaxSlices = 8;
 // of the shared memory goes to weight stages: the stream from HBM needs ~2 us x 45 GB/s per SM in flight.
 __host__ __device__ constexpr int dec_tile_bytes(int rows_dn) { return rows_dn == 8 ? 4096 : 2048; }
 __host__ __device__ constexpr int dec_stages(int rows_dn, int smem_budget) {
-    int n = (smem_budget - 1024 - kDecTailBytes - kDecCacheChunks * dec_tile_bytes(rows_dn)) / (16384 + 512);
+    int n = (smem_budget - 1024 - kDecTailBytes - kDecCacheChunks * dec_tile_bytes(rows_dn)) / (32768 + 1024);
     return n > kDecStagesMax ? kDecStagesMax : n;
 }
 
@@ -65,12 +69,13 @@ struct DecodeParams {
     int rows_dn;               // token rows per term of the down product's operand tiles: 4 or 8
     int stages;                // weight stages in use
     uint32_t a_tx_bytes;
-    float* router_part;        // [T][E][n_slices]
+    float* router_part;        // [T][E][8 slice slots]; slots >= n_slices are zero
     float* gu_part;            // [item][kDecParts][8 tokens][128 rows]
     float* dn_part;
-    unsigned* counters;        // [0] router done, [1] CTAs exited, [2] padding, [3] test hook; [4 ..] gu_done[items], then dn_done[tiles]
-    int gu_items_cap;          // start of dn_done = 4 + gu_items_cap
-    unsigned router_expected_extra;  // 0; a test sets 1 so that the first wait can never complete
+    unsigned* counters;        // [0] pass number; [1] router shares written since set-up (never reset); [4+256 ..) flags
+                               // [items][4 parts] "part written in pass n"; then dn_done[tiles] (arrival counters that wrap to zero)
+    int gu_items_cap;          // start of dn_done = 4 + 256 + 4 * gu_items_cap
+    unsigned router_expected_extra;  // 0; a test sets 1: the router wait then expects one share more than will ever arrive
     long long wait_limit;      // SM clocks a wait may take
     int* status;
     float* out;                // [T][H]
@@ -115,6 +120,7 @@ __device__ __forceinline__ bool wait_counter(const unsigned* p, unsigned target,
             atomicCAS(status, 0, code);
             return false;
         }
+        __nanosleep(64);
     }
 }
 
@@ -134,10 +140,54 @@ __device__ __forceinline__ bool mbar_wait_quiet(uint64_t* bar, uint32_t parity, 
                 atomicCAS(status, 0, code);
                 break;
             }
-            __nanosleep(sleep_ns);
+            if (sleep_ns) __nanosleep(sleep_ns);
         }
     }
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// Release-ordered increment of a counter another CTA polls with ld.acquire: the writes this thread made
+// (and, through a preceding CTA barrier, the writes of its CTA) are visible to whoever sees the count.
+__device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Arrival counter that wraps to zero at `last`: returns the value before the increment.
+__device__ __forceinline__ unsigned atom_acq_rel_inc(unsigned* p, unsigned last) {
+    unsigned old;
+    asm volatile("atom.acq_rel.gpu.global.inc.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(last) : "memory");
+    return old;
+}
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
+// Bounded wait until the n (<= 4) flags at p all equal `want`.  The polls are relaxed loads, all in
+// flight together (an acquire load would order each poll behind the one before it); one fence after
+// the flags have been seen orders the reads of the data they guard.
+__device__ __forceinline__ bool wait_flags(const unsigned* p, int n, unsigned want, volatile int* abort_flag, int* status, int code,
+                                           long long limit) {
+    const long long t0 = clock64();
+    while (true) {
+        unsigned f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = i < n ? ld_relaxed_u32(p + i) : want;
+        if (f[0] == want && f[1] == want && f[2] == want && f[3] == want) {
+            fence_acq_rel_gpu();
+            return true;
+        }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > limit) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
@@ -251,20 +301,21 @@ __device__ __forceinline__ void dec_topk_warp(const float* lgt, int E, int k, in
 }
 
 __global__ void __launch_bounds__(kDecThreads, 1)
-decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_constant__ CUtensorMap tmDN, const DecodeParams p) {
+decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_constant__ CUtensorMap tmGU2,
+                    const __grid_constant__ CUtensorMap tmDN, const __grid_constant__ CUtensorMap tmDN2, const DecodeParams p) {
     using namespace sm100;
     const int STAGES = p.stages;
     const int RD = p.rows_dn, TILE = dec_tile_bytes(RD);
     constexpr int ACC_COLS = 32;                // TMEM columns of one accumulator buffer (down: 4 terms x 8 tokens)
     constexpr int SF_UNIT = 2 * ACC_COLS;       // two atoms of unit scales for the token operand
-    constexpr int SF_BASE = SF_UNIT + 8;        // weight scale atoms, 4 columns per stage
+    constexpr int SF_BASE = SF_UNIT + 8;        // weight scale atoms, 2 x 4 columns per stage
     constexpr uint32_t TMEM_COLS = 128;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* stages = smem;                                    // weight boxes, 16 KB each
-    uint8_t* cache = stages + STAGES * 16384;                  // token-operand tiles, one per K chunk
-    uint8_t* sfa_ring = cache + kDecCacheChunks * TILE;        // weight scale atoms, 512 B per stage
-    uint8_t* tail = sfa_ring + STAGES * 512;
+    uint8_t* stages = smem;                                    // weight boxes, two chunks = 32 KB per stage
+    uint8_t* cache = stages + STAGES * 32768;                  // token-operand tiles, one per K chunk
+    uint8_t* sfa_ring = cache + kDecCacheChunks * TILE;        // weight scale atoms, 2 x 512 B per stage
+    uint8_t* tail = sfa_ring + STAGES * 1024;
     uint64_t* full = reinterpret_cast<uint64_t*>(tail);
     uint64_t* empty = full + kDecStagesMax;
     uint64_t* acc_full = empty + kDecStagesMax;
@@ -290,10 +341,10 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
     const int cta = blockIdx.x, grid = gridDim.x;
     if (tid == 0) DEC_STAMP(0);
     const int T = p.T, H = p.H, E = p.E, k = p.k, n_ent = T * k;
-    unsigned* const router_done = p.counters;
-    unsigned* const exit_count = p.counters + 1;
-    unsigned* const gu_done = p.counters + 4;
-    unsigned* const dn_done = p.counters + 4 + p.gu_items_cap;
+    const unsigned pass = __ldcg(p.counters) + 1u;   // written by CTA 0 at the end of the previous pass
+    unsigned* const router_count = p.counters + 1;
+    unsigned* const gu_flag = p.counters + 4 + 256;
+    unsigned* const dn_done = p.counters + 4 + 256 + 4 * p.gu_items_cap;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -310,7 +361,9 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
         s_misc[0] = 0;
         fence_barrier_init();
         prefetch_tmap(&tmGU);
+        prefetch_tmap(&tmGU2);
         prefetch_tmap(&tmDN);
+        prefetch_tmap(&tmDN2);
     }
     if (tid < 128) unit_atom[tid] = 0x7f7f7f7fu;
     if (tid < 8) s_amax[tid] = 0u;
@@ -411,26 +464,38 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
             for (int t = 0; t < kDecMaxTok; ++t) {
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
-                if (lane == 0 && t < T) __stcg(p.router_part + ((size_t)t * E + e) * p.n_slices + sl, acc[t]);
+                if (lane == 0 && t < T) __stcg(p.router_part + ((size_t)t * E + e) * kDecMaxSlices + sl, acc[t]);
             }
-            if (lane == 0) {
-                __threadfence();
-                atomicAdd(router_done, 1u);
-            }
+            if (lane == 0) red_release_add(router_count, 1u);
             __syncwarp();
         }
         if (q4 == 0 && lane == 0) DEC_STAMP(2);
         {
-            int ok = 1;
-            if (lane == 0)
-                ok = wait_counter(router_done, (unsigned)(E * p.n_slices) + p.router_expected_extra, abort_flag, p.status, 7, p.wait_limit);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            // the router counter is never reset: after this pass's n_router shares it stands at pass * n_router
+            // (mod 2^32).  One lane per CTA polls it; the other warps wait at the named barrier.
+            if (q4 == 0) {
+                const unsigned target = pass * (unsigned)(E * p.n_slices) + p.router_expected_extra;
+                if (lane == 0) {
+                    const long long t0 = clock64();
+                    while ((int)(ld_acquire_u32(router_count) - target) < 0) {
+                        if (*abort_flag || clock64() - t0 > p.wait_limit) {
+                            *abort_flag = 1;
+                            atomicCAS(p.status, 0, 7);
+                            break;
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            named_bar_sync(1, 128);
+            const int ok = !*abort_flag;
             if (ok) {
                 for (int t = q4; t < T; t += 4) {  // logits, top k, softmax: every CTA, identically
                     for (int e = lane; e < E; e += 32) {
-                        float v = 0.f;
-                        const float* part = p.router_part + ((size_t)t * E + e) * p.n_slices;
-                        for (int sl = 0; sl < p.n_slices; ++sl) v += __ldcg(part + sl);
+                        // all eight slice slots in two loads (slots beyond n_slices stay zero from set-up), added in order
+                        const float4* part = reinterpret_cast<const float4*>(p.router_part + ((size_t)t * E + e) * kDecMaxSlices);
+                        const float4 a = __ldcg(part), b = __ldcg(part + 1);
+                        float v = ((((((a.x + a.y) + a.z) + a.w) + b.x) + b.y) + b.z) + b.w;
                         v += bf16_bits_to_float(p.br[e]);
                         if (p.logit_bias) v += p.logit_bias[e];
                         s_lg[t * E + e] = v;
@@ -491,34 +556,46 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
     if (*abort_flag) {
         // nothing was started: fall through to the exit protocol
     } else if (warp == 0) {
-        // ---- weight producer: one 128 x 128 box (TMA, nibbles expanded to bytes) + its scale atom per chunk
-        int n = 0;
+        // ---- weight producer: per stage two K chunks = one 256 x 128 box (TMA, nibbles expanded to bytes) + their
+        //      scale atoms; the odd last chunk of a run travels alone.  Divisions happen once per run of an item;
+        //      stage, phase and box index are carried incrementally.
+        int s = 0, par = 0;
         for (int phase = 0; phase < 2; ++phase) {
             const DecPhase& ph = phase ? dn : gu;
-            const CUtensorMap* map = phase ? &tmDN : &tmGU;
+            const CUtensorMap* map1 = phase ? &tmDN : &tmGU;
+            const CUtensorMap* map2 = phase ? &tmDN2 : &tmGU2;
             const uint8_t* sfa = phase ? p.dn_sfa : p.gu_sfa;
             const int lo = phase ? dn_lo : gu_lo, hi = phase ? dn_hi : gu_hi;
-            for (int f = lo; f < hi; ++f, ++n) {
-                const int item = f / ph.n_chunks, c = f - item * ph.n_chunks;
+            for (int f = lo; f < hi;) {
+                const int item = f / ph.n_chunks, c0 = f - item * ph.n_chunks;
+                const int c1 = min(ph.n_chunks, c0 + (hi - f));
                 const int es = item / ph.m_tiles, m = item - es * ph.m_tiles;
-                const int s = n % STAGES, par = (n / STAGES) & 1;
-                const int ok = mbar_wait(&empty[s], par ^ 1, abort_flag, p.status, 1, p.wait_limit);
-                if (!__all_sync(0xffffffffu, ok)) goto roles_done;
-                if (lane == 0 && n == 0) DEC_STAMP(10);
-                if (elect_one()) {
-                    const uint32_t box = (uint32_t)((s_exp[es] * ph.m_tiles + m) * ph.n_chunks + c);
-                    mbar_expect_tx(&full[s], p.a_tx_bytes + 512);
-                    tma_load_2d(stages + s * 16384, map, &full[s], 0, (int)(box * 128));
-                    bulk_load(sfa_ring + s * 512, sfa + (size_t)box * 512, 512, &full[s]);
+                uint32_t box = (uint32_t)((s_exp[es] * ph.m_tiles + m) * ph.n_chunks + c0);
+                for (int left = c1 - c0; left > 0; left -= 2, box += 2) {
+                    const int ok = mbar_wait(&empty[s], par ^ 1, abort_flag, p.status, 1, p.wait_limit);
+                    if (!__all_sync(0xffffffffu, ok)) goto roles_done;
+                    if (elect_one()) {
+                        if (left >= 2) {
+                            mbar_expect_tx(&full[s], 2 * (p.a_tx_bytes + 512));
+                            tma_load_2d(stages + s * 32768, map2, &full[s], 0, (int)(box * 128));
+                            bulk_load(sfa_ring + s * 1024, sfa + (size_t)box * 512, 1024, &full[s]);
+                        } else {
+                            mbar_expect_tx(&full[s], p.a_tx_bytes + 512);
+                            tma_load_2d(stages + s * 32768, map1, &full[s], 0, (int)(box * 128));
+                            bulk_load(sfa_ring + s * 1024, sfa + (size_t)box * 512, 512, &full[s]);
+                        }
+                    }
+                    __syncwarp();
+                    if (++s == STAGES) { s = 0; par ^= 1; }
                 }
-                __syncwarp();
+                f += c1 - c0;
             }
         }
         // every stage must have been released before the CTA may retire (late asynchronous arrives)
-        for (int i = 0; i < STAGES; ++i, ++n) {
-            const int s = n % STAGES, par = (n / STAGES) & 1;
+        for (int i = 0; i < STAGES; ++i) {
             const int ok = mbar_wait(&empty[s], par ^ 1, abort_flag, p.status, 6, p.wait_limit);
             if (!__all_sync(0xffffffffu, ok)) goto roles_done;
+            if (++s == STAGES) { s = 0; par ^= 1; }
         }
     } else if (warp == 1) {
         // ---- MMA issuer -------------------------------------------------------------------------------
@@ -528,7 +605,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
         }
         __syncwarp();
         const uint32_t stage_base = smem_u32(stages), cache_base = smem_u32(cache), sfa_base = smem_u32(sfa_ring);
-        int n = 0, seg = 0, frees = 0, fulls = 0, cur_es = -1;
+        int s = 0, par = 0, seg = 0, frees = 0, fulls = 0, cur_es = -1;
         for (int phase = 0; phase < 2; ++phase) {
             const DecPhase& ph = phase ? dn : gu;
             const int lo = phase ? dn_lo : gu_lo, hi = phase ? dn_hi : gu_hi;
@@ -547,6 +624,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
                         }
                         ok = mbar_wait(cache_full, fulls & 1, abort_flag, p.status, 9, p.wait_limit);
                         if (!__all_sync(0xffffffffu, ok)) goto roles_done;
+                        if (lane == 0 && fulls == 0) DEC_STAMP(15);
                         ++fulls;
                         cur_es = es;
                     }
@@ -556,23 +634,31 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
                 if (!__all_sync(0xffffffffu, ok)) goto roles_done;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + b * ACC_COLS;
-                for (int c = c0; c < c1; ++c, ++n) {
-                    const int s = n % STAGES, par = (n / STAGES) & 1;
+                uint32_t b_tile = cache_base + c0 * TILE, first = 0;
+                for (int left = c1 - c0; left > 0; left -= 2) {
                     ok = mbar_wait(&full[s], par, abort_flag, p.status, 3, p.wait_limit);
                     if (!__all_sync(0xffffffffu, ok)) goto roles_done;
-                    if (lane == 0 && (n & 7) == 0 && n < 40) DEC_STAMP(11 + (n >> 3));
+                    if (lane == 0 && !phase && f == lo && first == 0) DEC_STAMP(11);
                     tc_fence_after();
                     if (elect_one()) {
-                        const uint32_t sf_tmem = tmem_base + SF_BASE + s * 4;
-                        tc_copy_sf(sf_tmem, make_sf_desc(sfa_base + s * 512));
-                        const uint64_t a_desc = make_sw128_desc(stage_base + s * 16384), b_desc = make_sw128_desc(cache_base + c * TILE);
+                        const uint32_t st = stage_base + s * 32768, sf_tmem = tmem_base + SF_BASE + s * 8, sf_smem = sfa_base + s * 1024;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * (1u << 29), sf_tmem, tmem_base + SF_UNIT,
-                                         (uint32_t)((c - c0) | j));
+                        for (int kc = 0; kc < 2; ++kc) {
+                            if (kc < left) {
+                                tc_copy_sf(sf_tmem + 4 * kc, make_sf_desc(sf_smem + 512 * kc));
+                                const uint64_t a_desc = make_sw128_desc(st + 16384 * kc), b_desc = make_sw128_desc(b_tile + kc * TILE);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    mma_mxf8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * (1u << 29), sf_tmem + 4 * kc,
+                                                 tmem_base + SF_UNIT, first | (uint32_t)(kc | j));
+                            }
+                        }
                         tc_commit(&empty[s]);
                     }
                     __syncwarp();
+                    first = 1;
+                    b_tile += 2 * TILE;
+                    if (++s == STAGES) { s = 0; par ^= 1; }
                 }
                 if (elect_one()) tc_commit(&acc_full[b]);
                 __syncwarp();
@@ -611,7 +697,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
                 {
                     // the four epilogue warps meet at named barriers below, so they must leave together: each
                     // posts its verdict on the wait, and all of them go on only if all four saw the accumulator
-                    const int ok = (int)mbar_wait_quiet(&acc_full[b], apar, abort_flag, p.status, 4, p.wait_limit, 100);
+                    const int ok = (int)mbar_wait_quiet(&acc_full[b], apar, abort_flag, p.status, 4, p.wait_limit, 0);
                     if (lane == 0) s_vote[q] = ok;
                     named_bar_sync(1, 128);
                     if (!(s_vote[0] & s_vote[1] & s_vote[2] & s_vote[3])) goto roles_done;
@@ -655,17 +741,15 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
                         __stcg(dst + j * 128, v[j] * __uint_as_float((uint32_t)sb << 23));
                     }
                 }
-                __threadfence();
-                named_bar_sync(1, 128);
+                named_bar_sync(1, 128);  // the 128 threads' stores precede the one release below
                 if (!phase) {
-                    if (et == 0) atomicAdd(&gu_done[item], 1u);
+                    if (et == 0) st_release_u32(gu_flag + 4 * item + part, pass);
+                    if (et == 0) DEC_STAMP(10);
                 } else {
                     if (et == 0) {
                         unsigned expected = 0;
                         for (int x = 0; x < n_exp; ++x) expected += (unsigned)dn.parts(x * dn.m_tiles + m);
-                        const unsigned old = atomicAdd(&dn_done[m], 1u);
-                        s_misc[1] = (old + 1 == expected);
-                        __threadfence();
+                        s_misc[1] = (atom_acq_rel_inc(&dn_done[m], expected - 1u) == expected - 1u);
                     }
                     named_bar_sync(1, 128);
                     const bool last = s_misc[1] != 0;
@@ -675,16 +759,26 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
                         const int col = 128 * m + et;
                         if (col < H) {
                             for (int t = 0; t < T; ++t) {
-                                float o = 0.f;
-                                for (int s = 0; s < k; ++s) {
-                                    const int ent = t * k + s, xs = s_ent_es[ent], jj = s_ent_j[ent];
-                                    const int it = xs * dn.m_tiles + m, np = dn.parts(it);
-                                    float y = 0.f;
-                                    for (int pp = 0; pp < np; ++pp)
-                                        y += __ldcg(p.dn_part + ((size_t)it * kDecParts + pp) * 1024 + jj * 128 + et);
-                                    y += bf16_bits_to_float(p.dn_bias[(size_t)s_exp[xs] * H + col]);
-                                    o += s_w[ent] * y;
+                                // the k slots' parts, all loads in flight together (a chain of dependent L2 round trips otherwise)
+                                float y[kMaxTopK][kDecParts], bias[kMaxTopK];
+#pragma unroll
+                                for (int s = 0; s < kMaxTopK; ++s) {
+                                    bias[s] = 0.f;
+#pragma unroll
+                                    for (int pp = 0; pp < kDecParts; ++pp) y[s][pp] = 0.f;
+                                    if (s < k) {
+                                        const int ent = t * k + s, xs = s_ent_es[ent], jj = s_ent_j[ent];
+                                        const int it = xs * dn.m_tiles + m, np = dn.parts(it);
+                                        bias[s] = bf16_bits_to_float(p.dn_bias[(size_t)s_exp[xs] * H + col]);
+#pragma unroll
+                                        for (int pp = 0; pp < kDecParts; ++pp)
+                                            if (pp < np) y[s][pp] = __ldcg(p.dn_part + ((size_t)it * kDecParts + pp) * 1024 + jj * 128 + et);
+                                    }
                                 }
+                                float o = 0.f;
+#pragma unroll
+                                for (int s = 0; s < kMaxTopK; ++s)
+                                    if (s < k) o += s_w[t * k + s] * ((((y[s][0] + y[s][1]) + y[s][2]) + y[s][3]) + bias[s]);
                                 p.out[(size_t)t * H + col] = o;
                             }
                         }
@@ -722,45 +816,62 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
             }
             // the tiles in place are still being read until the MMA warp says otherwise
             if (!mbar_wait_quiet(cache_free, epoch & 1, abort_flag, p.status, 5, p.wait_limit, 400)) goto roles_done;
+            if (bt == 0 && epoch == 0) DEC_STAMP(12);
             const int ntok = s_ntok[es];
-            // real tasks (chunk c, row j < ntok, 16-channel unit u) spread evenly over the builder threads, then zero rows
-            for (int task = bt; task < (c_hi - c_lo) * ntok * 8; task += kDecBuilderThreads) {
-                const int u = task & 7, j = (task >> 3) % ntok, c = c_lo + (task >> 3) / ntok;
+            // real tasks (chunk c, row j < ntok, 4 channels) spread evenly over the builder threads, then zero rows
+            for (int task = bt; task < (c_hi - c_lo) * ntok * 32; task += kDecBuilderThreads) {
+                const int w4 = task & 31, j = (task >> 5) % ntok, c = c_lo + (task >> 5) / ntok;
+                const int u = w4 >> 2;                  // 16-byte unit of the row; this task fills 4 of its bytes per term
                 uint8_t* tile = cache + c * TILE;
-                const int ch0 = 128 * c + 16 * u;       // first of this unit's 16 channels
-                const int gm = ch0 >> 6;                // gate_up tile holding them: rows 32 * (u & 3) .. + 15 gate, + 16 .. + 31 linear
+                const int ch0 = 128 * c + 4 * w4;       // first of this task's 4 channels
+                const int gm = ch0 >> 6;                // gate_up tile holding them: gate row 32 * ((ch % 64) / 16) + ch % 16, linear row 16 further
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
                 if (gm < gu.m_tiles && ch0 < p.I) {
                     const int gitem = es * gu.m_tiles + gm, np = gu.parts(gitem);
-                    if (!wait_counter(&gu_done[gitem], (unsigned)np, abort_flag, p.status, 8, p.wait_limit)) goto roles_done;
-                    const int tok = s_tok[es * 8 + j];
-                    const uint16_t* bias = p.gu_bias + (size_t)s_exp[es] * 2 * p.I + 2 * ch0;
-                    uint4 braw[4];
-#pragma unroll
-                    for (int x = 0; x < 4; ++x) braw[x] = __ldg(reinterpret_cast<const uint4*>(bias) + x);  // 16 (gate, linear) bias pairs
-                    float gl[32];
-#pragma unroll
-                    for (int x = 0; x < 32; ++x) gl[x] = 0.f;
-                    for (int pp = 0; pp < np; ++pp) {
-                        const float4* src = reinterpret_cast<const float4*>(p.gu_part + ((size_t)gitem * kDecParts + pp) * 1024 + tok * 128 + 32 * (u & 3));
-                        float4 r[8];
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) r[x] = __ldcg(src + x);
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) {
-                            gl[4 * x] += r[x].x; gl[4 * x + 1] += r[x].y; gl[4 * x + 2] += r[x].z; gl[4 * x + 3] += r[x].w;
-                        }
+                    const uint4 braw = __ldg(reinterpret_cast<const uint4*>(p.gu_bias + (size_t)s_exp[es] * 2 * p.I + 2 * ch0));  // 4 (gate, linear) pairs
+                    {
+                        // one lane per distinct item polls (the lanes of a warp share one or two items): every poll that
+                        // is not sent leaves room in the memory system for the stores that are being waited for
+                        const unsigned same = __match_any_sync(__activemask(), gitem);
+                        int ok = 1;
+                        if ((__ffs(same) - 1) == lane) ok = wait_flags(gu_flag + 4 * gitem, np, pass, abort_flag, p.status, 8, p.wait_limit);
+                        ok = __shfl_sync(same, ok, __ffs(same) - 1);
+                        if (!ok) goto roles_done;
+                        fence_acq_rel_gpu();
                     }
-                    const uint32_t* bw = reinterpret_cast<const uint32_t*>(braw);
-                    float v[16];
+                    if (bt == 0 && epoch == 0) DEC_STAMP(13);
+                    const int tok = s_tok[es * 8 + j];
+                    const int row_g = 32 * ((ch0 & 63) >> 4) + (ch0 & 15);
+                    float4 gs = make_float4(0.f, 0.f, 0.f, 0.f), ls = gs;
+                    for (int pp = 0; pp < np; ++pp) {
+                        const float* src = p.gu_part + ((size_t)gitem * kDecParts + pp) * 1024 + tok * 128 + row_g;
+                        const float4 g4 = __ldcg(reinterpret_cast<const float4*>(src)), l4 = __ldcg(reinterpret_cast<const float4*>(src + 16));
+                        gs.x += g4.x; gs.y += g4.y; gs.z += g4.z; gs.w += g4.w;
+                        ls.x += l4.x; ls.y += l4.y; ls.z += l4.z; ls.w += l4.w;
+                    }
+                    const float gsum[4] = {gs.x, gs.y, gs.z, gs.w}, lsum[4] = {ls.x, ls.y, ls.z, ls.w};
+                    const uint32_t bw[4] = {braw.x, braw.y, braw.z, braw.w};
 #pragma unroll
-                    for (int x = 0; x < 16; ++x) {
-                        const float gg = fminf(gl[x] + __uint_as_float(bw[x] << 16), p.limit);
-                        const float ll = fminf(fmaxf(gl[16 + x] + __uint_as_float(bw[x] & 0xffff0000u), -p.limit), p.limit);
+                    for (int x = 0; x < 4; ++x) {
+                        const float gg = fminf(gsum[x] + __uint_as_float(bw[x] << 16), p.limit);
+                        const float ll = fminf(fmaxf(lsum[x] + __uint_as_float(bw[x] & 0xffff0000u), -p.limit), p.limit);
                         v[x] = gg / (1.f + expf(-p.alpha * gg)) * (ll + 1.f);
                     }
-                    store_terms16<4>(tile, RD, j, u, v, sb_dn);
-                } else {
-                    store_zero16<4>(tile, RD, j, u);
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {  // four e4m3 terms, 4 bytes each
+                    const float inv = __uint_as_float((uint32_t)(254 - (sb_dn - 4 * t)) << 23);
+                    const float scale = __uint_as_float((uint32_t)(sb_dn - 4 * t) << 23);
+                    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
+                    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+                    const int n = t * RD + j;
+                    *reinterpret_cast<uint32_t*>(tile + (n >> 3) * 1024 + (n & 7) * 128 + ((u ^ (n & 7)) << 4) + ((w4 & 3) << 2)) =
+                        (uint32_t)lo | ((uint32_t)hi << 16);
+                    if (t < 3) {
+                        __half2_raw blo = __nv_cvt_fp8x2_to_halfraw2(lo, __NV_E4M3), bhi = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
+                        const float2 flo = __half22float2(*reinterpret_cast<__half2*>(&blo)), fhi = __half22float2(*reinterpret_cast<__half2*>(&bhi));
+                        v[0] -= flo.x * scale; v[1] -= flo.y * scale; v[2] -= fhi.x * scale; v[3] -= fhi.y * scale;
+                    }
                 }
             }
             for (int task = bt; task < (c_hi - c_lo) * (RD - ntok) * 8; task += kDecBuilderThreads) {
@@ -769,6 +880,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
             }
             fence_proxy_async();
             __syncwarp();
+            if (bt == 0 && epoch == 0) DEC_STAMP(14);
             if (lane == 0) mbar_arrive(cache_full);
             f = f_end;
         }
@@ -786,21 +898,8 @@ roles_done:
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    // the CTA that exits last leaves the counters ready for the next pass
-    if (tid == 0) {
-        __threadfence();
-        const unsigned old = atomicAdd(exit_count, 1u);
-        s_misc[2] = (old == (unsigned)grid - 1u);
-    }
-    __syncthreads();
-    if (s_misc[2]) {
-        for (int i = tid; i < gu.n_items; i += kDecThreads) gu_done[i] = 0u;
-        for (int i = tid; i < p.dn_m_tiles; i += kDecThreads) dn_done[i] = 0u;
-        if (tid == 0) {
-            *router_done = 0u;
-            *exit_count = 0u;
-        }
-    }
+    // the next pass gets the next number (a pass that gave up advances it too: its flags then mean nothing)
+    if (cta == 0 && tid == 0) __stcg(p.counters, pass);
     if (tid == 0) DEC_STAMP(8);
 }
 

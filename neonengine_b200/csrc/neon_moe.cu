@@ -561,13 +561,14 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         const int exp_max = std::min(cfg->n_experts, t_dec * cfg->top_k);
         const int gu_tiles = 2 * cfg->inter / 128, dn_tiles = (cfg->hidden + 127) / 128;
         h->dec_gu_items_cap = exp_max * gu_tiles;
-        h->dec_counter_words = 4 + h->dec_gu_items_cap + dn_tiles;
+        h->dec_counter_words = 4 + 256 + 4 * h->dec_gu_items_cap + dn_tiles;
         if ((rc = dev_alloc(h, &h->dec_router_part, (size_t)kDecMaxTok * cfg->n_experts * kDecMaxSlices)) ||
             (rc = dev_alloc(h, &h->dec_gu_part, (size_t)h->dec_gu_items_cap * kDecParts * 1024)) ||
             (rc = dev_alloc(h, &h->dec_dn_part, (size_t)exp_max * dn_tiles * kDecParts * 1024)) ||
             (rc = dev_alloc(h, &h->dec_counters, (size_t)h->dec_counter_words)))
             return bail(rc);
-        if (cudaMemset(h->dec_counters, 0, (size_t)h->dec_counter_words * 4) != cudaSuccess)
+        if (cudaMemset(h->dec_router_part, 0, (size_t)kDecMaxTok * cfg->n_experts * kDecMaxSlices * 4) != cudaSuccess ||
+            cudaMemset(h->dec_counters, 0, (size_t)h->dec_counter_words * 4) != cudaSuccess)
             return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
         int coop = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, cfg->device);
@@ -783,7 +784,7 @@ static int launch_decode_fused(neon_moe_handle* h, const void* hidden, int T, co
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    CU(h, cudaLaunchKernelEx(&cfg, decode_fused_kernel, h->tm_gu, h->tm_dn, p));
+    CU(h, cudaLaunchKernelEx(&cfg, decode_fused_kernel, h->tm_gu, h->tm_gu2, h->tm_dn, h->tm_dn2, p));
     h->launches++;
     return NEON_MOE_OK;
 }

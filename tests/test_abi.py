@@ -55,6 +55,14 @@ def test_exports_every_declared_svgf_symbol(lib):
     assert set(names) == set(_lib.SVGF_SIGNATURES), "python binding table out of sync with the header"
 
 
+def test_exports_every_declared_path_tracer_symbol(lib):
+    names = declared_symbols("neon_pt.h", "neon_pt_")
+    assert len(names) >= 8
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in neon_pt.h but not exported"
+    assert set(names) == set(_lib.PT_SIGNATURES), "python binding table out of sync with the header"
+
+
 def test_water_create_rejects_bad_config(lib):
     h = ctypes.c_void_p()
     cfg = _lib.NeonWaterConfig(8, 1, 4, 4, 0.1, 1.0, 1.0, 0.0, 1.0, 0.002)  # one cell along x

@@ -744,6 +744,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side-configs", action="store_true",
                     help="default run only: skip the cfg0 and cfg2 blocks measured beside the headline workload")
+    ap.add_argument("--ep-nccl-exchange", action="store_true",
+                    help="multi-GPU runs only: exchange rows with grouped ncclSend/ncclRecv instead of the library's own peer stores")
     ap.add_argument("--no-n1-base", action="store_true",
                     help="multi-GPU runs only: skip rank 0's single-GPU run of the same workload")
     ap.add_argument("--decoder-layers", type=int, default=None,
@@ -983,6 +985,45 @@ class MoeRun:
                 return self.W.slice_experts(lo, hi)
         return parity_sample(hid, self.lb, out.cpu().numpy(), idx.cpu().numpy(), weights, self.shape, sample)
 
+    def mxf4_variant(self, steps, ceil4):
+        """The same workload with option mxf4_prefill: activations quantised to MXFP4, both expert products on
+        tcgen05.mma.kind::mxf4.  Outside the accuracy contract by construction (4-bit activations), so it is
+        reported beside the default path, with its error against the quantisation-aware oracle and the plain one."""
+        import oracle
+        torch, shape, T, k = self.torch, self.shape, self.T, self.shape.top_k
+        self.layer.set_option("mxf4_prefill", 1)
+        try:
+            self.warm(3)
+            groups = self.timed_groups(steps)
+            ms = statistics.median(groups) / steps
+            stage_ms, _ = self.stage_profile(steps)
+            out, idx, _ = self.run(self.d_batches[0], logit_bias=self.d_lb, want_routing=True)
+            torch.cuda.synchronize()
+            hid = self.batches[0]
+            ridx, rw = oracle.route(hid, self.W.router_w, self.W.router_b, k, self.lb)
+            sample = np.unique(np.linspace(0, T - 1, 6).astype(np.int32))
+            got = out.cpu().numpy().astype(np.float64)[sample]
+            ref_q = oracle.experts(hid, ridx, rw, self.W, tokens=sample, quant_act=True)
+            ref = oracle.experts(hid, ridx, rw, self.W, tokens=sample)
+            eq = np.abs(got - ref_q)
+            layer_tf = T * k * shape.flops_per_pair / (ms * 1e-3) / 1e12
+            gemm_tf = T * k * shape.flops_per_pair / ((stage_ms["gate_up"] + stage_ms["down"]) * 1e-3) / 1e12
+            return {"option": "mxf4_prefill=1 (MXFP4-quantised activations, tcgen05.mma.kind::mxf4.block_scale.scale_vec::2X)",
+                    "ms_per_step": ms, "value": T / (ms * 1e-3), "unit": "tokens/s", "stage_ms_per_step": stage_ms,
+                    "layer_tflops": layer_tf, "layer_frac_of_mxf4_ceiling": layer_tf / ceil4,
+                    "layer_frac_of_mxfp4_nominal_9000": layer_tf / 9000.0,
+                    "expert_gemms_tflops": gemm_tf, "expert_gemms_frac_of_mxf4_ceiling": gemm_tf / ceil4,
+                    "expert_gemms_frac_of_mxfp4_nominal_9000": gemm_tf / 9000.0,
+                    "parity_vs_quantisation_aware_oracle": {
+                        "routing_mismatches": int((ridx != idx.cpu().numpy()).any(axis=1).sum()), "tokens": int(sample.size),
+                        "max_abs": float(eq.max()), "mean_rel": float(eq.mean() / np.abs(ref_q).mean()),
+                        "outputs_over_2e-2": float((eq > 2e-2).mean())},
+                    "error_vs_plain_oracle": {"max_abs": float(np.abs(got - ref).max()),
+                                              "mean_rel": float(np.abs(got - ref).mean() / np.abs(ref).mean()),
+                                              "note": "4-bit activations: outside the 2e-2 / 5e-3 contract by construction"}}
+        finally:
+            self.layer.set_option("mxf4_prefill", 0)
+
     def close(self):
         self.layer.close()
         del self.d_batches, self.d_out
@@ -1051,6 +1092,8 @@ def side_config(workload, args, local_rank, peaks, peak_kind, traffic_table):
     out = {"description": run.desc, "tokens_per_step": run.T, "ms_per_step": ms / args.steps,
            "ms_per_step_min": min(groups) / args.steps, "groups": len(groups), "value": run.T / step_s, "unit": "tokens/s",
            "roofline": roof, "parity": run.parity(8), "status": run.layer.status()}
+    if run.T > 384 and "mma_issue_ceiling_tflops" in roof:
+        out["mxf4_variant"] = run.mxf4_variant(args.steps, roof["mma_issue_ceiling_tflops"]["mxf4_128x256"])
     run.close()
     return out
 
@@ -1086,6 +1129,12 @@ def run_moe(args, rank, world, local_rank):
         ids = [layer.ep_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         layer.ep_init(ids[0])
+
+        def gather(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+        ep_peer = (not args.ep_nccl_exchange) and layer.ep_enable_peer_stores(gather)
     n_batches, batches, lb = run.n_batches, run.batches, run.lb
 
     # pinned host buffers for the end-to-end arm
@@ -1150,6 +1199,9 @@ def run_moe(args, rank, world, local_rank):
                     "algorithmic_flops_per_launch": ep_rows * shape.flops_per_pair,
                     "ep_stage_ms_per_step_max_over_ranks": ep_ms, "rows_received_rank0": ep_rows,
                     "all_to_all_exposed_ms": ep_ms["dispatch_a2a"] + ep_ms["combine_a2a"],
+                    "exchange": ("this library's own stores into the peers' buffers over NVLink (token rows by a scatter kernel, outputs from "
+                                 "the down product's epilogue); NCCL gathers the histograms and orders the ranks"
+                                 if ep_peer else "grouped ncclSend/ncclRecv"),
                     "mma_issue_ceiling_tflops": {"mxf8f6f4_128x128": ceil8, "mxf4_128x256": ceil4},
                     "frac_of_mxf4_ceiling": achieved / ceil4, "frac_of_mxfp4_nominal_9000": achieved / 9000.0}
         roofline["frac"] = achieved / roofline["peak"]
@@ -1162,6 +1214,9 @@ def run_moe(args, rank, world, local_rank):
             roofline["weak_efficiency_same_workload"] = n1[0] / (ms / args.steps)
     else:
         roofline = moe_roofline(run, step_s, stage_ms, 0, peaks, peak_kind, traffic_table)
+    mxf4_variant = None
+    if not ep and T > 384 and "mma_issue_ceiling_tflops" in roofline and not any(o.startswith("mxf4_prefill") for o in args.option):
+        mxf4_variant = run.mxf4_variant(args.steps, roofline["mma_issue_ceiling_tflops"]["mxf4_128x256"])
 
     parity = run.parity(16 if ep else 8) if rank == 0 or ep else None
     if ep:   # the pass is collective: every rank ran it, rank 0 checked its own tokens
@@ -1186,6 +1241,8 @@ def run_moe(args, rank, world, local_rank):
                     "api": "neon_moe_forward_host_batches (pipelined copies" + ("; every batch an expert-parallel pass)" if ep else ")"),
                     "blocking_call_per_step_value": tokens_per_step * e2e_steps / e2e_blocking_s},
             "gpu_launches": int(launches), "roofline": roofline, "parity": parity, "clocks": clk}
+    if mxf4_variant:
+        line["mxf4_variant"] = mxf4_variant
 
     if rank == 0 and world == 1 and args.workload == "cfg1" and not args.no_side_configs:
         run.close()

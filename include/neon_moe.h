@@ -142,6 +142,20 @@ int neon_moe_ep_init(neon_moe_handle* h, const void* id128);
 int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden_bf16, int T, const float* logit_bias,
                         float* out_f32, int32_t* topk_idx, float* topk_w, void* cuda_stream);
 
+/* Exchanges by this library's own stores over NVLink instead of NCCL send/receive.  Every rank exports 128
+ * bytes (CUDA IPC handles of its two receive buffers), the application gathers them by any host channel
+ * (ranks in rank order) and hands all of them to every rank's import, which maps the peers' buffers; when
+ * EVERY rank has imported successfully, every rank sets option "ep_peer" to 1 (a collective decision: the
+ * ranks must use the same exchange).  From then on neon_moe_forward_ep writes token rows straight into the
+ * expert owners' receive buffers, and the down product's epilogue writes each output row straight into its
+ * token owner's buffer while the product runs; NCCL only gathers the histograms and orders the ranks
+ * (two barriers per pass).  Same results as the NCCL exchange.  One process per GPU, one node. */
+int neon_moe_ep_peer_export(neon_moe_handle* h, void* handles128);
+int neon_moe_ep_peer_import(neon_moe_handle* h, const void* all_handles /* ep_size x 128 bytes */);
+
+/* Exchanges the last neon_moe_forward_ep call needed: 1, or more when it ran as split passes. */
+int neon_moe_ep_subpasses(const neon_moe_handle* h);
+
 /* Device times of the last expert-parallel pass, ms[5] = {route+dispatch+pack, counts +
  * dispatch all-to-all, local experts, combine all-to-all, combine}; rows received by this
  * rank in *rows_received (may be NULL).  Synchronises. */
@@ -225,6 +239,18 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * "router_mma" (default 1): passes above router_wide_max tokens compute the router logits on tensor
  * cores (mma.sync, 16 tokens per CTA; 32 or 128 experts); 0 = the CUDA-core router that shares each
  * weight read between 8 tokens.  Same routing; logits differ in summation order only.
+ * "decode_fused" (default 1) / "decode_fused_tokens" (default 1, at most 8): passes of up to that many
+ * tokens (and top_k * T <= 32) run as ONE cooperative kernel - router, both expert products, SwiGLU and
+ * combine, no dispatch pass; its CTAs wait for one another with bounded waits (status word on a timeout).
+ * Measured at the gpt-oss-20b shapes it wins for single-token passes and loses above, hence the default.
+ * "decode_wait_limit": SM clocks such a wait may take (default 4e8).  "decode_stall_test": 1 makes the
+ * kernel's first wait expect a signal nobody sends, so that the bounded wait can be tested without
+ * faulting the GPU.
+ * "mxf4_prefill" (default 0): 1 runs passes of more than 384 tokens on tcgen05.mma.kind::mxf4 with the
+ * activations quantised to MXFP4 (blocks of 32, E8M0 scale 2^(floor(log2 amax) - 2), nearest e2m1, ties to
+ * even).  Four-bit activations put the result ~20 % (mean relative) away from the unquantised one - far
+ * outside the 2e-2 / 5e-3 contract - so it is an option; it agrees with an oracle that applies the same
+ * quantisation to accumulation noise.
  * "n_ctas", "ctas_per_sm": grid size of the grouped GEMMs (default: one CTA per SM).
  * Routing is deterministic for a given router kernel, but the three routers (one CTA per token,
  * tensor-core, and the one neon_moe_forward_static uses) add the 2880 products in different

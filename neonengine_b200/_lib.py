@@ -127,6 +127,9 @@ SIGNATURES = {
     "neon_moe_ep_times": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
     "neon_moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  ctypes.POINTER(c_int)]),
+    "neon_moe_ep_subpasses": (c_int, [c_void_p]),
+    "neon_moe_ep_peer_export": (c_int, [c_void_p, c_void_p]),
+    "neon_moe_ep_peer_import": (c_int, [c_void_p, c_void_p]),
     "neon_moe_ep_overflow": (c_int, [c_void_p, c_int, c_int, c_void_p, ctypes.POINTER(c_int)]),
     "neon_moe_forward_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "neon_moe_forward_host_batches": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),

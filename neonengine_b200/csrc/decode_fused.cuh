@@ -47,7 +47,8 @@ constexpr int kDecBuilderThreads = 384;  // 12 builder warps
 constexpr int kDecThreads = 64 + 128 + kDecBuilderThreads;
 constexpr int kDecCacheChunks = 24;      // K chunks of a product at most: one token-operand tile each
 constexpr int kDecTailBytes = 12 * 1024; // barriers, routing tables, logits
-constexpr int kDecMaxSlices = 8;
+constexpr int kDecMaxSlices = 16;       // K slices of a router dot product (one warp computes one slice of one expert)
+constexpr int kDecRouterWarps = 3;      // warps 3..5 of every CTA compute router shares
 // Token-operand tiles: gate_up = 2 terms x 8 token rows (2 KB); down = 4 terms x R rows, R = 4 when no
 // expert can have more than 4 tokens (T <= 4: 2 KB tiles), else 8 (4 KB tiles).  What the tiles leave
 // of the shared memory goes to weight stages: the stream from HBM needs ~2 us x 45 GB/s per SM in flight.
@@ -69,7 +70,7 @@ struct DecodeParams {
     int rows_dn;               // token rows per term of the down product's operand tiles: 4 or 8
     int stages;                // weight stages in use
     uint32_t a_tx_bytes;
-    float* router_part;        // [T][E][8 slice slots]; slots >= n_slices are zero
+    float* router_part;        // [T][E][16 slice slots]; slots >= n_slices are zero
     float* gu_part;            // [item][kDecParts][8 tokens][128 rows]
     float* dn_part;
     unsigned* counters;        // [0] pass number; [1] router shares written since set-up (never reset); [4+256 ..) flags
@@ -120,7 +121,6 @@ __device__ __forceinline__ bool wait_counter(const unsigned* p, unsigned target,
             atomicCAS(status, 0, code);
             return false;
         }
-        __nanosleep(64);
     }
 }
 
@@ -346,6 +346,50 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
     unsigned* const gu_flag = p.counters + 4 + 256;
     unsigned* const dn_done = p.counters + 4 + 256 + 4 * p.gu_items_cap;
 
+    // ---- router shares first, before anything else is set up: they need no shared memory, and every CTA waits for them.
+    //      Unit u = (expert, K slice) is computed by warp 3 + u % 3 of CTA u / 3: one 16-byte load per lane and token.
+    if (warp >= 3 && warp < 3 + kDecRouterWarps) {
+        const int unit = cta * kDecRouterWarps + (warp - 3);
+        if (unit < E * p.n_slices) {
+            const int nvec = H / 8;
+            const int e = unit % E, sl = unit / E;
+            const int vps = (nvec + p.n_slices - 1) / p.n_slices, v0 = sl * vps, v1 = min(nvec, v0 + vps);
+            float acc[kDecMaxTok];
+#pragma unroll
+            for (int t = 0; t < kDecMaxTok; ++t) acc[t] = 0.f;
+            const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * H);
+            for (int vb = v0; vb < v1; vb += 32) {
+                const int v = vb + lane;
+                const uint4 wv = v < v1 ? __ldg(wrow + v) : make_uint4(0, 0, 0, 0);
+                uint4 xv[kDecMaxTok];
+#pragma unroll
+                for (int t = 0; t < kDecMaxTok; ++t)
+                    xv[t] = (t < T && v < v1) ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * H) + v) : make_uint4(0, 0, 0, 0);
+                const uint32_t wa[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int t = 0; t < kDecMaxTok; ++t) {
+                    const uint32_t xa[4] = {xv[t].x, xv[t].y, xv[t].z, xv[t].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[t] = fmaf(__uint_as_float(xa[j] << 16), __uint_as_float(wa[j] << 16), acc[t]);
+                        acc[t] = fmaf(__uint_as_float(xa[j] & 0xffff0000u), __uint_as_float(wa[j] & 0xffff0000u), acc[t]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < kDecMaxTok; ++t) {
+                if (t < T) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+                    if (lane == 0) __stcg(p.router_part + ((size_t)t * E + e) * kDecMaxSlices + sl, acc[t]);
+                }
+            }
+            if (lane == 0) red_release_add(router_count, 1u);
+            __syncwarp();
+        }
+        if (warp == 3 && lane == 0) DEC_STAMP(2);
+    }
+
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
@@ -423,53 +467,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
     } else if (warp >= 2) {
         // ---- epilogue warps, first job: the router --------------------------------------------------------
         const int q4 = warp - 2;
-        if (q4 == 0 && cta < E * p.n_slices) {
-            // this CTA's (expert, K slice) dot product for every token: one warp, all loads in flight at once
-            const int nvec = H / 8;
-            const int e = cta % E, sl = cta / E;
-            const int vps = (nvec + p.n_slices - 1) / p.n_slices, v0 = sl * vps, v1 = min(nvec, v0 + vps);
-            float acc[kDecMaxTok];
-#pragma unroll
-            for (int t = 0; t < kDecMaxTok; ++t) acc[t] = 0.f;
-            const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * H);
-            for (int vb = v0; vb < v1; vb += 32 * 4) {  // four vectors per lane in flight for the weights and for every token
-                uint4 wv[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int v = vb + 32 * i + lane;
-                    wv[i] = v < v1 ? __ldg(wrow + v) : make_uint4(0, 0, 0, 0);
-                }
-#pragma unroll
-                for (int t = 0; t < kDecMaxTok; ++t) {
-                    if (t < T) {
-                        uint4 xv[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int v = vb + 32 * i + lane;
-                            xv[i] = v < v1 ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * H) + v) : make_uint4(0, 0, 0, 0);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint32_t xa[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w}, wa[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                acc[t] = fmaf(__uint_as_float(xa[j] << 16), __uint_as_float(wa[j] << 16), acc[t]);
-                                acc[t] = fmaf(__uint_as_float(xa[j] & 0xffff0000u), __uint_as_float(wa[j] & 0xffff0000u), acc[t]);
-                            }
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < kDecMaxTok; ++t) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
-                if (lane == 0 && t < T) __stcg(p.router_part + ((size_t)t * E + e) * kDecMaxSlices + sl, acc[t]);
-            }
-            if (lane == 0) red_release_add(router_count, 1u);
-            __syncwarp();
-        }
-        if (q4 == 0 && lane == 0) DEC_STAMP(2);
         {
             // the router counter is never reset: after this pass's n_router shares it stands at pass * n_router
             // (mod 2^32).  One lane per CTA polls it; the other warps wait at the named barrier.
@@ -492,10 +489,11 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
             if (ok) {
                 for (int t = q4; t < T; t += 4) {  // logits, top k, softmax: every CTA, identically
                     for (int e = lane; e < E; e += 32) {
-                        // all eight slice slots in two loads (slots beyond n_slices stay zero from set-up), added in order
+                        // all sixteen slice slots in four loads (slots beyond n_slices stay zero from set-up), added in order
                         const float4* part = reinterpret_cast<const float4*>(p.router_part + ((size_t)t * E + e) * kDecMaxSlices);
-                        const float4 a = __ldcg(part), b = __ldcg(part + 1);
+                        const float4 a = __ldcg(part), b = __ldcg(part + 1), c = __ldcg(part + 2), d = __ldcg(part + 3);
                         float v = ((((((a.x + a.y) + a.z) + a.w) + b.x) + b.y) + b.z) + b.w;
+                        v = (((((((v + c.x) + c.y) + c.z) + c.w) + d.x) + d.y) + d.z) + d.w;
                         v += bf16_bits_to_float(p.br[e]);
                         if (p.logit_bias) v += p.logit_bias[e];
                         s_lg[t * E + e] = v;
@@ -829,16 +827,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
                 if (gm < gu.m_tiles && ch0 < p.I) {
                     const int gitem = es * gu.m_tiles + gm, np = gu.parts(gitem);
                     const uint4 braw = __ldg(reinterpret_cast<const uint4*>(p.gu_bias + (size_t)s_exp[es] * 2 * p.I + 2 * ch0));  // 4 (gate, linear) pairs
-                    {
-                        // one lane per distinct item polls (the lanes of a warp share one or two items): every poll that
-                        // is not sent leaves room in the memory system for the stores that are being waited for
-                        const unsigned same = __match_any_sync(__activemask(), gitem);
-                        int ok = 1;
-                        if ((__ffs(same) - 1) == lane) ok = wait_flags(gu_flag + 4 * gitem, np, pass, abort_flag, p.status, 8, p.wait_limit);
-                        ok = __shfl_sync(same, ok, __ffs(same) - 1);
-                        if (!ok) goto roles_done;
-                        fence_acq_rel_gpu();
-                    }
+                    if (!wait_flags(gu_flag + 4 * gitem, np, pass, abort_flag, p.status, 8, p.wait_limit)) goto roles_done;
                     if (bt == 0 && epoch == 0) DEC_STAMP(13);
                     const int tok = s_tok[es * 8 + j];
                     const int row_g = 32 * ((ch0 & 63) >> 4) + (ch0 & 15);

@@ -100,6 +100,64 @@ inline int ep_first_overflow(const int32_t* all_counts, int ep_size, int n_exper
     return -1;
 }
 
+// ---- exchanges by plain stores into the peers' buffers (NVLink peer-to-peer) ----------------------
+// With the peers' receive buffers mapped into this process (CUDA IPC), a rank writes the rows it owes
+// straight where they belong: token rows into the expert owner's xrecv, expert outputs - from the down
+// product's epilogue, tile by tile while the product runs - into the token owner's yrecv.  No copy
+// engine, no library kernel and no TMA multicast touches peer memory: only this library's own st.global.
+constexpr int kMaxPeerRanks = 8;
+
+// Where the rows of one block go: block b (rows [row_off[b], row_off[b + 1]) of the local order) lands in
+// buffer base[b] starting at row dst_off[b].
+template <typename T>
+struct PeerRows {
+    int n_ranks;  // 0 = not in use
+    int row_off[kMaxPeerRanks + 1];
+    int dst_off[kMaxPeerRanks];
+    T* base[kMaxPeerRanks];
+};
+
+template <typename T>
+__device__ __forceinline__ T* peer_row(const PeerRows<T>& t, int row, int width) {
+    int b = 0;
+    while (b + 1 < t.n_ranks && row >= t.row_off[b + 1]) ++b;
+    return t.base[b] + (size_t)(t.dst_off[b] + row - t.row_off[b]) * width;
+}
+
+// Host side of the two tables of one rank, from the gathered histograms.  rows(a -> b) = entries rank a
+// routes to rank b's experts.  Dispatch: my sorted rows for rank r start at send_off[r] and land in r's xrecv
+// behind the rows of the ranks before me.  Return: received rows from rank r start at recv_off[r] and go
+// back into r's yrecv where r's sorted rows for me start.
+inline void ep_peer_offsets(const int32_t* all_counts, int ep_size, int n_experts, int rank, int32_t* dispatch_dst_off,
+                            int32_t* return_dst_off) {
+    const int nl = n_experts / ep_size;
+    auto rows = [&](int a, int b) {
+        int s = 0;
+        for (int e = 0; e < nl; ++e) s += all_counts[(size_t)a * n_experts + b * nl + e];
+        return s;
+    };
+    for (int r = 0; r < ep_size; ++r) {
+        int d = 0, b = 0;
+        for (int q = 0; q < rank; ++q) {
+            d += rows(q, r);   // rows of lower ranks in r's receive buffer
+            b += rows(r, q);   // rows r sends to lower ranks, in r's sorted order
+        }
+        dispatch_dst_off[r] = d;
+        return_dst_off[r] = b;
+    }
+}
+
+// Token rows to the expert owners: sorted entry p -> its place in the owner's xrecv (16-byte vectors).
+__global__ void scatter_rows_kernel(const uint16_t* __restrict__ hidden, const int32_t* __restrict__ perm, int k, int H, int n,
+                                    PeerRows<uint16_t> t) {
+    const int p = blockIdx.x;
+    if (p >= n) return;
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)(perm[p] / k) * H);
+    uint4* dst = reinterpret_cast<uint4*>(peer_row(t, p, H));
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+}
+
 // xsend[p, :] = hidden[perm[p] / k, :] for the n sorted entries (16-byte vectors).
 __global__ void pack_rows_kernel(const uint16_t* __restrict__ hidden, const int32_t* __restrict__ perm, int k, int H, int n,
                                  uint16_t* __restrict__ xsend) {

@@ -16,6 +16,7 @@
 #include "moe_common.cuh"
 #include "moe_kernels.cuh"
 #include "sm100_ptx.cuh"
+#include "ep.cuh"
 
 namespace neon {
 
@@ -686,6 +687,9 @@ struct GmmParams {
     float* y;              // [n][hidden] fp32, sorted order
     int hidden;
     int* status;
+    // expert parallelism with peer stores: row perm[pos] of the received order goes straight into its token owner's
+    // buffer (peer.n_ranks == 0: rows go to y)
+    PeerRows<float> peer;
 };
 
 // MX4: packed 4-bit operands (kind::mxf4): a weight box is 8 KB in shared memory, rows are 64 B.
@@ -978,15 +982,22 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             // round by shuffles: the store loop below then has no dependent global loads.
             constexpr int NW = (BN_MAX + 31) / 32;
             float tok_scale[NW], tok_w[NW];
+            float* tok_dst[NW];  // down product: where each token's output row goes
 #pragma unroll
             for (int k = 0; k < NW; ++k) {
                 const int tix = 32 * k + lane;
                 const bool in = tix < rows;
                 tok_scale[k] = STACK ? (in ? (p.row_scale ? p.row_scale[row0 + tix] : p.row_scale_const) : 0.f) : 1.f;
-                tok_w[k] = (!GATE_UP && in) ? p.route_w[p.perm[row0 + tix]] : 0.f;
+                tok_w[k] = 0.f;
+                tok_dst[k] = nullptr;
+                if (!GATE_UP && in) {
+                    const int ent = p.perm[row0 + tix];
+                    tok_w[k] = p.route_w[ent];
+                    tok_dst[k] = p.peer.n_ranks ? peer_row(p.peer, ent, p.hidden) : p.y + (size_t)(row0 + tix) * p.hidden;
+                }
             }
             // one token's value of this lane's row: bias, then SwiGLU (gate_up) or the routing weight (down)
-            auto finish = [&](int tix, float acc, float w_tok) {
+            auto finish = [&](int tix, float acc, float w_tok, float* dst) {
                 const int pos = row0 + tix;
                 const float mine = acc + bias;
                 if (GATE_UP) {
@@ -997,7 +1008,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         p.a_out[(size_t)pos * p.inter + ch] = g / (1.f + expf(-p.alpha * g)) * (l + 1.f);
                     }
                 } else if (valid && tix < rows) {
-                    p.y[(size_t)pos * p.hidden + row] = w_tok * mine;
+                    dst[row] = w_tok * mine;
                 }
             };
             if (BN_MAX <= 32) {
@@ -1032,7 +1043,8 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     if (j < npad) {  // uniform over the warp
                         const float sc = STACK ? __shfl_sync(0xffffffffu, tok_scale[0], j) : 1.f;
                         const float wt = GATE_UP ? 0.f : __shfl_sync(0xffffffffu, tok_w[0], j);
-                        finish(j, STACK ? vals[j] * sc : vals[j], wt);
+                        float* dst = GATE_UP ? nullptr : reinterpret_cast<float*>(__shfl_sync(0xffffffffu, (unsigned long long)tok_dst[0], j));
+                        finish(j, STACK ? vals[j] * sc : vals[j], wt, dst);
                     }
                 }
                 continue;
@@ -1054,6 +1066,23 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                             for (int i = 0; i < 8; ++i) v[i] = fmaf(u[i], f, v[i]);
                         }
                     }
+                    if (GATE_UP && !STACK) {
+                        // two tokens per step: lanes 0..15 (gate rows) finish token j, lanes 16..31 (linear rows) token j + 1,
+                        // each half getting the other half's row of its token by one exchange - all 32 lanes do SwiGLU work
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2) {
+                            const float m0 = v[i] + bias, m1 = v[i + 1] + bias;
+                            const float got = __shfl_xor_sync(0xffffffffu, lane < 16 ? m1 : m0, 16);
+                            const float gate = lane < 16 ? m0 : got, lin = lane < 16 ? got : m1;
+                            const int tix = j8 + i + (lane >> 4);
+                            if (tix < rows) {
+                                const float g = fminf(gate, p.limit);
+                                const float l = fminf(fmaxf(lin, -p.limit), p.limit);
+                                p.a_out[(size_t)(row0 + tix) * p.inter + ch] = __fdividef(g, 1.f + __expf(-p.alpha * g)) * (l + 1.f);
+                            }
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int tix = j8 + i, pos = row0 + tix;
@@ -1068,7 +1097,8 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                             }
                         } else {
                             const float wt = __shfl_sync(0xffffffffu, tok_w[k], tix & 31);
-                            if (valid && tix < rows) p.y[(size_t)pos * p.hidden + row] = wt * mine;
+                            float* dst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, (unsigned long long)tok_dst[k], tix & 31));
+                            if (valid && tix < rows) dst[row] = wt * mine;
                         }
                     }
                 }
@@ -1077,6 +1107,7 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);
         }
+        if (!GATE_UP && p.peer.n_ranks) __threadfence_system();  // rows written into other GPUs' buffers: visible before the kernel ends
     }
 done:
     __syncwarp();

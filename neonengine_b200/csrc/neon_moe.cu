@@ -75,8 +75,11 @@ struct neon_moe_handle {
     CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
     CUtensorMap tm4_gu{}, tm4_dn{}, tm4_gu2{}, tm4_dn2{};  // the same boxes left packed (4-bit in shared memory)
     // one-launch decode pass (T <= 8): router partial sums, partial sums of both products, counters
-    int decode_fused = 1;         // 1 = passes of at most decode_max_tokens tokens run as one cooperative kernel
-    int decode_max_tokens = 0;    // largest pass the one-launch kernel serves on this handle (0 = not available)
+    int decode_fused = 1;         // 1 = passes of at most decode_fused_tokens tokens run as one cooperative kernel
+    int decode_max_tokens = 0;    // largest pass the one-launch kernel can serve on this handle (0 = not available)
+    int decode_fused_tokens = 1;  // largest pass it serves by default: measured per pass at the gpt-oss-20b shapes, one launch vs
+                                  // the multi-kernel path: T=1 36.5 vs 38.7 us, T=2 51 vs 49, T=8 129 vs 79 (more distinct experts per
+                                  // CTA run: more rebuilds of the token-operand tiles, longer combine)
     int decode_stall_test = 0;    // test hook: the kernel's first wait expects one arrival too many and must time out
     long long decode_wait_limit = kWaitLimitCycles;
     float *dec_router_part = nullptr, *dec_gu_part = nullptr, *dec_dn_part = nullptr;
@@ -91,6 +94,12 @@ struct neon_moe_handle {
     int32_t *all_counts_d = nullptr, *row_expert = nullptr, *host_pinned = nullptr;
     float *s_w = nullptr, *yrecv = nullptr, *yback = nullptr, *ones = nullptr;
     uint16_t *xsend = nullptr, *xrecv = nullptr;
+    // exchanges by peer stores: the peers' xrecv / yrecv mapped through CUDA IPC
+    int ep_peer = 0;                                // 1 = both exchanges are this library's own stores into peer memory
+    uint16_t* peer_x[kMaxPeerRanks] = {};
+    float* peer_y[kMaxPeerRanks] = {};
+    bool peer_mapped[kMaxPeerRanks] = {};
+    int32_t *ep_bar_src = nullptr, *ep_bar_dst = nullptr;
     cudaEvent_t ep_ev[6] = {};
     bool ep_timed = false;
     int ep_last_recv = 0;
@@ -184,9 +193,14 @@ void free_all(neon_moe_handle* h) {
                     h->x_act, h->a_act, h->x_scale, h->x_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
                     h->n_tiles, h->row_tile, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
                     h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv,
-                    h->dec_router_part, h->dec_gu_part, h->dec_dn_part, h->dec_counters};
+                    h->dec_router_part, h->dec_gu_part, h->dec_dn_part, h->dec_counters, h->ep_bar_src, h->ep_bar_dst};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    for (int r = 0; r < kMaxPeerRanks; ++r)
+        if (h->peer_mapped[r]) {
+            cudaIpcCloseMemHandle(h->peer_x[r]);
+            cudaIpcCloseMemHandle(h->peer_y[r]);
+        }
     if (h->host_pinned) cudaFreeHost(h->host_pinned);
     for (cudaEvent_t ev : h->ep_ev)
         if (ev) cudaEventDestroy(ev);
@@ -581,7 +595,8 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
             (rc = dev_alloc(h, &h->s_inv, ns)) || (rc = dev_alloc(h, &h->all_counts_d, E * cfg->ep_size)) ||
             (rc = dev_alloc(h, &h->row_expert, n)) || (rc = dev_alloc(h, &h->ones, n)) ||
             (rc = dev_alloc(h, &h->xsend, ns * Hh)) || (rc = dev_alloc(h, &h->xrecv, n * Hh)) ||
-            (rc = dev_alloc(h, &h->yrecv, ns * Hh)) || (rc = dev_alloc(h, &h->yback, n * Hh)))
+            (rc = dev_alloc(h, &h->yrecv, ns * Hh)) || (rc = dev_alloc(h, &h->yback, n * Hh)) ||
+            (rc = dev_alloc(h, &h->ep_bar_src, (size_t)4)) || (rc = dev_alloc(h, &h->ep_bar_dst, (size_t)cfg->ep_size + 4)))
             return bail(rc);
         if (cudaMallocHost(&h->host_pinned, (E * cfg->ep_size + n) * sizeof(int32_t)) != cudaSuccess)
             return bail(fail(h, NEON_MOE_ECUDA, "cudaMallocHost failed"));
@@ -638,7 +653,7 @@ int neon_moe_set_weights(neon_moe_handle* h, const void* router_w, const void* r
 // rows, k_eff = 1, route_w = 1).
 static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_eff, const int32_t* idx, int e_lo,
                         const float* route_w, const float* hidden_amax, float* out, cudaStream_t st, bool prof,
-                        bool dispatched = false) {
+                        bool dispatched = false, const PeerRows<float>* peer = nullptr) {
     const int H = h->cfg.hidden, I = h->cfg.inter, EL = h->n_local;
     const int n = rows * k_eff;
     DispatchArrays d{h->count, h->offset, h->perm, h->inv};
@@ -698,6 +713,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
             if (mx4_dn) g.row_scale_const = a_bound * (1.f / 6.f);  // split_rows_fp4_kernel's first-term scale
         }
         g.m_tiles = (H + 127) / 128; g.n_chunks = nch_i; g.rows_total = H;
+        if (peer) g.peer = *peer;  // the epilogue writes every row straight into its token owner's buffer
 #ifdef NEON_MOE_INSTRUMENT
         g.trace = h->trace_which == 1 ? nullptr : h->trace;
 #endif
@@ -732,6 +748,7 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         launch_expert<false>(h, p, rows, st);
         mark(h, st, prof);
     }
+    if (peer && h->path == 2) return NEON_MOE_OK;  // nothing to gather: the rows are where they belong
     dim3 cgrid((H / 4 + 127) / 128, rows);
     if (h->path == 2)
         launch_k(h->pdl != 0, combine_main_kernel, cgrid, dim3(128), 0, st, (const float*)h->y, (const int32_t*)h->inv, rows, H,
@@ -761,7 +778,7 @@ static int launch_decode_fused(neon_moe_handle* h, const void* hidden, int T, co
     p.gu_sfa = h->gu_sfa; p.dn_sfa = h->dn_sfa; p.gu_bias = h->gu_bias; p.dn_bias = h->dn_bias;
     p.gu_m_tiles = 2 * I / 128; p.dn_m_tiles = (H + 127) / 128; p.nch_h = h->kp_h / kChunkK; p.nch_i = h->kp_i / kChunkK;
     const int grid = h->n_sms;
-    p.n_slices = std::max(1, std::min(kDecMaxSlices, grid / E));
+    p.n_slices = std::max(1, std::min(kDecMaxSlices, grid * kDecRouterWarps / E));  // (expert, slice) units for the 3 router warps of every CTA
     p.rows_dn = T <= 4 ? 4 : 8;
     p.stages = dec_stages(p.rows_dn, kDecodeSmemBytes);
     p.a_tx_bytes = h->a_tx_bytes;
@@ -894,7 +911,7 @@ static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const fl
     CU(h, cudaSetDevice(h->cfg.device));
     const int k = h->cfg.top_k, n = T * k;
     const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
-    if (h->path == 2 && h->decode_fused && T <= h->decode_max_tokens && !prof && h->tile_override == 0 && !h->mx4 && !h->fuse_dispatch) {
+    if (h->path == 2 && h->decode_fused && T <= std::min(h->decode_max_tokens, h->decode_fused_tokens) && !prof && h->tile_override == 0 && !h->mx4 && !h->fuse_dispatch) {
         int rc = launch_decode_fused(h, hidden, T, logit_bias, out, st);
         if (rc) return rc;
         if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
@@ -966,6 +983,49 @@ int neon_moe_ep_init(neon_moe_handle* h, const void* id128) {
     return NEON_MOE_OK;
 }
 
+int neon_moe_ep_peer_export(neon_moe_handle* h, void* handles128) {
+    if (!h || !handles128) return NEON_MOE_EINVAL;
+    if (h->cfg.ep_size < 2 || !h->xrecv || !h->yrecv) return fail(h, NEON_MOE_ESTATE, "peer export needs an expert-parallel handle");
+    CU(h, cudaSetDevice(h->cfg.device));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t hx, hy;
+    CU(h, cudaIpcGetMemHandle(&hx, h->xrecv));
+    CU(h, cudaIpcGetMemHandle(&hy, h->yrecv));
+    memcpy(handles128, &hx, 64);
+    memcpy(static_cast<char*>(handles128) + 64, &hy, 64);
+    return NEON_MOE_OK;
+}
+
+int neon_moe_ep_peer_import(neon_moe_handle* h, const void* all_handles) {
+    if (!h || !all_handles) return NEON_MOE_EINVAL;
+    const int G = h->cfg.ep_size, me = h->cfg.ep_rank;
+    if (G < 2 || G > kMaxPeerRanks) return fail(h, NEON_MOE_EINVAL, "peer stores serve 2..%d ranks", kMaxPeerRanks);
+    CU(h, cudaSetDevice(h->cfg.device));
+    for (int r = 0; r < G; ++r) {
+        if (r == me) {
+            h->peer_x[r] = h->xrecv;
+            h->peer_y[r] = h->yrecv;
+            continue;
+        }
+        if (h->peer_mapped[r]) continue;
+        cudaIpcMemHandle_t hx, hy;
+        memcpy(&hx, static_cast<const char*>(all_handles) + (size_t)r * 128, 64);
+        memcpy(&hy, static_cast<const char*>(all_handles) + (size_t)r * 128 + 64, 64);
+        void *px = nullptr, *py = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&px, hx, cudaIpcMemLazyEnablePeerAccess);
+        if (e == cudaSuccess) e = cudaIpcOpenMemHandle(&py, hy, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            if (px) cudaIpcCloseMemHandle(px);
+            cudaGetLastError();
+            return fail(h, NEON_MOE_ECUDA, "mapping rank %d's buffers failed: %s", r, cudaGetErrorString(e));
+        }
+        h->peer_x[r] = static_cast<uint16_t*>(px);
+        h->peer_y[r] = static_cast<float*>(py);
+        h->peer_mapped[r] = true;
+    }
+    return NEON_MOE_OK;
+}
+
 int neon_moe_ep_plan(const int32_t* all_counts, int ep_size, int n_experts, int rank, int32_t* send_rows,
                      int32_t* send_off, int32_t* recv_rows, int32_t* recv_off, int32_t* row_expert, int row_expert_cap,
                      int* n_recv) {
@@ -1014,7 +1074,7 @@ static int ep_pass(neon_moe_handle* h, const uint16_t* hidden, int T, const floa
     int32_t* all_counts = h->host_pinned;
     int32_t* row_expert_h = h->host_pinned + (size_t)E * G;
     CU(h, cudaMemcpyAsync(all_counts, h->all_counts_d, (size_t)E * G * 4, cudaMemcpyDeviceToHost, st));
-    if (n > 0) {  // runs while the histograms travel
+    if (n > 0 && !(h->ep_peer && h->path == 2)) {  // runs while the histograms travel (the peer-store exchange needs no packed copy)
         pack_rows_kernel<<<n, 128, 0, st>>>(hidden, h->s_perm, k, H, n, h->xsend);
         h->launches++;
     }
@@ -1043,6 +1103,42 @@ static int ep_pass(neon_moe_handle* h, const uint16_t* hidden, int T, const floa
     h->ep_last_recv = R;
     h->ep_subpasses++;
     if (R > 0) CU(h, cudaMemcpyAsync(h->row_expert, row_expert_h, (size_t)R * 4, cudaMemcpyHostToDevice, st));
+    const bool peer = h->ep_peer && h->path == 2 && G <= kMaxPeerRanks;
+    // a collective with nothing to move: when it has run on this rank, every rank's work enqueued before it has finished
+    auto rank_barrier = [&]() -> int {
+        NC(h, nc.AllGather(h->ep_bar_src, h->ep_bar_dst, 1, ncclInt32, h->comm, st));
+        return NEON_MOE_OK;
+    };
+    if (peer) {
+        // 3'. token rows straight into the expert owners' receive buffers (this library's own stores over NVLink)
+        int32_t disp_off[kMaxPeerRanks], ret_off[kMaxPeerRanks];
+        ep_peer_offsets(all_counts, G, E, me, disp_off, ret_off);
+        PeerRows<uint16_t> tx{};
+        PeerRows<float> ty{};
+        tx.n_ranks = ty.n_ranks = G;
+        for (int r = 0; r < G; ++r) {
+            tx.row_off[r] = send_off[r]; tx.dst_off[r] = disp_off[r]; tx.base[r] = h->peer_x[r];
+            ty.row_off[r] = recv_off[r]; ty.dst_off[r] = ret_off[r]; ty.base[r] = h->peer_y[r];
+        }
+        tx.row_off[G] = n;
+        ty.row_off[G] = R;
+        if (n > 0) {
+            scatter_rows_kernel<<<n, 128, 0, st>>>(hidden, h->s_perm, k, H, n, tx);
+            h->launches++;
+        }
+        int rc = rank_barrier();  // every rank's rows have landed before anyone multiplies
+        if (rc) return rc;
+        CU(h, cudaEventRecord(h->ep_ev[2], st));
+        // 4'. local experts; the down product's epilogue writes every output row into its token owner's yrecv
+        if (R > 0) {
+            rc = experts_core(h, h->xrecv, R, 1, h->row_expert, 0, h->ones, nullptr, h->yback, st, false, false, &ty);
+            if (rc) return rc;
+        }
+        CU(h, cudaEventRecord(h->ep_ev[3], st));
+        rc = rank_barrier();      // every rank's products are done: all rows of my tokens are in yrecv
+        if (rc) return rc;
+        CU(h, cudaEventRecord(h->ep_ev[4], st));
+    } else {
     // 3. token rows to the owners of their experts
     NC(h, nc.GroupStart());
     for (int r = 0; r < G; ++r) {
@@ -1065,6 +1161,7 @@ static int ep_pass(neon_moe_handle* h, const uint16_t* hidden, int T, const floa
     }
     NC(h, nc.GroupEnd());
     CU(h, cudaEventRecord(h->ep_ev[4], st));
+    }
     // 6. routing-weighted sum of each token's slots, fixed slot order
     if (T > 0) {
         dim3 cgrid((H / 4 + 127) / 128, T);
@@ -1093,6 +1190,8 @@ int neon_moe_forward_ep(neon_moe_handle* h, const void* hidden, int T, const flo
     h->ep_subpasses = 0;
     return ep_pass(h, static_cast<const uint16_t*>(hidden), T, logit_bias, out, topk_idx, topk_w, static_cast<cudaStream_t>(cuda_stream), 0);
 }
+
+int neon_moe_ep_subpasses(const neon_moe_handle* h) { return h ? h->ep_subpasses : 0; }
 
 int neon_moe_ep_times(neon_moe_handle* h, double* ms5, int* rows_received) {
     if (!h || !ms5) return NEON_MOE_EINVAL;
@@ -1247,8 +1346,18 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     } else if (!strcmp(name, "graph_max_tokens")) {
         h->graph_max_tokens = (int)value;
         drop_graphs(h);
+    } else if (!strcmp(name, "ep_peer")) {
+        if (value) {
+            for (int r = 0; r < h->cfg.ep_size && r < kMaxPeerRanks; ++r)
+                if (!h->peer_x[r]) return fail(h, NEON_MOE_ESTATE, "ep_peer before neon_moe_ep_peer_import");
+            if (h->cfg.ep_size > kMaxPeerRanks) return fail(h, NEON_MOE_EINVAL, "peer stores serve at most %d ranks", kMaxPeerRanks);
+        }
+        h->ep_peer = value != 0;
     } else if (!strcmp(name, "decode_fused")) {
         h->decode_fused = (int)value;
+    } else if (!strcmp(name, "decode_fused_tokens")) {
+        if (value < 0 || value > kDecMaxTok) return fail(h, NEON_MOE_EINVAL, "decode_fused_tokens must lie in [0, %d]", kDecMaxTok);
+        h->decode_fused_tokens = (int)value;
     } else if (!strcmp(name, "decode_stall_test")) {
         h->decode_stall_test = (int)value;
     } else if (!strcmp(name, "decode_wait_limit")) {

@@ -120,6 +120,21 @@ class MoeLayerSystem:
         assert len(unique_id) == 128
         self._check(self._lib.neon_moe_ep_init(self._h, ctypes.c_char_p(unique_id)), "neon_moe_ep_init")
 
+    def ep_enable_peer_stores(self, all_gather_object) -> bool:
+        """Collective: maps every peer's receive buffers (CUDA IPC) and, when that worked on EVERY rank,
+        switches both exchanges to this library's own stores over NVLink.  ``all_gather_object(obj)`` must
+        return the list of every rank's ``obj`` in rank order (e.g. a wrapper of
+        ``torch.distributed.all_gather_object``).  Returns whether peer stores are in use."""
+        buf = ctypes.create_string_buffer(128)
+        ok = self._lib.neon_moe_ep_peer_export(self._h, buf) == 0
+        handles = all_gather_object(buf.raw if ok else None)
+        ok = ok and all(x is not None for x in handles)
+        if ok:
+            ok = self._lib.neon_moe_ep_peer_import(self._h, ctypes.c_char_p(b"".join(handles))) == 0
+        ok = all(all_gather_object(bool(ok)))
+        self.set_option("ep_peer", 1 if ok else 0)
+        return ok
+
     def run_ep(self, hidden, logit_bias=None, out=None, want_routing=False, stream=None):
         """Expert-parallel pass over this rank's tokens (collective across the group)."""
         import torch

@@ -1,6 +1,10 @@
-"""Expert parallelism on GPUs: two ranks (one process per GPU) run `neon_moe_forward_ep`
-through the C ABI and must reproduce the single-process CPU oracle: routing bit-exact,
-outputs within the contract tolerance.  Skipped when fewer than two GPUs are visible."""
+"""Expert parallelism on GPUs: ranks (one process per GPU) run `neon_moe_forward_ep` through the C ABI and
+must reproduce the single-process CPU oracle: routing bit-exact, outputs within the contract tolerance.
+Every case runs with the NCCL send/receive exchange and (names starting "peer_") with the exchanges done
+by the library's own stores into the peers' buffers.  Cases: ragged token counts on 2 ranks; 32 experts on up to 4 ranks; the 128-expert shape with 1024
+tokens per rank (128-token tiles, tensor-core router); and a pass whose rows do not fit a rank's
+receive room, which every rank must notice from the gathered histograms and run as split passes.
+Skipped when fewer than two GPUs are visible."""
 import os
 import socket
 import sys
@@ -18,7 +22,17 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, T, out_dir):
+def _oracle_sample(oracle, synth, shape, seed, hidden, sample):
+    """Oracle outputs of the sampled tokens, expert by expert (only the touched experts are generated)."""
+    router = synth.make_weights(shape, seed, experts=(0, 1))
+    ridx, rw = oracle.route(hidden, router.router_w, router.router_b, shape.top_k)
+    ref = np.zeros((len(sample), shape.hidden), np.float64)
+    for e in sorted(set(ridx[sample].ravel().tolist())):
+        ref += oracle.experts(hidden, ridx, rw, synth.make_weights(shape, seed, experts=(e, e + 1)), tokens=sample, e_lo=e)
+    return ridx, ref
+
+
+def _worker(rank, world, port, case, out_dir):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -33,35 +47,67 @@ def _worker(rank, world, port, T, out_dir):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.cuda.set_device(rank)
-    shape = synth.MoeShape(hidden=2880, inter=2880, n_experts=8, top_k=4)
-    full = synth.make_weights(shape, 31)
-    nl = shape.n_experts // world
-    layer = MoeLayerSystem(shape, full.slice_experts(rank * nl, (rank + 1) * nl), max_tokens=T + world,
-                           device=rank, ep_rank=rank, ep_size=world)
+    E, seed = case["E"], case["seed"]
+    shape = synth.MoeShape(hidden=2880, inter=2880, n_experts=E, top_k=4)
+    nl = E // world
+    mine = synth.make_weights(shape, seed, experts=(rank * nl, (rank + 1) * nl))
+    T = case["T"][rank]
+    layer = MoeLayerSystem(shape, mine, max_tokens=max(T, 1), device=rank, ep_rank=rank, ep_size=world)
     ids = [MoeLayerSystem.ep_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(ids, src=0)
     layer.ep_init(ids[0])
+    if case.get("peer"):                        # both exchanges as the library's own stores into the peers' buffers
+
+        def gather(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+        assert layer.ep_enable_peer_stores(gather), "peer buffers could not be mapped"
     for step in range(2):                       # two passes: buffers are reused
-        hidden = synth.make_hidden(T + rank, full, 31, stream=10 * step + rank)   # ragged T across ranks
+        hidden = synth.make_hidden(T, mine, seed, stream=10 * step + rank)
         h = torch.from_numpy(hidden.view(np.int16)).cuda()
         out, idx, w = layer.run_ep(h, want_routing=True)
         torch.cuda.synchronize()
-        ref, ridx, rw = oracle.moe_forward(hidden, full)
+        sample = np.unique(np.linspace(0, T - 1, min(T, case["sample"])).astype(np.int32))
+        ridx, ref = _oracle_sample(oracle, synth, shape, seed, hidden, sample)
         np.testing.assert_array_equal(idx.cpu().numpy(), ridx)
-        assert_close(out.cpu().numpy(), ref, f"rank {rank} step {step}")
+        assert_close(out.cpu().numpy()[sample], ref, f"rank {rank} step {step}")
         assert layer.status() == 0
+        if case.get("expect_split"):
+            sub = layer._lib.neon_moe_ep_subpasses(layer._h)
+            assert sub > 1, "the rows cannot have fitted one exchange"
     dist.barrier()
     open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     layer.close()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("T", [6, 200])
-def test_two_gpu_expert_parallel_matches_oracle(tmp_path, T):
+CASES = {
+    "ragged_2": dict(world=2, E=8, seed=31, T=[6, 7], sample=8),
+    "ragged_200": dict(world=2, E=8, seed=31, T=[200, 201], sample=12),
+    "e32_up_to_4_ranks": dict(world=4, E=32, seed=5, T=[64, 65, 66, 67], sample=8),
+    "e128_1024_tokens": dict(world=2, E=128, seed=9, T=[1024, 1024], sample=6),
+    # rank 0 has room for 2 * 12 * 4 = 96 rows; rank 1 routes 300 tokens of which about half the entries go to rank 0:
+    # every rank sees the overflow in the gathered histograms and halves its token range until the halves fit
+    "overflow_runs_as_split_passes": dict(world=2, E=8, seed=13, T=[12, 300], sample=10, expect_split=True),
+    # the same exchanges as the library's own stores over NVLink (CUDA IPC mappings of the peers' buffers)
+    "peer_ragged_200": dict(world=2, E=8, seed=31, T=[200, 201], sample=12, peer=True),
+    "peer_e32_up_to_4_ranks": dict(world=4, E=32, seed=5, T=[64, 65, 66, 67], sample=8, peer=True),
+    "peer_e128_1024_tokens": dict(world=2, E=128, seed=9, T=[1024, 1024], sample=6, peer=True),
+    "peer_overflow_runs_as_split_passes": dict(world=2, E=8, seed=13, T=[12, 300], sample=10, expect_split=True, peer=True),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_expert_parallel_matches_oracle(tmp_path, name):
     import torch
     import torch.multiprocessing as mp
-    if torch.cuda.device_count() < 2:
+    case = dict(CASES[name])
+    have = torch.cuda.device_count()
+    if have < 2:
         pytest.skip("needs two GPUs")
-    world = 2
-    mp.spawn(_worker, args=(world, _free_port(), T, str(tmp_path)), nprocs=world, join=True)
+    world = min(case["world"], have if case["E"] % max(have, 1) == 0 else 2)
+    world = 2 if world == 3 else world
+    case["T"] = case["T"][:world]
+    mp.spawn(_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))

@@ -386,6 +386,7 @@ def test_one_launch_decode_pass(full20b, T):
     lb = synth.zipf_logit_bias(shape.n_experts) if T in (4, 8) else None
     hidden = synth.make_hidden(T, W, 70 + T, logit_bias=lb)
     layer.set_option("use_graphs", 0)
+    layer.set_option("decode_fused_tokens", 8)      # by default only single-token passes take the one-launch kernel
     try:
         before = layer.launch_count
         out, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, what=f"one-launch T={T}")
@@ -399,6 +400,7 @@ def test_one_launch_decode_pass(full20b, T):
         assert_close(out, multi, f"one-launch vs multi-kernel T={T}")
     finally:
         layer.set_option("decode_fused", 1)
+        layer.set_option("decode_fused_tokens", 1)
         layer.set_option("use_graphs", 1)
 
 
@@ -409,6 +411,7 @@ def test_one_launch_decode_bounded_wait_reports_and_recovers(full20b):
     shape, W, layer = full20b
     hidden = synth.make_hidden(2, W, 90)
     layer.set_option("use_graphs", 0)
+    layer.set_option("decode_fused_tokens", 8)
     try:
         layer.set_option("decode_wait_limit", 100_000_000)   # ~50 ms of SM clocks
         layer.set_option("decode_stall_test", 1)
@@ -419,6 +422,7 @@ def test_one_launch_decode_bounded_wait_reports_and_recovers(full20b):
         check_against_oracle(layer, W, hidden, what="after a timed-out pass")
     finally:
         layer.set_option("decode_stall_test", 0)
+        layer.set_option("decode_fused_tokens", 1)
         layer.set_option("use_graphs", 1)
 
 

@@ -275,6 +275,10 @@ int neon_moe_read_profile(neon_moe_handle* h, double* ms, int* n_forwards);
 /* Number of kernel launches the handle has issued since creation (for launch accounting). */
 int64_t neon_moe_launch_count(const neon_moe_handle* h);
 
+/* CTAs the paired (two-SM MMA) kernel was last launched with: twice the number of CTA pairs the device can
+ * hold at once (option "pair_mma"); 0 before its first launch. */
+int neon_moe_pair_ctas(const neon_moe_handle* h);
+
 /* Text of the last error on this handle (h == NULL: of this thread's last failed
  * neon_moe_create or neon_moe_forward_static).
  * Owned by the library; valid until the next call on the handle. */
@@ -296,6 +300,15 @@ const char* neon_moe_version(void);
  * floating-point operations.  The measured ceiling of the prefill roofline (no library has one for
  * these instruction kinds); the engine has no counterpart. */
 int neon_moe_mma_rate(int device, int kind, int n, int chunks, double* ms, int64_t* cycles);
+
+/* Self-check of the two-SM form of the block-scaled tensor-core instruction (tcgen05 cta_group::2) that the
+ * paired grouped GEMM uses: a cluster of two CTAs multiplies constant e4m3 operands held in shared memory
+ * (CTA c: A = a_c, its half of the N operand = b_c; a = {1, 0.5}, b = {1, 2}) with `chunks` x 4 accumulating
+ * 256 x n x 32 MMAs issued by the leader CTA.  d32 receives, per CTA, rows {0, 37, 100, 127} x columns
+ * {0, n/2 - 1, n/2, n - 1} of that CTA's accumulator: chunks * 128 * a_c * b_(column half) when M = 256
+ * splits by CTA and N is the concatenation of the two halves.  tmem_addr2: the tensor-memory base each CTA
+ * got; cycles: SM clocks from first issue to completion.  n: 32 or 64.  No engine counterpart. */
+int neon_moe_mma_pair_probe(int device, int n, int chunks, float* d32, uint32_t* tmem_addr2, int64_t* cycles);
 
 #ifdef __cplusplus
 }

@@ -147,15 +147,19 @@ inline void ep_peer_offsets(const int32_t* all_counts, int ep_size, int n_expert
     }
 }
 
-// Token rows to the expert owners: sorted entry p -> its place in the owner's xrecv (16-byte vectors).
-__global__ void scatter_rows_kernel(const uint16_t* __restrict__ hidden, const int32_t* __restrict__ perm, int k, int H, int n,
-                                    PeerRows<uint16_t> t) {
-    const int p = blockIdx.x;
-    if (p >= n) return;
-    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)(perm[p] / k) * H);
-    uint4* dst = reinterpret_cast<uint4*>(peer_row(t, p, H));
-    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
-    __threadfence_system();
+// Token rows to the expert owners: sorted entry p -> its place in the owner's xrecv (16-byte vectors).  A fixed
+// grid of CTAs walks the rows; one system-scope fence per CTA, after a CTA barrier, publishes all of its stores
+// (a fence per thread costs far more than the copy).
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const uint16_t* __restrict__ hidden, const int32_t* __restrict__ perm, int k,
+                                                           int H, int n, PeerRows<uint16_t> t) {
+    const int nvec = H / 8;
+    for (int p = blockIdx.x; p < n; p += gridDim.x) {
+        const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)(perm[p] / k) * H);
+        uint4* dst = reinterpret_cast<uint4*>(peer_row(t, p, H));
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) __threadfence_system();
 }
 
 // xsend[p, :] = hidden[perm[p] / k, :] for the n sorted entries (16-byte vectors).

@@ -1107,7 +1107,10 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);
         }
-        if (!GATE_UP && p.peer.n_ranks) __threadfence_system();  // rows written into other GPUs' buffers: visible before the kernel ends
+        if (!GATE_UP && p.peer.n_ranks) {  // rows written into other GPUs' buffers: published before the kernel ends
+            __syncwarp();
+            if (lane == 0) __threadfence_system();
+        }
     }
 done:
     __syncwarp();

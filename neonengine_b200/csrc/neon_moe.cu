@@ -15,9 +15,11 @@
 
 #include "moe_kernels.cuh"
 #include "gmm_sm100.cuh"
+#include "gmm_pair_sm100.cuh"
 #include "ep.cuh"
 #include "decode_fused.cuh"
 #include "mma_rate.cuh"
+#include "mma_pair.cuh"
 
 using namespace neon;
 
@@ -85,6 +87,8 @@ struct neon_moe_handle {
     float *dec_router_part = nullptr, *dec_gu_part = nullptr, *dec_dn_part = nullptr;
     unsigned* dec_counters = nullptr;
     int dec_gu_items_cap = 0, dec_counter_words = 0;
+    int pair_ctas = 0;            // CTAs the paired kernel was last launched with (2 x resident clusters)
+    int pair_mma = 0;             // decode tiles (16 / 32 tokens): 1 = clusters of two CTAs on two-SM MMAs (tcgen05 cta_group::2)
     int mxf4_prefill = 0;         // 128-token tiles: 1 = activations quantised to MXFP4, tcgen05.mma.kind::mxf4 (outside the accuracy contract)
     int mx4 = 0;                  // decode tiles: 1 = kind::mxf4 with e2m1 activation terms, 0 = kind::mxf8f6f4 with e4m3 terms
     // expert parallelism: source-side routing/dispatch over all experts, exchange buffers
@@ -323,6 +327,20 @@ int make_weight_map(neon_moe_handle* h, CUtensorMap* map, void* base, uint64_t n
     return NEON_MOE_OK;
 }
 
+// 2-D map over the scale atoms of the weight boxes (512 bytes each, as 128 32-bit words): box = one or two atoms.
+int make_atom_map(neon_moe_handle* h, CUtensorMap* map, const void* base, uint64_t n_atoms, uint32_t box_atoms) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {128, n_atoms};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, box_atoms};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(h, NEON_MOE_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return NEON_MOE_OK;
+}
+
 // Upload (when needed) and re-tile one MXFP4 matrix set into the "tc" format.
 int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* scales, int rows, int K, int gate_up,
                    int on_device, uint8_t** wt, uint8_t** sfa, CUtensorMap* map, CUtensorMap* map2, CUtensorMap* map4,
@@ -391,6 +409,46 @@ int launch_gmm_one(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap
     return NEON_MOE_OK;
 }
 
+// The paired kernel for decode tiles (gmm_pair_sm100.cuh): clusters of two CTAs, grid = an even number of CTAs.
+template <int BN, int TERMS, bool GATE_UP>
+int launch_gmm_pair(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMap& tm2, GmmParams p, cudaStream_t st) {
+    using L = PairSmem<BN, TERMS>;
+    static bool configured[kMaxDevicesAttr] = {};
+    auto kern = gmm_pair_kernel<BN, TERMS, GATE_UP>;
+    CUtensorMap ts1, ts2;  // scale atoms, fetched by TMA so that the peer's copies can report to the leader's barrier
+    const uint64_t n_atoms = (uint64_t)h->n_local * p.m_tiles * p.n_chunks;
+    int rc;
+    if ((rc = make_atom_map(h, &ts1, p.sfa, n_atoms, 1)) || (rc = make_atom_map(h, &ts2, p.sfa, n_atoms, 2))) return rc;
+    if (!configured[h->cfg.device]) {
+        CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::smem_bytes(L::kStages)));
+        configured[h->cfg.device] = true;
+    }
+    int stages = L::kStages;
+    if (h->max_stages > 0) stages = std::max(2, std::min(stages, h->max_stages));
+    p.stages = stages;
+    p.tmem_cols = L::tmem_cols(stages);
+    // The kernel is persistent: a pair that cannot be resident with the others would run after them and double the
+    // time.  Pairs need two SMs of one TPC, so fewer than n_sms / 2 may fit: ask the runtime how many do.
+    static int max_pairs[kMaxDevicesAttr] = {};
+    if (!max_pairs[h->cfg.device]) {
+        cudaLaunchConfig_t q{};
+        q.gridDim = dim3(h->n_sms & ~1);
+        q.blockDim = dim3(192);
+        q.dynamicSmemBytes = (size_t)L::smem_bytes(L::kStages);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = h->n_sms / 2;
+        }
+        max_pairs[h->cfg.device] = n;
+    }
+    const int pairs = std::min(max_pairs[h->cfg.device], h->n_sms / 2);
+    launch_k(h->pdl != 0, kern, dim3(2 * pairs), dim3(192), (size_t)L::smem_bytes(stages), st, tm2, tm1, ts2, ts1, p);
+    h->launches++;
+    h->pair_ctas = 2 * pairs;
+    return NEON_MOE_OK;
+}
+
 // e4m3 terms of the fp32 SwiGLU output fed to the down product of 128-token (prefill) tiles.  Each
 // term carries ~4 significant bits; three would already meet the accuracy contract (measured
 // max-abs 3.4e-3 at T=256) but were measured no faster (0.762 vs 0.757 ms at T=4096: that launch is
@@ -406,6 +464,10 @@ int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, cons
         const CUtensorMap& q2 = GATE_UP ? h->tm4_gu2 : h->tm4_dn2;
         if (tile_tokens == 16) return launch_gmm_one<16, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
         return launch_gmm_one<32, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
+    }
+    if (tile_tokens <= 32 && h->pair_mma) {
+        if (tile_tokens == 16) return launch_gmm_pair<16, TERMS, GATE_UP>(h, tm1, tm2, p, st);
+        return launch_gmm_pair<32, TERMS, GATE_UP>(h, tm1, tm2, p, st);
     }
     if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
     if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
@@ -492,9 +554,52 @@ out:
     return rc;
 }
 
+int neon_moe_mma_pair_probe(int device, int n, int chunks, float* d32, uint32_t* tmem_addr2, int64_t* cycles) {
+    if (!d32 || !tmem_addr2 || !cycles || n < 32 || n > 64 || n % 32 || chunks < 1 || chunks > (1 << 16)) return NEON_MOE_EINVAL;  // 128 columns of tensor memory: accumulator + scale atoms
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev || cudaSetDevice(device) != cudaSuccess) {
+        cudaGetLastError();
+        return NEON_MOE_ECUDA;
+    }
+    const size_t smem = 16384 + 16384 + 512 + 1024;
+    MmaPairOut* d_out = nullptr;
+    MmaPairOut host{};
+    int rc = NEON_MOE_ECUDA;
+    if (cudaMalloc(&d_out, sizeof(MmaPairOut)) != cudaSuccess || cudaMemset(d_out, 0, sizeof(MmaPairOut)) != cudaSuccess ||
+        cudaFuncSetAttribute(mma_pair_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(d_out);
+        return rc;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2);       // one CTA pair
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, mma_pair_probe_kernel, n, chunks, d_out) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess &&
+        cudaMemcpy(&host, d_out, sizeof host, cudaMemcpyDeviceToHost) == cudaSuccess) {
+        memcpy(d32, host.d, sizeof host.d);
+        tmem_addr2[0] = host.tmem_addr[0];
+        tmem_addr2[1] = host.tmem_addr[1];
+        *cycles = host.cycles;
+        rc = host.status ? NEON_MOE_EDEVICE : NEON_MOE_OK;
+    }
+    cudaGetLastError();
+    cudaFree(d_out);
+    return rc;
+}
+
 const char* neon_moe_last_error(const neon_moe_handle* h) { return h ? h->err.c_str() : g_create_error.c_str(); }
 
 int64_t neon_moe_launch_count(const neon_moe_handle* h) { return h ? h->launches : 0; }
+
+int neon_moe_pair_ctas(const neon_moe_handle* h) { return h ? h->pair_ctas : 0; }
 
 int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
     if (!cfg || !out) return fail(nullptr, NEON_MOE_EINVAL, "null argument");
@@ -1123,7 +1228,7 @@ static int ep_pass(neon_moe_handle* h, const uint16_t* hidden, int T, const floa
         tx.row_off[G] = n;
         ty.row_off[G] = R;
         if (n > 0) {
-            scatter_rows_kernel<<<n, 128, 0, st>>>(hidden, h->s_perm, k, H, n, tx);
+            scatter_rows_kernel<<<std::min(n, 8 * h->n_sms), 256, 0, st>>>(hidden, h->s_perm, k, H, n, tx);
             h->launches++;
         }
         int rc = rank_barrier();  // every rank's rows have landed before anyone multiplies
@@ -1363,6 +1468,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     } else if (!strcmp(name, "decode_wait_limit")) {
         if (value < 1000) return fail(h, NEON_MOE_EINVAL, "decode_wait_limit is in SM clocks, at least 1000");
         h->decode_wait_limit = (long long)value;
+    } else if (!strcmp(name, "pair_mma")) {
+        h->pair_mma = (int)value;
     } else if (!strcmp(name, "mxf4_prefill")) {
         h->mxf4_prefill = (int)value;
     } else if (!strcmp(name, "mx4")) {

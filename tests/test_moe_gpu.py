@@ -459,3 +459,41 @@ def test_mxf4_prefill_against_the_quantisation_aware_oracle(full20b, capsys):
     assert mean_rel_q <= 5e-3 and frac_over <= 1e-3, (mean_rel_q, frac_over)
     assert mean_rel_plain > 5e-3          # 4-bit activations cannot meet the contract against the unquantised result
     layer.close()
+
+
+@pytest.mark.parametrize("T", [3, 17, 64, 200, 384])
+def test_two_sm_mma_decode_tiles(full20b, T):
+    """Option pair_mma: decode tiles on clusters of two CTAs and two-SM MMAs (tcgen05 cta_group::2).  Same
+    routing, dispatch and - the same products accumulated in the same order - the same output bits as the
+    one-CTA kernel; checked against the oracle as well.  T=3 and 17 leave the second tile of odd tile counts
+    and ragged token tiles to both CTAs of a pair."""
+    shape, W, layer = full20b
+    lb = synth.zipf_logit_bias(shape.n_experts) if T == 64 else None
+    hidden = synth.make_hidden(T, W, 200 + T, logit_bias=lb)
+    toks = None if T <= 64 else np.arange(1, T, 23, dtype=np.int32)
+    layer.set_option("decode_fused", 0)
+    try:
+        ref = run_device(layer, hidden, lb)[0]
+        layer.set_option("pair_mma", 1)
+        out, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, tokens=toks, what=f"pair_mma T={T}")
+        np.testing.assert_array_equal(out, ref)
+    finally:
+        layer.set_option("pair_mma", 0)
+        layer.set_option("decode_fused", 1)
+
+
+def test_two_sm_mma_instruction_self_check():
+    """The library's self-check of the two-SM instruction form: M = 256 splits by CTA, the N operand is the
+    concatenation of the two CTAs' halves, the multicast commit reaches both CTAs (no timeout)."""
+    import ctypes
+    lib = __import__("neonengine_b200._lib", fromlist=["load"]).load()
+    for n, chunks in ((64, 3), (32, 1)):
+        d = np.zeros((2, 4, 4), np.float32)
+        addr = np.zeros(2, np.uint32)
+        cyc = ctypes.c_int64()
+        assert lib.neon_moe_mma_pair_probe(0, n, chunks, d.ctypes.data, addr.ctypes.data, ctypes.byref(cyc)) == 0
+        want = chunks * 128.0 * np.array([1, 1, 2, 2], np.float32)
+        np.testing.assert_array_equal(d[0], np.tile(want, (4, 1)))
+        np.testing.assert_array_equal(d[1], np.tile(0.5 * want, (4, 1)))
+        assert addr[0] == addr[1] and cyc.value > 0
+    assert lib.neon_moe_mma_pair_probe(0, 48, 1, d.ctypes.data, addr.ctypes.data, ctypes.byref(cyc)) == 1

@@ -251,6 +251,13 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * even).  Four-bit activations put the result ~20 % (mean relative) away from the unquantised one - far
  * outside the 2e-2 / 5e-3 contract - so it is an option; it agrees with an oracle that applies the same
  * quantisation to accumulation noise.
+ * "pair_mma" (default 2): decode-sized tiles (16 / 32 tokens) on clusters of two CTAs whose leader issues two-SM
+ * MMAs (tcgen05 cta_group::2, 256 weight rows per instruction): 0 never, 1 always, 2 for passes that route at
+ * most 384 entries (96 tokens at top-4), where it measured 1-5 % faster per pass; results are bit-identical to
+ * the one-CTA kernel's.
+ * "ep_peer" (default 0; expert-parallel handles, after neon_moe_ep_peer_import on every rank): 1 makes both
+ * exchanges of neon_moe_forward_ep this library's own stores into the peers' buffers instead of NCCL
+ * all-to-alls.  Every rank must set the same value.
  * "n_ctas", "ctas_per_sm": grid size of the grouped GEMMs (default: one CTA per SM).
  * Routing is deterministic for a given router kernel, but the three routers (one CTA per token,
  * tensor-core, and the one neon_moe_forward_static uses) add the 2880 products in different

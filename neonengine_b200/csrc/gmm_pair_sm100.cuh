@@ -152,16 +152,45 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     cluster_sync_all();  // both CTAs' barriers, unit atoms and tensor memory exist before anyone signals across
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();
     const int mp_tiles = (p.m_tiles + 1) / 2;            // pairs of weight tiles per expert (the last may be half empty)
-    const int n_items = *p.n_tiles * mp_tiles;
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     constexpr size_t act_stride = kFullActBytes;
     const uint32_t full_leader = mapa_shared(smem_u32(&full[0]), 0);  // the leader's stage barriers (this CTA's own for the leader)
+    // Weight boxes and scale atoms of one stage.  They report to the LEADER's barrier from both CTAs (the long latency,
+    // from HBM); the leader raises that barrier's byte count for both.
+    auto load_weights = [&](int s, int kc, int box_row, uint32_t atom) {
+        uint8_t* st = smem + s * L::kStage;
+        if (leader) {
+            mbar_expect_tx_only(&full[s], kc * (2 * (p.a_tx_bytes + 512)));
+            tma_load_2d(st, kc == 2 ? &tmA : &tmA1, &full[s], 0, box_row);
+            tma_load_2d(st + SFA_OFF, kc == 2 ? &tmS : &tmS1, &full[s], 0, (int)atom);
+        } else {
+            tma_load_2d_pair(st, kc == 2 ? &tmA : &tmA1, full_leader + s * 8, 0, box_row);
+            tma_load_2d_pair(st + SFA_OFF, kc == 2 ? &tmS : &tmS1, full_leader + s * 8, 0, (int)atom);
+        }
+    };
+    // The weights of the first item's first stages do not depend on the predecessor kernel, only on the tile list,
+    // which (p.prefetch) an earlier kernel of the stream completed before this grid could start: fetch them now, so
+    // that the copy from HBM overlaps the predecessor's run.
+    int n_pre = 0;
+    if (warp == 0 && p.prefetch) {
+        const int n_items0 = *reinterpret_cast<const volatile int32_t*>(p.n_tiles) * mp_tiles;
+        if (pair < n_items0) {
+            const int tile = pair / mp_tiles, m = 2 * (pair - tile * mp_tiles) + (int)crank;
+            const int e = reinterpret_cast<const volatile int32_t*>(p.tile_expert)[tile];
+            const uint32_t box = (uint32_t)((e * p.m_tiles + min(m, p.m_tiles - 1)) * p.n_chunks);
+            n_pre = min(STAGES, (p.n_chunks + KC - 1) / KC);
+            if (elect_one())
+                for (int s = 0; s < n_pre; ++s) load_weights(s, min(KC, p.n_chunks - s * KC), (int)(box + s * KC) * 128, box + s * KC);
+            __syncwarp();
+        }
+    }
+    pdl_wait();
+    const int n_items = *p.n_tiles * mp_tiles;
 
     if (warp == 0) {
         // ---- producer (both CTAs): own weight tile + own half of the stacked token rows -------------------
-        int s = 0, ph = 0;
+        int s = 0, ph = 0, g = 0;  // g: stages issued so far (the first n_pre already hold their weights)
         for (int item = pair; item < n_items; item += n_pairs) {
             const int tile = item / mp_tiles, m = 2 * (item - tile * mp_tiles) + (int)crank;
             const int m_ld = min(m, p.m_tiles - 1);  // the absent second tile of an odd count: a duplicate load, never stored
@@ -171,26 +200,20 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int box_row = (int)(box * 128);
             uint32_t atom = box;  // row of the scale-atom tensor (one 512-byte atom per weight box)
             const uint8_t* act_src = p.act + (size_t)tile * p.n_chunks * act_stride + crank * half_bytes;
-            for (int left = p.n_chunks; left > 0; left -= KC) {
+            for (int left = p.n_chunks; left > 0; left -= KC, ++g) {
                 const int kc = left >= KC ? KC : 1;
-                const int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
-                if (!__all_sync(0xffffffffu, ok)) goto done;
+                if (g >= n_pre) {
+                    const int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
+                    if (!__all_sync(0xffffffffu, ok)) goto done;
+                }
                 uint8_t* st = smem + s * L::kStage;
                 if (elect_one()) {
-                    // The weight box and its scale atoms (from HBM, the long latency) report to the LEADER's barrier from both
-                    // CTAs; the token rows (from L2, early) report to a barrier of their own CTA, and the peer forwards its
-                    // "rows landed" to the leader.  The leader arms its barrier for both CTAs' weight bytes.
-                    if (leader) {
-                        mbar_expect_tx(&full[s], kc * (2 * (p.a_tx_bytes + 512) + half_bytes));
-                        for (int k = 0; k < kc; ++k) bulk_load(st + ACT_OFF + k * L::kActBytes, act_src + k * act_stride, half_bytes, &full[s]);
-                        tma_load_2d(st, kc == 2 ? &tmA : &tmA1, &full[s], 0, box_row);
-                        tma_load_2d(st + SFA_OFF, kc == 2 ? &tmS : &tmS1, &full[s], 0, (int)atom);
-                    } else {
-                        mbar_expect_tx(&peer_full[s], kc * half_bytes);
-                        for (int k = 0; k < kc; ++k) bulk_load(st + ACT_OFF + k * L::kActBytes, act_src + k * act_stride, half_bytes, &peer_full[s]);
-                        tma_load_2d_pair(st, kc == 2 ? &tmA : &tmA1, full_leader + s * 8, 0, box_row);
-                        tma_load_2d_pair(st + SFA_OFF, kc == 2 ? &tmS : &tmS1, full_leader + s * 8, 0, (int)atom);
-                    }
+                    if (g >= n_pre) load_weights(s, kc, box_row, atom);
+                    // The token rows (from L2, early) report to a barrier of their own CTA; the leader's is the stage barrier,
+                    // on which this is also the one arrival; the peer's warp 1 forwards its "rows landed" to the leader.
+                    uint64_t* rows_bar = leader ? &full[s] : &peer_full[s];
+                    mbar_expect_tx(rows_bar, kc * half_bytes);
+                    for (int k = 0; k < kc; ++k) bulk_load(st + ACT_OFF + k * L::kActBytes, act_src + k * act_stride, half_bytes, rows_bar);
                 }
                 __syncwarp();
                 box_row += KC * 128;

@@ -88,7 +88,12 @@ struct neon_moe_handle {
     unsigned* dec_counters = nullptr;
     int dec_gu_items_cap = 0, dec_counter_words = 0;
     int pair_ctas = 0;            // CTAs the paired kernel was last launched with (2 x resident clusters)
-    int pair_mma = 0;             // decode tiles (16 / 32 tokens): 1 = clusters of two CTAs on two-SM MMAs (tcgen05 cta_group::2)
+    // Decode tiles (16 / 32 tokens) on clusters of two CTAs with two-SM MMAs (tcgen05 cta_group::2): 0 never, 1 always,
+    // 2 when the pass routes at most kPairMaxEntries entries.  Measured per pass at the gpt-oss shapes, single vs paired
+    // (Zipf / uniform routing): T=8 58.5 vs 56.6 / 79.3 vs 75.6 us, T=16 72.2 vs 68.6 / 94.2 vs 91.0, T=64 107.9 vs 103.1 /
+    // 115.8 vs 112.3, T=96 120.7 vs 118.2 / 118.9 vs 118.0, T=128 131.0 vs 131.3 / 123.6 vs 129.4, T=256 190 vs 193 / 180 vs 194.
+    int pair_mma = 2;
+    int pass_entries = 0;         // routed entries of the pass being launched
     int mxf4_prefill = 0;         // 128-token tiles: 1 = activations quantised to MXFP4, tcgen05.mma.kind::mxf4 (outside the accuracy contract)
     int mx4 = 0;                  // decode tiles: 1 = kind::mxf4 with e2m1 activation terms, 0 = kind::mxf8f6f4 with e4m3 terms
     // expert parallelism: source-side routing/dispatch over all experts, exchange buffers
@@ -454,6 +459,7 @@ int launch_gmm_pair(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMa
 // max-abs 3.4e-3 at T=256) but were measured no faster (0.762 vs 0.757 ms at T=4096: that launch is
 // bound by activation traffic, not by the tensor cores), so four stay for the extra accuracy.
 constexpr int kDownTermsPrefill = 4;
+constexpr int kPairMaxEntries = 96 * 4;  // passes of up to 96 tokens at top-4 take the paired kernel
 constexpr int kMx4Terms = 6;  // e2m1 terms per activation value on the packed 4-bit path
 
 template <int TERMS, bool GATE_UP>
@@ -465,7 +471,7 @@ int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, cons
         if (tile_tokens == 16) return launch_gmm_one<16, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
         return launch_gmm_one<32, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
     }
-    if (tile_tokens <= 32 && h->pair_mma) {
+    if (tile_tokens <= 32 && (h->pair_mma == 1 || (h->pair_mma == 2 && h->pass_entries <= kPairMaxEntries))) {
         if (tile_tokens == 16) return launch_gmm_pair<16, TERMS, GATE_UP>(h, tm1, tm2, p, st);
         return launch_gmm_pair<32, TERMS, GATE_UP>(h, tm1, tm2, p, st);
     }
@@ -785,6 +791,8 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         launch_split<2, true>(h, tt, tl, hidden, H, n, k_eff, hidden_amax, 0.f, h->x_act, h->x_scale, st);
         DBG_SYNC(h, st, "split_rows (hidden)");
         GmmParams g{};
+        h->pass_entries = n;
+        g.prefetch = tt <= 32 && !h->mx4;  // the stacked split of the hidden rows precedes: it waits before it lets successors start
         g.a_tx_bytes = h->a_tx_bytes;
 #ifdef NEON_MOE_INSTRUMENT
         g.trace = h->trace_which == 2 ? nullptr : h->trace;
@@ -1469,6 +1477,7 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         if (value < 1000) return fail(h, NEON_MOE_EINVAL, "decode_wait_limit is in SM clocks, at least 1000");
         h->decode_wait_limit = (long long)value;
     } else if (!strcmp(name, "pair_mma")) {
+        if (value < 0 || value > 2) return fail(h, NEON_MOE_EINVAL, "pair_mma is 0 (never), 1 (always) or 2 (small passes)");
         h->pair_mma = (int)value;
     } else if (!strcmp(name, "mxf4_prefill")) {
         h->mxf4_prefill = (int)value;

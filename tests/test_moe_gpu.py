@@ -472,13 +472,14 @@ def test_two_sm_mma_decode_tiles(full20b, T):
     hidden = synth.make_hidden(T, W, 200 + T, logit_bias=lb)
     toks = None if T <= 64 else np.arange(1, T, 23, dtype=np.int32)
     layer.set_option("decode_fused", 0)
+    layer.set_option("pair_mma", 0)
     try:
         ref = run_device(layer, hidden, lb)[0]
         layer.set_option("pair_mma", 1)
         out, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, tokens=toks, what=f"pair_mma T={T}")
         np.testing.assert_array_equal(out, ref)
     finally:
-        layer.set_option("pair_mma", 0)
+        layer.set_option("pair_mma", 2)
         layer.set_option("decode_fused", 1)
 
 

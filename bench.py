@@ -1048,10 +1048,12 @@ def moe_roofline(run, step_s, stage_ms, n_prof, peaks, peak_kind, traffic_table)
         gu_ms = stage_ms["gate_up"]
         gu_bytes = mean_touched * gu_expert_bytes + T * H * 2 + T * k * I * 4
         achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peaks["hbm_gbs"],
+        # passes of up to 96 tokens run the grouped GEMM on CTA pairs (two-SM MMAs), larger ones on single CTAs
+        kern = "gmm_pair_kernel" if run.layer.pair_ctas() > 0 else "gmm_bs_kernel"
+        roof = {"bound": "hbm", "kernel": kern + "<gate_up>", "achieved": achieved, "peak": peaks["hbm_gbs"],
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
                 "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gu_ms}
-        ent = traffic_table.get(("gmm_bs_kernel_gate_up", run.workload))
+        ent = traffic_table.get((kern + "_gate_up", run.workload))
         if ent:   # ncu capture of one launch, scaled by the experts this run touched
             roof["traffic"] = ent["bytes"] * mean_touched / ent["units"]
             roof["traffic_source"] = f"ncu capture at commit {ent['commit']} ({ent['bytes']:.0f} B at {ent['units']:.0f} experts touched), scaled"

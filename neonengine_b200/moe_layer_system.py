@@ -230,6 +230,10 @@ class MoeLayerSystem:
     def launch_count(self) -> int:
         return int(self._lib.neon_moe_launch_count(self._h))
 
+    def pair_ctas(self) -> int:
+        """CTAs the paired (two-SM MMA) grouped GEMM was last launched with; 0 if it has not run."""
+        return int(self._lib.neon_moe_pair_ctas(self._h))
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             self._lib.neon_moe_destroy(self._h)

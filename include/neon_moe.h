@@ -243,6 +243,9 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * tokens (and top_k * T <= 32) run as ONE cooperative kernel - router, both expert products, SwiGLU and
  * combine, no dispatch pass; its CTAs wait for one another with bounded waits (status word on a timeout).
  * Measured at the gpt-oss-20b shapes it wins for single-token passes and loses above, hence the default.
+ * "decode_sliced" (default 0): 1 runs one-launch passes of up to 4 tokens on the variant that slices the layer by
+ * intermediate channel (each CTA computes 128 channels of one expert through both products, one grid-wide
+ * barrier, no partial sums between the products); measured no faster (T = 1: 36.3 vs 35.1-36.5 us).
  * "decode_wait_limit": SM clocks such a wait may take (default 4e8).  "decode_stall_test": 1 makes the
  * kernel's first wait expect a signal nobody sends, so that the bounded wait can be tested without
  * faulting the GPU.
@@ -301,12 +304,23 @@ const char* neon_moe_version(void);
 /* Measures the issue rate of the block-scaled tensor-core instruction the grouped GEMM uses, with
  * the operands resident in shared memory (no global traffic): every SM issues `chunks` groups of
  * accumulating 128 x n MMAs (kind 0: tcgen05.mma.kind::mxf8f6f4, 4 instructions of K = 32 per group;
- * kind 1: kind::mxf4, 2 instructions of K = 64 per group) back to back.  n: 16..256, multiple of 16.
+ * kind 1: kind::mxf4, 2 instructions of K = 64 per group) back to back; kinds 2 and 3 are kinds 0 and 1
+ * with one scale-atom copy (tcgen05.cp) before every group, as the decode kernels issue them.
+ * n: 16..256, multiple of 16.
  * ms receives the duration of the launch (CUDA events), cycles the SM clocks one SM needed from the
  * first issue to the completion of the last instruction.  Work per SM = chunks * 2 * 128 * n * 128
  * floating-point operations.  The measured ceiling of the prefill roofline (no library has one for
  * these instruction kinds); the engine has no counterpart. */
 int neon_moe_mma_rate(int device, int kind, int n, int chunks, double* ms, int64_t* cycles);
+
+/* Measures the rate at which one SM's TMA unit brings weight boxes into shared memory: every SM keeps `stages`
+ * loads of two 128 x 128 four-bit boxes (16 KB of global memory) in flight, `loads` loads in all, with no
+ * consumer.  packed 0: the expanding map the kind::mxf8f6f4 kernels use (one byte per nibble plus padding: 32 KB
+ * land in shared memory; stages <= 6); packed 1: nibbles stay packed (kind::mxf4; stages <= 8).  The boxes come
+ * from a buffer of buffer_bytes (>= 1 MiB) that the SMs walk round-robin: a few MiB stay in L2, several hundred
+ * stream from HBM.  ms receives the launch duration, cycles the SM clocks CTA 0 needed.  Bytes per SM = loads *
+ * 16384.  The engine has no counterpart. */
+int neon_moe_tma_rate(int device, int packed, int stages, int64_t buffer_bytes, int loads, double* ms, int64_t* cycles);
 
 /* Self-check of the two-SM form of the block-scaled tensor-core instruction (tcgen05 cta_group::2) that the
  * paired grouped GEMM uses: a cluster of two CTAs multiplies constant e4m3 operands held in shared memory

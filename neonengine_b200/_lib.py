@@ -139,6 +139,8 @@ SIGNATURES = {
     "neon_moe_profile": (c_int, [c_void_p, c_int]),
     "neon_moe_read_profile": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
     "neon_moe_pair_ctas": (c_int, [c_void_p]),
+    "neon_moe_tma_rate": (c_int, [c_int, c_int, c_int, ctypes.c_int64, c_int, ctypes.POINTER(ctypes.c_double),
+                                  ctypes.POINTER(ctypes.c_int64)]),
     "neon_moe_launch_count": (ctypes.c_int64, [c_void_p]),
     "neon_moe_last_error": (ctypes.c_char_p, [c_void_p]),
     "neon_moe_destroy": (c_int, [c_void_p]),

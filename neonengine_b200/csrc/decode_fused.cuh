@@ -300,6 +300,192 @@ __device__ __forceinline__ void dec_topk_warp(const float* lgt, int E, int k, in
     }
 }
 
+// One share of the router: the dot products of one K slice of one expert's router row with every token, by one
+// warp (one 16-byte load per lane and token); the share goes to router_part and is counted in *router_count.
+__device__ __forceinline__ void dec_router_share(const DecodeParams& p, int unit, int lane, unsigned* router_count) {
+    const int T = p.T, H = p.H, E = p.E;
+    if (unit < E * p.n_slices) {
+        const int nvec = H / 8;
+        const int e = unit % E, sl = unit / E;
+        const int vps = (nvec + p.n_slices - 1) / p.n_slices, v0 = sl * vps, v1 = min(nvec, v0 + vps);
+        float acc[kDecMaxTok];
+#pragma unroll
+        for (int t = 0; t < kDecMaxTok; ++t) acc[t] = 0.f;
+        const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * H);
+        for (int vb = v0; vb < v1; vb += 32) {
+            const int v = vb + lane;
+            const uint4 wv = v < v1 ? __ldg(wrow + v) : make_uint4(0, 0, 0, 0);
+            uint4 xv[kDecMaxTok];
+#pragma unroll
+            for (int t = 0; t < kDecMaxTok; ++t)
+                xv[t] = (t < T && v < v1) ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * H) + v) : make_uint4(0, 0, 0, 0);
+            const uint32_t wa[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int t = 0; t < kDecMaxTok; ++t) {
+                const uint32_t xa[4] = {xv[t].x, xv[t].y, xv[t].z, xv[t].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[t] = fmaf(__uint_as_float(xa[j] << 16), __uint_as_float(wa[j] << 16), acc[t]);
+                    acc[t] = fmaf(__uint_as_float(xa[j] & 0xffff0000u), __uint_as_float(wa[j] & 0xffff0000u), acc[t]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kDecMaxTok; ++t) {
+            if (t < T) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+                if (lane == 0) __stcg(p.router_part + ((size_t)t * E + e) * kDecMaxSlices + sl, acc[t]);
+            }
+        }
+        if (lane == 0) red_release_add(router_count, 1u);
+        __syncwarp();
+    }
+}
+
+// Builder warps (kDecBuilderThreads threads, bt = index among them): every token's largest magnitude, then the gate_up
+// token-operand tiles of ALL tokens (two e4m3 terms, 8 token rows per term, one 2 KB tile of stride `TILE` per K chunk;
+// the same for every expert).  Ends with the tiles written (the caller fences them for the async proxy).
+__device__ __forceinline__ void dec_build_x_tiles(const DecodeParams& p, uint8_t* cache, int TILE, unsigned* s_amax, int bt, int lane) {
+    const int T = p.T, H = p.H;
+    const int nvec = H / 8;
+    for (int t = 0; t < T; ++t) {
+        unsigned m = 0u;
+        const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)t * H);
+        for (int v = bt; v < nvec; v += kDecBuilderThreads) {
+            const uint4 xv = __ldg(xr + v);
+            const uint32_t a[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m = max(m, max(a[j] & 0x7fffu, (a[j] >> 16) & 0x7fffu));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0 && m) atomicMax(&s_amax[t], m);
+    }
+    named_bar_sync(2, kDecBuilderThreads);
+    // real tasks (chunk c, token t < T, 16-byte unit u) spread evenly over the builder threads, then zero rows
+    for (int task = bt; task < p.nch_h * T * 8; task += kDecBuilderThreads) {
+        const int u = task & 7, t = (task >> 3) % T, c = (task >> 3) / T;
+        uint8_t* tile = cache + c * TILE;
+        const int kk = 128 * c + 16 * u;
+        if (kk < H) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)t * H + kk);
+            const uint4 r0 = __ldg(src), r1 = __ldg(src + 1);
+            const uint32_t raw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+            float v[16];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                v[2 * x] = __uint_as_float(raw[x] << 16);
+                v[2 * x + 1] = __uint_as_float(raw[x] & 0xffff0000u);
+            }
+            store_terms16<2>(tile, 8, t, u, v, term_scale_byte(__uint_as_float(s_amax[t] << 16), 2));
+        } else {
+            store_zero16<2>(tile, 8, t, u);
+        }
+    }
+    for (int task = bt; task < p.nch_h * (8 - T) * 8; task += kDecBuilderThreads) {
+        const int u = task & 7, t = T + (task >> 3) % (8 - T), c = (task >> 3) / (8 - T);
+        store_zero16<2>(cache + c * TILE, 8, t, u);
+    }
+}
+
+// Routing tables of a pass in shared memory.
+struct DecTables {
+    int* idx;        // [32] expert of every entry
+    float* w;        // [32] routing weight of every entry
+    int* ent_es;     // [32] expert slot of every entry
+    int* ent_j;      // [32] row of the entry inside its expert
+    int* exp;        // [32] expert id of every slot (ascending)
+    int* ntok;       // [32] tokens of every slot
+    int* tok;        // [32][8] token of every row
+    float* lg;       // [8][E] logits
+    int* misc;       // [0] number of distinct experts
+};
+
+// The four epilogue warps (q4 = 0..3, meeting at named barrier 1): wait until every router share of this pass has been
+// counted, add the slices, top k and softmax per token, then the tables of distinct experts and their tokens.  CTA 0 also
+// writes the routing and the dispatch permutation to global memory.  On a timeout the abort flag is set and the tables
+// are left unwritten.
+__device__ __forceinline__ void dec_route(const DecodeParams& p, const DecTables& tb, int q4, int lane, int cta, unsigned pass,
+                                          unsigned* router_count, volatile int* abort_flag) {
+    const int T = p.T, E = p.E, k = p.k, n_ent = T * k;
+    int* const s_idx = tb.idx; float* const s_w = tb.w; int* const s_ent_es = tb.ent_es; int* const s_ent_j = tb.ent_j;
+    int* const s_exp = tb.exp; int* const s_ntok = tb.ntok; int* const s_tok = tb.tok; float* const s_lg = tb.lg;
+    int* const s_misc = tb.misc;
+    {
+        // the router counter is never reset: after this pass's n_router shares it stands at pass * n_router
+        // (mod 2^32).  One lane per CTA polls it; the other warps wait at the named barrier.
+        if (q4 == 0) {
+            const unsigned target = pass * (unsigned)(E * p.n_slices) + p.router_expected_extra;
+            if (lane == 0) {
+                const long long t0 = clock64();
+                while ((int)(ld_acquire_u32(router_count) - target) < 0) {
+                    if (*abort_flag || clock64() - t0 > p.wait_limit) {
+                        *abort_flag = 1;
+                        atomicCAS(p.status, 0, 7);
+                        break;
+                    }
+                }
+            }
+            __syncwarp();
+        }
+        named_bar_sync(1, 128);
+        const int ok = !*abort_flag;
+        if (ok) {
+            for (int t = q4; t < T; t += 4) {  // logits, top k, softmax: every CTA, identically
+                for (int e = lane; e < E; e += 32) {
+                    // all sixteen slice slots in four loads (slots beyond n_slices stay zero from set-up), added in order
+                    const float4* part = reinterpret_cast<const float4*>(p.router_part + ((size_t)t * E + e) * kDecMaxSlices);
+                    const float4 a = __ldcg(part), b = __ldcg(part + 1), c = __ldcg(part + 2), d = __ldcg(part + 3);
+                    float v = ((((((a.x + a.y) + a.z) + a.w) + b.x) + b.y) + b.z) + b.w;
+                    v = (((((((v + c.x) + c.y) + c.z) + c.w) + d.x) + d.y) + d.z) + d.w;
+                    v += bf16_bits_to_float(p.br[e]);
+                    if (p.logit_bias) v += p.logit_bias[e];
+                    s_lg[t * E + e] = v;
+                }
+                __syncwarp();
+                dec_topk_warp(s_lg + t * E, E, k, lane, s_idx + t * k, s_w + t * k);
+            }
+        }
+    }
+    named_bar_sync(1, 128);
+    if (q4 == 0 && lane == 0) DEC_STAMP(3);
+    if (q4 == 0 && !*abort_flag) {
+        // one entry (token, slot) per lane: slot of its expert among the distinct experts (ascending
+        // id), its row among that expert's tokens (ascending token), its place in the sorted order
+        const int e = lane < n_ent ? s_idx[lane] : -1 - lane;  // idle lanes get unique negative keys
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const bool first = lane < n_ent && (__ffs(peers) - 1) == lane;
+        const int j_row = __popc(peers & ((1u << lane) - 1u));
+        int es = 0, pos = j_row;
+        for (int o = 0; o < n_ent; ++o) {
+            const int eo = __shfl_sync(0xffffffffu, e, o);
+            const bool fo = __shfl_sync(0xffffffffu, (int)first, o) != 0;
+            if (eo < e) {
+                ++pos;
+                if (fo) ++es;
+            }
+        }
+        if (lane < n_ent) {
+            s_ent_es[lane] = es;
+            s_ent_j[lane] = j_row;
+            s_tok[es * 8 + j_row] = lane / k;
+            if (first) {
+                s_exp[es] = e;
+                s_ntok[es] = __popc(peers);
+            }
+            if (cta == 0) {
+                p.idx[lane] = e;
+                p.route_w[lane] = s_w[lane];
+                p.d.perm[pos] = lane;
+                p.d.inv[lane] = pos;
+            }
+        }
+        const unsigned firsts = __ballot_sync(0xffffffffu, first);
+        if (lane == 0) s_misc[0] = __popc(firsts);
+    }
+}
+
 __global__ void __launch_bounds__(kDecThreads, 1)
 decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_constant__ CUtensorMap tmGU2,
                     const __grid_constant__ CUtensorMap tmDN, const __grid_constant__ CUtensorMap tmDN2, const DecodeParams p) {
@@ -349,44 +535,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
     // ---- router shares first, before anything else is set up: they need no shared memory, and every CTA waits for them.
     //      Unit u = (expert, K slice) is computed by warp 3 + u % 3 of CTA u / 3: one 16-byte load per lane and token.
     if (warp >= 3 && warp < 3 + kDecRouterWarps) {
-        const int unit = cta * kDecRouterWarps + (warp - 3);
-        if (unit < E * p.n_slices) {
-            const int nvec = H / 8;
-            const int e = unit % E, sl = unit / E;
-            const int vps = (nvec + p.n_slices - 1) / p.n_slices, v0 = sl * vps, v1 = min(nvec, v0 + vps);
-            float acc[kDecMaxTok];
-#pragma unroll
-            for (int t = 0; t < kDecMaxTok; ++t) acc[t] = 0.f;
-            const uint4* wrow = reinterpret_cast<const uint4*>(p.wr + (size_t)e * H);
-            for (int vb = v0; vb < v1; vb += 32) {
-                const int v = vb + lane;
-                const uint4 wv = v < v1 ? __ldg(wrow + v) : make_uint4(0, 0, 0, 0);
-                uint4 xv[kDecMaxTok];
-#pragma unroll
-                for (int t = 0; t < kDecMaxTok; ++t)
-                    xv[t] = (t < T && v < v1) ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)t * H) + v) : make_uint4(0, 0, 0, 0);
-                const uint32_t wa[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-                for (int t = 0; t < kDecMaxTok; ++t) {
-                    const uint32_t xa[4] = {xv[t].x, xv[t].y, xv[t].z, xv[t].w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        acc[t] = fmaf(__uint_as_float(xa[j] << 16), __uint_as_float(wa[j] << 16), acc[t]);
-                        acc[t] = fmaf(__uint_as_float(xa[j] & 0xffff0000u), __uint_as_float(wa[j] & 0xffff0000u), acc[t]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < kDecMaxTok; ++t) {
-                if (t < T) {
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
-                    if (lane == 0) __stcg(p.router_part + ((size_t)t * E + e) * kDecMaxSlices + sl, acc[t]);
-                }
-            }
-            if (lane == 0) red_release_add(router_count, 1u);
-            __syncwarp();
-        }
+        dec_router_share(p, cta * kDecRouterWarps + (warp - 3), lane, router_count);
         if (warp == 3 && lane == 0) DEC_STAMP(2);
     }
 
@@ -423,122 +572,14 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmGU, const __grid_const
         // ---- builders, first job: token maxima, then the gate_up token-operand tiles of ALL tokens (the
         //      same for every expert), while the epilogue warps route
         const int bt = tid - 192;
-        const int nvec = H / 8;
-        for (int t = 0; t < T; ++t) {
-            unsigned m = 0u;
-            const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)t * H);
-            for (int v = bt; v < nvec; v += kDecBuilderThreads) {
-                const uint4 xv = __ldg(xr + v);
-                const uint32_t a[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) m = max(m, max(a[j] & 0x7fffu, (a[j] >> 16) & 0x7fffu));
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if (lane == 0 && m) atomicMax(&s_amax[t], m);
-        }
-        named_bar_sync(2, kDecBuilderThreads);
-        // real tasks (chunk c, token t < T, 16-byte unit u) spread evenly over the builder threads, then zero rows
-        for (int task = bt; task < p.nch_h * T * 8; task += kDecBuilderThreads) {
-            const int u = task & 7, t = (task >> 3) % T, c = (task >> 3) / T;
-            uint8_t* tile = cache + c * TILE;
-            const int kk = 128 * c + 16 * u;
-            if (kk < H) {
-                const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)t * H + kk);
-                const uint4 r0 = __ldg(src), r1 = __ldg(src + 1);
-                const uint32_t raw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-                float v[16];
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    v[2 * x] = __uint_as_float(raw[x] << 16);
-                    v[2 * x + 1] = __uint_as_float(raw[x] & 0xffff0000u);
-                }
-                store_terms16<2>(tile, 8, t, u, v, term_scale_byte(__uint_as_float(s_amax[t] << 16), 2));
-            } else {
-                store_zero16<2>(tile, 8, t, u);
-            }
-        }
-        for (int task = bt; task < p.nch_h * (8 - T) * 8; task += kDecBuilderThreads) {
-            const int u = task & 7, t = T + (task >> 3) % (8 - T), c = (task >> 3) / (8 - T);
-            store_zero16<2>(cache + c * TILE, 8, t, u);
-        }
+        dec_build_x_tiles(p, cache, TILE, s_amax, bt, lane);
         fence_proxy_async();
         if (bt == 0) DEC_STAMP(9);
     } else if (warp >= 2) {
         // ---- epilogue warps, first job: the router --------------------------------------------------------
         const int q4 = warp - 2;
-        {
-            // the router counter is never reset: after this pass's n_router shares it stands at pass * n_router
-            // (mod 2^32).  One lane per CTA polls it; the other warps wait at the named barrier.
-            if (q4 == 0) {
-                const unsigned target = pass * (unsigned)(E * p.n_slices) + p.router_expected_extra;
-                if (lane == 0) {
-                    const long long t0 = clock64();
-                    while ((int)(ld_acquire_u32(router_count) - target) < 0) {
-                        if (*abort_flag || clock64() - t0 > p.wait_limit) {
-                            *abort_flag = 1;
-                            atomicCAS(p.status, 0, 7);
-                            break;
-                        }
-                    }
-                }
-                __syncwarp();
-            }
-            named_bar_sync(1, 128);
-            const int ok = !*abort_flag;
-            if (ok) {
-                for (int t = q4; t < T; t += 4) {  // logits, top k, softmax: every CTA, identically
-                    for (int e = lane; e < E; e += 32) {
-                        // all sixteen slice slots in four loads (slots beyond n_slices stay zero from set-up), added in order
-                        const float4* part = reinterpret_cast<const float4*>(p.router_part + ((size_t)t * E + e) * kDecMaxSlices);
-                        const float4 a = __ldcg(part), b = __ldcg(part + 1), c = __ldcg(part + 2), d = __ldcg(part + 3);
-                        float v = ((((((a.x + a.y) + a.z) + a.w) + b.x) + b.y) + b.z) + b.w;
-                        v = (((((((v + c.x) + c.y) + c.z) + c.w) + d.x) + d.y) + d.z) + d.w;
-                        v += bf16_bits_to_float(p.br[e]);
-                        if (p.logit_bias) v += p.logit_bias[e];
-                        s_lg[t * E + e] = v;
-                    }
-                    __syncwarp();
-                    dec_topk_warp(s_lg + t * E, E, k, lane, s_idx + t * k, s_w + t * k);
-                }
-            }
-        }
-        named_bar_sync(1, 128);
-        if (q4 == 0 && lane == 0) DEC_STAMP(3);
-        if (q4 == 0 && !*abort_flag) {
-            // one entry (token, slot) per lane: slot of its expert among the distinct experts (ascending
-            // id), its row among that expert's tokens (ascending token), its place in the sorted order
-            const int e = lane < n_ent ? s_idx[lane] : -1 - lane;  // idle lanes get unique negative keys
-            const unsigned peers = __match_any_sync(0xffffffffu, e);
-            const bool first = lane < n_ent && (__ffs(peers) - 1) == lane;
-            const int j_row = __popc(peers & ((1u << lane) - 1u));
-            int es = 0, pos = j_row;
-            for (int o = 0; o < n_ent; ++o) {
-                const int eo = __shfl_sync(0xffffffffu, e, o);
-                const bool fo = __shfl_sync(0xffffffffu, (int)first, o) != 0;
-                if (eo < e) {
-                    ++pos;
-                    if (fo) ++es;
-                }
-            }
-            if (lane < n_ent) {
-                s_ent_es[lane] = es;
-                s_ent_j[lane] = j_row;
-                s_tok[es * 8 + j_row] = lane / k;
-                if (first) {
-                    s_exp[es] = e;
-                    s_ntok[es] = __popc(peers);
-                }
-                if (cta == 0) {
-                    p.idx[lane] = e;
-                    p.route_w[lane] = s_w[lane];
-                    p.d.perm[pos] = lane;
-                    p.d.inv[lane] = pos;
-                }
-            }
-            const unsigned firsts = __ballot_sync(0xffffffffu, first);
-            if (lane == 0) s_misc[0] = __popc(firsts);
-        }
+        const DecTables tb{s_idx, s_w, s_ent_es, s_ent_j, s_exp, s_ntok, s_tok, s_lg, s_misc};
+        dec_route(p, tb, q4, lane, cta, pass, router_count, abort_flag);
     }
     __syncthreads();  // routing tables and the gate_up token-operand tiles are in shared memory
     if (tid == 0) DEC_STAMP(4);

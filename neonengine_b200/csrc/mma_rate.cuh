@@ -18,7 +18,7 @@ struct MmaRateOut {
 };
 
 template <bool MX4>
-__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int n, int chunks, MmaRateOut* out) {
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int n, int chunks, int sf_per_chunk, MmaRateOut* out) {
     using namespace sm100;
     extern __shared__ __align__(1024) uint8_t rate_smem[];
     __shared__ uint64_t done_bar;
@@ -54,17 +54,21 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int n, int chunks, Mma
             t0 = clock64();
             if (MX4) {
                 const uint64_t a4 = make_sw64_desc(sb + kA), b4 = make_sw64_desc(sb + kB);
-                for (int c = 0; c < chunks; ++c)
+                for (int c = 0; c < chunks; ++c) {
+                    if (sf_per_chunk) tc_copy_sf(sf_a, make_sf_desc(sb + kSF));  // as the GEMMs do: one weight scale atom per K = 128
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
                         mma_mxf4(tmem_base, a4 + 2 * j, b4 + 2 * j, idesc0 + j * (2u << 29), sf_a, sf_b, (uint32_t)(c | j));
+                }
             } else {
                 const uint64_t a_desc = make_sw128_desc(sb + kA), b_desc = make_sw128_desc(sb + kB);
-                for (int c = 0; c < chunks; ++c)
+                for (int c = 0; c < chunks; ++c) {
+                    if (sf_per_chunk) tc_copy_sf(sf_a, make_sf_desc(sb + kSF));
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         mma_mxf8f6f4(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc0 + j * (1u << 29), sf_a, sf_b,
                                      (uint32_t)(c | j));
+                }
             }
             tc_commit(&done_bar);
         }
@@ -90,6 +94,54 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int n, int chunks, Mma
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+// Copy-rate measurement of the weight stream into one SM's shared memory: one CTA per SM, one thread keeps
+// `stages` TMA loads of two weight boxes (256 rows x 128 four-bit columns = 16 KB in global memory) in flight,
+// each into its own stage, and reissues a stage as soon as its copy has landed.  No consumer.  With the
+// 16U4_ALIGN16B map the nibbles are expanded on the way (32 KB land in shared memory), with the packed map 16 KB.
+// CTA b reads boxes b, b + grid, ... of a buffer of n_pairs box pairs, wrapping around: a small buffer stays in L2,
+// a large one streams from HBM.
+struct TmaRateOut {
+    long long cycles;   // SM clocks CTA 0 needed for its `loads` copies
+    int status;
+};
+
+__global__ void __launch_bounds__(32, 1) tma_rate_kernel(const __grid_constant__ CUtensorMap tm, int n_pairs, int loads, int stages,
+                                                         uint32_t tx_bytes, int stage_bytes, TmaRateOut* out) {
+    using namespace sm100;
+    extern __shared__ __align__(1024) uint8_t rate_smem[];
+    __shared__ uint64_t full[8];
+    __shared__ int abort_flag, wait_status;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(rate_smem) + 1023) & ~uintptr_t(1023));
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+        abort_flag = 0;
+        wait_status = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tm);
+    }
+    fence_proxy_async();
+    __syncwarp();
+    const long long t0 = clock64();
+    bool ok = true;
+    int pair = blockIdx.x % n_pairs;
+    for (int i = 0; i < loads + stages && ok; ++i) {
+        const int s = i % stages;
+        if (i >= stages) ok = mbar_wait(&full[s], ((i / stages) - 1) & 1, &abort_flag, &wait_status, 1, 2000000000ll);  // the copy issued `stages` ago
+        if (ok && i < loads && elect_one()) {
+            mbar_expect_tx(&full[s], tx_bytes);
+            tma_load_2d(base + (size_t)s * stage_bytes, &tm, &full[s], 0, pair * 256);
+        }
+        __syncwarp();
+        pair += gridDim.x;
+        while (pair >= n_pairs) pair -= n_pairs;
+    }
+    const long long t1 = clock64();
+    if (threadIdx.x == 0) {
+        if (blockIdx.x == 0) out->cycles = t1 - t0;
+        if (!ok) out->status = 1;
+    }
 }
 
 }  // namespace neon

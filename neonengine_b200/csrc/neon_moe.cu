@@ -18,6 +18,7 @@
 #include "gmm_pair_sm100.cuh"
 #include "ep.cuh"
 #include "decode_fused.cuh"
+#include "decode_sliced.cuh"
 #include "mma_rate.cuh"
 #include "mma_pair.cuh"
 
@@ -77,6 +78,7 @@ struct neon_moe_handle {
     CUtensorMap tm_gu{}, tm_dn{}, tm_gu2{}, tm_dn2{};  // weight boxes of 128 rows and of 256 rows (two chunks)
     CUtensorMap tm4_gu{}, tm4_dn{}, tm4_gu2{}, tm4_dn2{};  // the same boxes left packed (4-bit in shared memory)
     // one-launch decode pass (T <= 8): router partial sums, partial sums of both products, counters
+    int decode_sliced = 0;        // 1 = the one-launch pass runs sliced by intermediate channel (decode_sliced.cuh) where it can; measured no faster
     int decode_fused = 1;         // 1 = passes of at most decode_fused_tokens tokens run as one cooperative kernel
     int decode_max_tokens = 0;    // largest pass the one-launch kernel can serve on this handle (0 = not available)
     int decode_fused_tokens = 1;  // largest pass it serves by default: measured per pass at the gpt-oss-20b shapes, one launch vs
@@ -85,6 +87,8 @@ struct neon_moe_handle {
     int decode_stall_test = 0;    // test hook: the kernel's first wait expects one arrival too many and must time out
     long long decode_wait_limit = kWaitLimitCycles;
     float *dec_router_part = nullptr, *dec_gu_part = nullptr, *dec_dn_part = nullptr;
+    float* dec_y_part = nullptr;  // decode_sliced_kernel: [CTA][token][padded hidden] contributions to the output
+    int dec_sliced_tokens = 0;    // largest pass decode_sliced_kernel can take (0: unavailable)
     unsigned* dec_counters = nullptr;
     int dec_gu_items_cap = 0, dec_counter_words = 0;
     int pair_ctas = 0;            // CTAs the paired kernel was last launched with (2 x resident clusters)
@@ -202,7 +206,7 @@ void free_all(neon_moe_handle* h) {
                     h->x_act, h->a_act, h->x_scale, h->x_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
                     h->n_tiles, h->row_tile, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
                     h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv,
-                    h->dec_router_part, h->dec_gu_part, h->dec_dn_part, h->dec_counters, h->ep_bar_src, h->ep_bar_dst};
+                    h->dec_router_part, h->dec_gu_part, h->dec_dn_part, h->dec_y_part, h->dec_counters, h->ep_bar_src, h->ep_bar_dst};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     for (int r = 0; r < kMaxPeerRanks; ++r)
@@ -459,6 +463,7 @@ int launch_gmm_pair(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMa
 // max-abs 3.4e-3 at T=256) but were measured no faster (0.762 vs 0.757 ms at T=4096: that launch is
 // bound by activation traffic, not by the tensor cores), so four stay for the extra accuracy.
 constexpr int kDownTermsPrefill = 4;
+constexpr int kDecodeSmemBytes = 227 * 1024;  // everything an SM has: what the token-operand tiles leave goes to weight stages
 constexpr int kPairMaxEntries = 96 * 4;  // passes of up to 96 tokens at top-4 take the paired kernel
 constexpr int kMx4Terms = 6;  // e2m1 terms per activation value on the packed 4-bit path
 
@@ -520,7 +525,7 @@ extern "C" {
 const char* neon_moe_version(void) { return "neon_moe 0.1 (sm_100a)"; }
 
 int neon_moe_mma_rate(int device, int kind, int n, int chunks, double* ms, int64_t* cycles) {
-    if (!ms || !cycles || (kind != 0 && kind != 1) || n < 16 || n > 256 || n % 16 || chunks < 1 || chunks > (1 << 20))
+    if (!ms || !cycles || kind < 0 || kind > 3 || n < 16 || n > 256 || n % 16 || chunks < 1 || chunks > (1 << 20))
         return NEON_MOE_EINVAL;
     int n_dev = 0, sms = 0;
     if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev || cudaSetDevice(device) != cudaSuccess ||
@@ -541,8 +546,8 @@ int neon_moe_mma_rate(int device, int kind, int n, int chunks, double* ms, int64
         goto out;
     for (int rep = 0; rep < 2; ++rep) {  // the first launch warms up
         cudaEventRecord(e0, nullptr);
-        if (kind == 1) mma_rate_kernel<true><<<sms, 128, smem>>>(n, chunks, d_out);
-        else mma_rate_kernel<false><<<sms, 128, smem>>>(n, chunks, d_out);
+        if (kind & 1) mma_rate_kernel<true><<<sms, 128, smem>>>(n, chunks, kind >> 1, d_out);
+        else mma_rate_kernel<false><<<sms, 128, smem>>>(n, chunks, kind >> 1, d_out);
         cudaEventRecord(e1, nullptr);
         if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) goto out;
     }
@@ -557,6 +562,54 @@ out:
     if (e0) cudaEventDestroy(e0);
     if (e1) cudaEventDestroy(e1);
     cudaFree(d_out);
+    return rc;
+}
+
+int neon_moe_tma_rate(int device, int packed, int stages, int64_t buffer_bytes, int loads, double* ms, int64_t* cycles) {
+    if (!ms || !cycles || stages < 1 || stages > (packed ? 8 : 6) || buffer_bytes < (1 << 20) || buffer_bytes > (int64_t(8) << 30) || loads < 1 ||
+        loads > (1 << 22))
+        return NEON_MOE_EINVAL;
+    int n_dev = 0, sms = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev || cudaSetDevice(device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+        cudaGetLastError();
+        return NEON_MOE_ECUDA;
+    }
+    const int n_pairs = (int)(buffer_bytes / 16384);
+    const int stage_bytes = packed ? 16384 : 32768;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    uint8_t* buf = nullptr;
+    TmaRateOut* d_out = nullptr;
+    TmaRateOut host{};
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    CUtensorMap tm;
+    float elapsed = 0.f;
+    int rc = NEON_MOE_ECUDA;
+    if (cudaMalloc(&buf, (size_t)n_pairs * 16384) != cudaSuccess || cudaMemset(buf, 0x22, (size_t)n_pairs * 16384) != cudaSuccess ||
+        cudaMalloc(&d_out, sizeof(TmaRateOut)) != cudaSuccess || cudaMemset(d_out, 0, sizeof(TmaRateOut)) != cudaSuccess ||
+        cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess ||
+        cudaFuncSetAttribute(tma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        make_weight_map(nullptr, &tm, buf, (uint64_t)n_pairs * 256, 256, packed != 0) != NEON_MOE_OK)
+        goto out;
+    for (int rep = 0; rep < 2; ++rep) {  // the first launch warms up (and brings a small buffer into L2)
+        cudaEventRecord(e0, nullptr);
+        // both maps report a box pair's 16 KB of global memory to the barrier (the expanding one writes 32 KB of shared memory)
+        tma_rate_kernel<<<sms, 32, smem>>>(tm, n_pairs, loads, stages, 16384u, stage_bytes, d_out);
+        cudaEventRecord(e1, nullptr);
+        if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) goto out;
+    }
+    if (cudaEventElapsedTime(&elapsed, e0, e1) != cudaSuccess ||
+        cudaMemcpy(&host, d_out, sizeof host, cudaMemcpyDeviceToHost) != cudaSuccess)
+        goto out;
+    *ms = elapsed;
+    *cycles = host.cycles;
+    rc = host.status ? NEON_MOE_EDEVICE : NEON_MOE_OK;
+out:
+    cudaGetLastError();
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(d_out);
+    cudaFree(buf);
     return rc;
 }
 
@@ -698,6 +751,13 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         int coop = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, cfg->device);
         h->decode_max_tokens = coop ? t_dec : 0;
+        // the channel-sliced variant: T <= 4, hidden a multiple of 4, at least 3 weight stages next to the output accumulator
+        int t2 = std::min(t_dec, kDec2MaxTok);
+        while (t2 > 0 && dec2_stages(t2, dn_tiles, kDecodeSmemBytes) < 3) --t2;
+        if (coop && t2 > 0 && cfg->hidden % 4 == 0 && cfg->inter % 64 == 0) {
+            if ((rc = dev_alloc(h, &h->dec_y_part, (size_t)h->n_sms * t2 * dn_tiles * 128))) return bail(rc);
+            h->dec_sliced_tokens = t2;
+        }
     }
     if (cfg->ep_size > 1) {
         const size_t ns = (size_t)h->n_src, E = (size_t)cfg->n_experts, Hh = (size_t)cfg->hidden;
@@ -874,7 +934,6 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
 }
 
 // Shared memory of decode_fused_kernel: the stage ring, barriers, routing tables and logits (+ alignment slack).
-constexpr int kDecodeSmemBytes = 227 * 1024;  // everything an SM has: what the token-operand tiles leave goes to weight stages
 
 // The whole pass as one cooperative launch (decode_fused.cuh).  The caller has checked T.
 static int launch_decode_fused(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out, cudaStream_t st) {
@@ -915,6 +974,49 @@ static int launch_decode_fused(neon_moe_handle* h, const void* hidden, int T, co
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     CU(h, cudaLaunchKernelEx(&cfg, decode_fused_kernel, h->tm_gu, h->tm_gu2, h->tm_dn, h->tm_dn2, p));
+    h->launches++;
+    return NEON_MOE_OK;
+}
+
+// The same pass sliced by intermediate channel (decode_sliced.cuh): T <= kDec2MaxTok.
+static int launch_decode_sliced(neon_moe_handle* h, const void* hidden, int T, const float* logit_bias, float* out, cudaStream_t st) {
+    static bool configured[kMaxDevicesAttr] = {};
+    if (!configured[h->cfg.device]) {
+        CU(h, cudaFuncSetAttribute(decode_sliced_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmemBytes));
+        configured[h->cfg.device] = true;
+    }
+    const int H = h->cfg.hidden, I = h->cfg.inter, E = h->cfg.n_experts;
+    DecodeParams p{};
+    p.x = static_cast<const uint16_t*>(hidden); p.wr = h->router_w; p.br = h->router_b; p.logit_bias = logit_bias;
+    p.T = T; p.H = H; p.I = I; p.E = E; p.k = h->cfg.top_k;
+    p.limit = h->cfg.swiglu_limit; p.alpha = h->cfg.swiglu_alpha;
+    p.gu_sfa = h->gu_sfa; p.dn_sfa = h->dn_sfa; p.gu_bias = h->gu_bias; p.dn_bias = h->dn_bias;
+    p.gu_m_tiles = 2 * I / 128; p.dn_m_tiles = (H + 127) / 128; p.nch_h = h->kp_h / kChunkK; p.nch_i = h->kp_i / kChunkK;
+    const int grid = h->n_sms;
+    p.n_slices = std::max(1, std::min(kDecMaxSlices, grid * kDecRouterWarps / E));
+    p.rows_dn = 4;
+    p.stages = dec2_stages(T, p.dn_m_tiles, kDecodeSmemBytes);
+    p.a_tx_bytes = h->a_tx_bytes;
+    p.router_part = h->dec_router_part; p.gu_part = nullptr; p.dn_part = h->dec_y_part;
+    p.counters = h->dec_counters; p.gu_items_cap = h->dec_gu_items_cap;
+    p.router_expected_extra = h->decode_stall_test ? 1u : 0u;
+    p.wait_limit = h->decode_wait_limit;
+    p.status = h->status; p.out = out; p.idx = h->idx; p.route_w = h->route_w;
+    p.d = DispatchArrays{h->count, h->offset, h->perm, h->inv};
+#ifdef NEON_MOE_INSTRUMENT
+    p.trace = h->trace;
+#endif
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = kDecodeSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident at once: they meet at a grid-wide barrier
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CU(h, cudaLaunchKernelEx(&cfg, decode_sliced_kernel, h->tm_gu, h->tm_gu2, h->tm_dn, p));
     h->launches++;
     return NEON_MOE_OK;
 }
@@ -1025,7 +1127,8 @@ static int forward_eager(neon_moe_handle* h, const void* hidden, int T, const fl
     const int k = h->cfg.top_k, n = T * k;
     const bool prof = h->profiling && h->events_used + 5 <= 5 * kMaxProfiledForwards;
     if (h->path == 2 && h->decode_fused && T <= std::min(h->decode_max_tokens, h->decode_fused_tokens) && !prof && h->tile_override == 0 && !h->mx4 && !h->fuse_dispatch) {
-        int rc = launch_decode_fused(h, hidden, T, logit_bias, out, st);
+        int rc = (h->decode_sliced && T <= h->dec_sliced_tokens) ? launch_decode_sliced(h, hidden, T, logit_bias, out, st)
+                                                                  : launch_decode_fused(h, hidden, T, logit_bias, out, st);
         if (rc) return rc;
         if (topk_idx) CU(h, cudaMemcpyAsync(topk_idx, h->idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
         if (topk_w) CU(h, cudaMemcpyAsync(topk_w, h->route_w, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
@@ -1468,6 +1571,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
         h->ep_peer = value != 0;
     } else if (!strcmp(name, "decode_fused")) {
         h->decode_fused = (int)value;
+    } else if (!strcmp(name, "decode_sliced")) {
+        h->decode_sliced = (int)value;
     } else if (!strcmp(name, "decode_fused_tokens")) {
         if (value < 0 || value > kDecMaxTok) return fail(h, NEON_MOE_EINVAL, "decode_fused_tokens must lie in [0, %d]", kDecMaxTok);
         h->decode_fused_tokens = (int)value;

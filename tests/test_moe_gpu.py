@@ -376,17 +376,42 @@ def test_mma_rate_measurement():
     assert lib.neon_moe_mma_rate(0, 0, 100, 16, ctypes.byref(ms), ctypes.byref(cyc)) == 1   # n not a multiple of 16
 
 
-@pytest.mark.parametrize("T", [1, 2, 4, 7, 8])
-def test_one_launch_decode_pass(full20b, T):
+def test_tma_copy_rate_measurement():
+    """The library's copy-rate probe: one SM's TMA unit streaming weight boxes with no consumer.  From a buffer
+    that stays in L2 a box pair lands every few hundred clocks; from a buffer far larger than L2 the whole GPU
+    runs at HBM pace; the scale-copy variant of the MMA probe costs a few clocks per instruction more."""
+    from neonengine_b200 import mma_rate
+    l2 = mma_rate.tma_copy_rate(False, 4, 8, 1024)
+    hbm = mma_rate.tma_copy_rate(False, 4, 1024, 1024)
+    packed = mma_rate.tma_copy_rate(True, 4, 8, 1024)
+    assert 20.0 < l2["bytes_per_cycle_per_sm"] < 128.0
+    assert 3000.0 < hbm["gbs"] < 9000.0
+    assert hbm["gbs"] < l2["gbs"]
+    assert 0.5 < packed["bytes_per_cycle_per_sm"] / l2["bytes_per_cycle_per_sm"] < 2.0
+    plain = mma_rate.measure("mxf8f6f4", 32, 2048)
+    with_sf = mma_rate.measure("mxf8f6f4+sf", 32, 2048)
+    assert plain["cycles_per_mma"] <= with_sf["cycles_per_mma"] < 2 * plain["cycles_per_mma"]
+    lib = __import__("neonengine_b200._lib", fromlist=["load"]).load()
+    import ctypes
+    ms, cyc = ctypes.c_double(), ctypes.c_int64()
+    assert lib.neon_moe_tma_rate(0, 0, 7, 8 << 20, 16, ctypes.byref(ms), ctypes.byref(cyc)) == 1   # too many stages
+
+
+@pytest.mark.parametrize("T,sliced", [(1, 1), (2, 1), (3, 1), (4, 1), (1, 0), (2, 0), (4, 0), (7, 1), (8, 1)])
+def test_one_launch_decode_pass(full20b, T, sliced):
     """Passes of at most 8 tokens run as ONE cooperative kernel (router, both expert products,
-    SwiGLU and combine; no dispatch pass).  Routing and the dispatch arrays it reports are
-    bit-exact against the oracle, outputs within the contract; it launches exactly one kernel;
-    two runs give the same bits; and the multi-kernel path agrees within the contract."""
+    SwiGLU and combine; no dispatch pass): up to 4 tokens sliced by intermediate channel (sliced = 1),
+    above that - or with option decode_sliced 0 - cut into equal runs of K chunks.  Routing and the
+    dispatch arrays it reports are bit-exact against the oracle, outputs within the contract; it
+    launches exactly one kernel; two runs give the same bits; and the multi-kernel path agrees
+    within the contract.  The two kernels share their pass counters, so the cases also check that
+    they can alternate."""
     shape, W, layer = full20b
     lb = synth.zipf_logit_bias(shape.n_experts) if T in (4, 8) else None
     hidden = synth.make_hidden(T, W, 70 + T, logit_bias=lb)
     layer.set_option("use_graphs", 0)
     layer.set_option("decode_fused_tokens", 8)      # by default only single-token passes take the one-launch kernel
+    layer.set_option("decode_sliced", sliced)
     try:
         before = layer.launch_count
         out, _ = check_against_oracle(layer, W, hidden, logit_bias=lb, what=f"one-launch T={T}")
@@ -398,20 +423,25 @@ def test_one_launch_decode_pass(full20b, T):
         multi = run_device(layer, hidden, lb)[0]
         assert layer.launch_count - before > 1
         assert_close(out, multi, f"one-launch vs multi-kernel T={T}")
+        assert layer.status() == 0
     finally:
         layer.set_option("decode_fused", 1)
+        layer.set_option("decode_sliced", 0)
         layer.set_option("decode_fused_tokens", 1)
         layer.set_option("use_graphs", 1)
 
 
-def test_one_launch_decode_bounded_wait_reports_and_recovers(full20b):
+@pytest.mark.parametrize("sliced", [1, 0])
+def test_one_launch_decode_bounded_wait_reports_and_recovers(full20b, sliced):
     """Failure detection without a GPU fault: a test hook makes the kernel's first wait expect one
     arrival more than the grid can deliver.  Every CTA gives up after the (shortened) limit, the
-    pass returns, the status word names the wait, and the next pass is correct again."""
+    pass returns, the status word names the wait, and the next pass is correct again.  Both
+    one-launch kernels."""
     shape, W, layer = full20b
     hidden = synth.make_hidden(2, W, 90)
     layer.set_option("use_graphs", 0)
     layer.set_option("decode_fused_tokens", 8)
+    layer.set_option("decode_sliced", sliced)
     try:
         layer.set_option("decode_wait_limit", 100_000_000)   # ~50 ms of SM clocks
         layer.set_option("decode_stall_test", 1)
@@ -422,6 +452,7 @@ def test_one_launch_decode_bounded_wait_reports_and_recovers(full20b):
         check_against_oracle(layer, W, hidden, what="after a timed-out pass")
     finally:
         layer.set_option("decode_stall_test", 0)
+        layer.set_option("decode_sliced", 0)
         layer.set_option("decode_fused_tokens", 1)
         layer.set_option("use_graphs", 1)
 

@@ -148,15 +148,25 @@ inline void ep_peer_offsets(const int32_t* all_counts, int ep_size, int n_expert
 }
 
 // Token rows to the expert owners: sorted entry p -> its place in the owner's xrecv (16-byte vectors).  A fixed
-// grid of CTAs walks the rows; one system-scope fence per CTA, after a CTA barrier, publishes all of its stores
-// (a fence per thread costs far more than the copy).
+// grid walks the rows, one warp per row, four vectors per lane in flight (the stores cross NVLink: what limits
+// them is how many are outstanding); one system-scope fence per CTA, after a CTA barrier, publishes all of its
+// stores (a fence per thread costs far more than the copy).
 __global__ void __launch_bounds__(256) scatter_rows_kernel(const uint16_t* __restrict__ hidden, const int32_t* __restrict__ perm, int k,
                                                            int H, int n, PeerRows<uint16_t> t) {
-    const int nvec = H / 8;
-    for (int p = blockIdx.x; p < n; p += gridDim.x) {
+    const int nvec = H / 8, lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    for (int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < n; p += warps) {
         const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)(perm[p] / k) * H);
         uint4* dst = reinterpret_cast<uint4*>(peer_row(t, p, H));
-        for (int i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
+        for (int i = lane; i < nvec; i += 128) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + 32 * j < nvec) v[j] = src[i + 32 * j];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + 32 * j < nvec) dst[i + 32 * j] = v[j];
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) __threadfence_system();

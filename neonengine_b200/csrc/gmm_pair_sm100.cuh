@@ -169,28 +169,12 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tma_load_2d_pair(st + SFA_OFF, kc == 2 ? &tmS : &tmS1, full_leader + s * 8, 0, (int)atom);
         }
     };
-    // The weights of the first item's first stages do not depend on the predecessor kernel, only on the tile list,
-    // which (p.prefetch) an earlier kernel of the stream completed before this grid could start: fetch them now, so
-    // that the copy from HBM overlaps the predecessor's run.
-    int n_pre = 0;
-    if (warp == 0 && p.prefetch) {
-        const int n_items0 = *reinterpret_cast<const volatile int32_t*>(p.n_tiles) * mp_tiles;
-        if (pair < n_items0) {
-            const int tile = pair / mp_tiles, m = 2 * (pair - tile * mp_tiles) + (int)crank;
-            const int e = reinterpret_cast<const volatile int32_t*>(p.tile_expert)[tile];
-            const uint32_t box = (uint32_t)((e * p.m_tiles + min(m, p.m_tiles - 1)) * p.n_chunks);
-            n_pre = min(STAGES, (p.n_chunks + KC - 1) / KC);
-            if (elect_one())
-                for (int s = 0; s < n_pre; ++s) load_weights(s, min(KC, p.n_chunks - s * KC), (int)(box + s * KC) * 128, box + s * KC);
-            __syncwarp();
-        }
-    }
     pdl_wait();
     const int n_items = *p.n_tiles * mp_tiles;
 
     if (warp == 0) {
         // ---- producer (both CTAs): own weight tile + own half of the stacked token rows -------------------
-        int s = 0, ph = 0, g = 0;  // g: stages issued so far (the first n_pre already hold their weights)
+        int s = 0, ph = 0;
         for (int item = pair; item < n_items; item += n_pairs) {
             const int tile = item / mp_tiles, m = 2 * (item - tile * mp_tiles) + (int)crank;
             const int m_ld = min(m, p.m_tiles - 1);  // the absent second tile of an odd count: a duplicate load, never stored
@@ -200,15 +184,13 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int box_row = (int)(box * 128);
             uint32_t atom = box;  // row of the scale-atom tensor (one 512-byte atom per weight box)
             const uint8_t* act_src = p.act + (size_t)tile * p.n_chunks * act_stride + crank * half_bytes;
-            for (int left = p.n_chunks; left > 0; left -= KC, ++g) {
+            for (int left = p.n_chunks; left > 0; left -= KC) {
                 const int kc = left >= KC ? KC : 1;
-                if (g >= n_pre) {
-                    const int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
-                    if (!__all_sync(0xffffffffu, ok)) goto done;
-                }
+                const int ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1, kWaitLimitCycles);
+                if (!__all_sync(0xffffffffu, ok)) goto done;
                 uint8_t* st = smem + s * L::kStage;
                 if (elect_one()) {
-                    if (g >= n_pre) load_weights(s, kc, box_row, atom);
+                    load_weights(s, kc, box_row, atom);
                     // The token rows (from L2, early) report to a barrier of their own CTA; the leader's is the stage barrier,
                     // on which this is also the one arrival; the peer's warp 1 forwards its "rows landed" to the leader.
                     uint64_t* rows_bar = leader ? &full[s] : &peer_full[s];

@@ -486,12 +486,8 @@ __global__ void __launch_bounds__(256) split_rows_stacked_kernel(const void* __r
                                                                  const int32_t* __restrict__ tile_rows, int tile_tokens,
                                                                  const float* __restrict__ amax_in, float amax_const,
                                                                  uint8_t* __restrict__ act, float* __restrict__ row_scale) {
-    // The split of the hidden rows (FROM_BF16) lets its successor start only after its own wait: from then on every
-    // later kernel of the pass starts with the routing kernels complete, which is what lets the grouped GEMMs fetch
-    // weights by the tile list before their own wait (GmmParams::prefetch).
-    if (!FROM_BF16) pdl_launch_dependents();
+    pdl_launch_dependents();
     pdl_wait();
-    if (FROM_BF16) pdl_launch_dependents();
     const int Kp = round_up_int(K, kChunkK), n_chunks = Kp / kChunkK;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_rows * n_chunks) return;
@@ -677,8 +673,6 @@ struct GmmParams {
     uint32_t a_tx_bytes;   // bytes one 128 x 128 4-bit box reports to its mbarrier
     int tmem_cols;         // TMEM columns to allocate (power of two)
     int stages;            // pipeline stages in use (<= GmmSmem::kStages)
-    int prefetch;          // 1: the tile list is complete once this grid runs, so weights may be fetched before
-                           //    the predecessor kernel (which writes the token operand) has finished
 #ifdef NEON_MOE_INSTRUMENT
     long long* trace;      // optional [2 roles][512 stages][2] clock stamps of CTA 0 (instrumented builds only)
 #endif

@@ -852,7 +852,6 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         DBG_SYNC(h, st, "split_rows (hidden)");
         GmmParams g{};
         h->pass_entries = n;
-        g.prefetch = tt <= 32 && !h->mx4;  // the stacked split of the hidden rows precedes: it waits before it lets successors start
         g.a_tx_bytes = h->a_tx_bytes;
 #ifdef NEON_MOE_INSTRUMENT
         g.trace = h->trace_which == 2 ? nullptr : h->trace;

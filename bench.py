@@ -1066,7 +1066,8 @@ def moe_roofline(run, step_s, stage_ms, n_prof, peaks, peak_kind, traffic_table)
         ceil8 = mma_rate.measure("mxf8f6f4", 128, 8192, device=run.local_rank)["tflops"]
         ceil4 = mma_rate.measure("mxf4", 256, 8192, device=run.local_rank)["tflops"]
         layer_tf = T * k * shape.flops_per_pair / step_s / 1e12
-        roof = {"bound": "tensor", "kernel": "gmm_bs_kernel<gate_up>", "achieved": achieved, "peak": peak,
+        kern = "gmm_pair_prefill_kernel" if run.layer.pair_ctas() > 0 else "gmm_bs_kernel"
+        roof = {"bound": "tensor", "kernel": kern + "<gate_up>", "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind + " bf16 burst", "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                 "algorithmic_flops_per_launch": gu_flops, "ms_per_launch": gu_ms, "layer_tflops": layer_tf,
                 "layer_frac_of_mxfp4_nominal_9000": layer_tf / 9000.0,

@@ -19,6 +19,7 @@
 #include "ep.cuh"
 #include "decode_fused.cuh"
 #include "decode_sliced.cuh"
+#include "gmm_pair_prefill_sm100.cuh"
 #include "mma_rate.cuh"
 #include "mma_pair.cuh"
 
@@ -97,6 +98,7 @@ struct neon_moe_handle {
     // (Zipf / uniform routing): T=8 58.5 vs 56.6 / 79.3 vs 75.6 us, T=16 72.2 vs 68.6 / 94.2 vs 91.0, T=64 107.9 vs 103.1 /
     // 115.8 vs 112.3, T=96 120.7 vs 118.2 / 118.9 vs 118.0, T=128 131.0 vs 131.3 / 123.6 vs 129.4, T=256 190 vs 193 / 180 vs 194.
     int pair_mma = 2;
+    int pair_prefill = 1;         // 128-token tiles on CTA pairs (two-SM MMAs, each CTA half of the token rows); 0 = one CTA per tile
     int pass_entries = 0;         // routed entries of the pass being launched
     int mxf4_prefill = 0;         // 128-token tiles: 1 = activations quantised to MXFP4, tcgen05.mma.kind::mxf4 (outside the accuracy contract)
     int mx4 = 0;                  // decode tiles: 1 = kind::mxf4 with e2m1 activation terms, 0 = kind::mxf8f6f4 with e4m3 terms
@@ -458,6 +460,43 @@ int launch_gmm_pair(neon_moe_handle* h, const CUtensorMap& tm1, const CUtensorMa
     return NEON_MOE_OK;
 }
 
+// 128-token (prefill) tiles on CTA pairs (gmm_pair_prefill_sm100.cuh).
+template <int TERMS, bool GATE_UP>
+int launch_gmm_pair_prefill(neon_moe_handle* h, const CUtensorMap& tm1, GmmParams p, cudaStream_t st) {
+    using L = PairPrefillSmem<TERMS>;
+    static bool configured[kMaxDevicesAttr] = {};
+    auto kern = gmm_pair_prefill_kernel<TERMS, GATE_UP>;
+    CUtensorMap ts1;  // scale atoms, fetched by TMA so that the peer's copies can report to the leader's barrier
+    int rc = make_atom_map(h, &ts1, p.sfa, (uint64_t)h->n_local * p.m_tiles * p.n_chunks, 1);
+    if (rc) return rc;
+    if (!configured[h->cfg.device]) {
+        CU(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::smem_bytes(L::kStages)));
+        configured[h->cfg.device] = true;
+    }
+    int stages = L::kStages;
+    if (h->max_stages > 0) stages = std::max(2, std::min(stages, h->max_stages));
+    p.stages = stages;
+    p.tmem_cols = L::tmem_cols(stages);
+    static int max_pairs[kMaxDevicesAttr] = {};
+    if (!max_pairs[h->cfg.device]) {  // pairs need two SMs of one TPC: ask the runtime how many clusters can be resident
+        cudaLaunchConfig_t q{};
+        q.gridDim = dim3(h->n_sms & ~1);
+        q.blockDim = dim3(192);
+        q.dynamicSmemBytes = (size_t)L::smem_bytes(L::kStages);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = h->n_sms / 2;
+        }
+        max_pairs[h->cfg.device] = n;
+    }
+    const int pairs = std::min(max_pairs[h->cfg.device], h->n_sms / 2);
+    launch_k(h->pdl != 0, kern, dim3(2 * pairs), dim3(192), (size_t)L::smem_bytes(stages), st, tm1, ts1, p);
+    h->launches++;
+    h->pair_ctas = 2 * pairs;
+    return NEON_MOE_OK;
+}
+
 // e4m3 terms of the fp32 SwiGLU output fed to the down product of 128-token (prefill) tiles.  Each
 // term carries ~4 significant bits; three would already meet the accuracy contract (measured
 // max-abs 3.4e-3 at T=256) but were measured no faster (0.762 vs 0.757 ms at T=4096: that launch is
@@ -484,6 +523,7 @@ int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, cons
     if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
     if (h->mxf4_prefill)  // MXFP4-quantised activations, both operands packed 4-bit, two chunks per stage
         return launch_gmm_one<128, 1, GATE_UP, false, 2, true>(h, GATE_UP ? h->tm4_gu : h->tm4_dn, GATE_UP ? h->tm4_gu2 : h->tm4_dn2, p, st);
+    if (h->pair_prefill) return launch_gmm_pair_prefill<TERMS, GATE_UP>(h, tm1, p, st);
     return launch_gmm_one<128, TERMS, GATE_UP, false, 1>(h, tm1, tm2, p, st);
 }
 
@@ -1583,6 +1623,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     } else if (!strcmp(name, "pair_mma")) {
         if (value < 0 || value > 2) return fail(h, NEON_MOE_EINVAL, "pair_mma is 0 (never), 1 (always) or 2 (small passes)");
         h->pair_mma = (int)value;
+    } else if (!strcmp(name, "pair_prefill")) {
+        h->pair_prefill = value != 0;
     } else if (!strcmp(name, "mxf4_prefill")) {
         h->mxf4_prefill = (int)value;
     } else if (!strcmp(name, "mx4")) {

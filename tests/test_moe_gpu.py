@@ -79,6 +79,16 @@ def full20b():
     layer.close()
 
 
+@pytest.fixture(scope="module")
+def full20b_prefill():
+    """The same layer with room for a 4096-token pass."""
+    shape = synth.MoeShape()
+    W = synth.make_weights(shape, 0)
+    layer = make_layer(shape, W, max_tokens=4096)
+    yield shape, W, layer
+    layer.close()
+
+
 def test_config0_decode_single_token(full20b):
     shape, W, layer = full20b
     for stream in range(3):
@@ -512,6 +522,26 @@ def test_two_sm_mma_decode_tiles(full20b, T):
     finally:
         layer.set_option("pair_mma", 2)
         layer.set_option("decode_fused", 1)
+
+
+@pytest.mark.parametrize("T", [385, 700, 4096])
+def test_two_sm_mma_prefill_tiles(full20b_prefill, T):
+    """128-token tiles on CTA pairs (option pair_prefill, the default): each CTA streams its own weight tile
+    and half of the token rows, the leader issues M = 256 instructions with the tile's own per-row block
+    scales.  Same products in the same order as the one-CTA kernel: identical output bits; checked against the
+    oracle as well.  T = 385 and 700 leave ragged last tiles (N not a multiple of 128)."""
+    shape, W, layer = full20b_prefill
+    hidden = synth.make_hidden(T, W, 400 + T)
+    toks = np.arange(1, T, max(1, T // 12), dtype=np.int32)
+    layer.set_option("pair_prefill", 0)
+    try:
+        ref = run_device(layer, hidden, None)[0]
+        layer.set_option("pair_prefill", 1)
+        out, _ = check_against_oracle(layer, W, hidden, tokens=toks, what=f"pair_prefill T={T}")
+        np.testing.assert_array_equal(out, ref)
+        assert layer.status() == 0
+    finally:
+        layer.set_option("pair_prefill", 1)
 
 
 def test_two_sm_mma_instruction_self_check():

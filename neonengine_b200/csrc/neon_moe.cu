@@ -498,10 +498,11 @@ int launch_gmm_pair_prefill(neon_moe_handle* h, const CUtensorMap& tm1, GmmParam
 }
 
 // e4m3 terms of the fp32 SwiGLU output fed to the down product of 128-token (prefill) tiles.  Each
-// term carries ~4 significant bits; three would already meet the accuracy contract (measured
-// max-abs 3.4e-3 at T=256) but were measured no faster (0.762 vs 0.757 ms at T=4096: that launch is
-// bound by activation traffic, not by the tensor cores), so four stay for the extra accuracy.
-constexpr int kDownTermsPrefill = 4;
+// term carries ~4 significant bits.  On the paired kernel the product is bound by tensor-core work, which
+// is proportional to the term count: three terms measured 0.44 ms against 0.57 ms with four at T=4096, with
+// max-abs 2.2e-3 / mean-rel 1.5e-5 against the oracle (four terms: 1.2e-3 / 6.6e-6; the contract is 2e-2 /
+// 5e-3).  The decode tiles keep four: they are bound by the weight stream, not by tensor work.
+constexpr int kDownTermsPrefill = 3;
 constexpr int kDecodeSmemBytes = 227 * 1024;  // everything an SM has: what the token-operand tiles leave goes to weight stages
 constexpr int kPairMaxEntries = 96 * 4;  // passes of up to 96 tokens at top-4 take the paired kernel
 constexpr int kMx4Terms = 6;  // e2m1 terms per activation value on the packed 4-bit path
@@ -515,9 +516,11 @@ int launch_gmm(neon_moe_handle* h, int tile_tokens, const CUtensorMap& tm1, cons
         if (tile_tokens == 16) return launch_gmm_one<16, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
         return launch_gmm_one<32, kMx4Terms, GATE_UP, true, 2, true>(h, q1, q2, p, st);
     }
-    if (tile_tokens <= 32 && (h->pair_mma == 1 || (h->pair_mma == 2 && h->pass_entries <= kPairMaxEntries))) {
-        if (tile_tokens == 16) return launch_gmm_pair<16, TERMS, GATE_UP>(h, tm1, tm2, p, st);
-        return launch_gmm_pair<32, TERMS, GATE_UP>(h, tm1, tm2, p, st);
+    if constexpr (TERMS % 2 == 0) {  // the paired decode kernel splits the stacked terms between its two CTAs
+        if (tile_tokens <= 32 && (h->pair_mma == 1 || (h->pair_mma == 2 && h->pass_entries <= kPairMaxEntries))) {
+            if (tile_tokens == 16) return launch_gmm_pair<16, TERMS, GATE_UP>(h, tm1, tm2, p, st);
+            return launch_gmm_pair<32, TERMS, GATE_UP>(h, tm1, tm2, p, st);
+        }
     }
     if (tile_tokens == 16) return launch_gmm_one<16, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);
     if (tile_tokens == 32) return launch_gmm_one<32, TERMS, GATE_UP, true, 2>(h, tm1, tm2, p, st);

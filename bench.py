@@ -1095,7 +1095,7 @@ def side_config(workload, args, local_rank, peaks, peak_kind, traffic_table):
     out = {"description": run.desc, "tokens_per_step": run.T, "ms_per_step": ms / args.steps,
            "ms_per_step_min": min(groups) / args.steps, "groups": len(groups), "value": run.T / step_s, "unit": "tokens/s",
            "roofline": roof, "parity": run.parity(8), "status": run.layer.status()}
-    if run.T > 384 and "mma_issue_ceiling_tflops" in roof:
+    if run.T > 224 and "mma_issue_ceiling_tflops" in roof:
         out["mxf4_variant"] = run.mxf4_variant(args.steps, roof["mma_issue_ceiling_tflops"]["mxf4_128x256"])
     run.close()
     return out
@@ -1218,7 +1218,7 @@ def run_moe(args, rank, world, local_rank):
     else:
         roofline = moe_roofline(run, step_s, stage_ms, 0, peaks, peak_kind, traffic_table)
     mxf4_variant = None
-    if not ep and T > 384 and "mma_issue_ceiling_tflops" in roofline and not any(o.startswith("mxf4_prefill") for o in args.option):
+    if not ep and T > 224 and "mma_issue_ceiling_tflops" in roofline and not any(o.startswith("mxf4_prefill") for o in args.option):
         mxf4_variant = run.mxf4_variant(args.steps, roofline["mma_issue_ceiling_tflops"]["mxf4_128x256"])
 
     parity = run.parity(16 if ep else 8) if rank == 0 or ep else None

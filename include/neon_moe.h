@@ -230,7 +230,7 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * "fuse_dispatch" (default 0): 1 = at decode-sized passes the router CTA that finishes last also
  * runs the dispatch, saving one launch (identical results; measured no faster than the separate
  * kernel under programmatic dependent launch, 0.1086 vs 0.1078 ms per 64-token pass).
- * "tile_tokens" (default 0 = by batch size: 16 up to 16 tokens, 32 up to 384, else 128): forces the
+ * "tile_tokens" (default 0 = by batch size: 16 up to 16 tokens, 32 up to 224, else 128): forces the
  * token-tile size of the grouped GEMMs (16 and 32 use the stacked-term kernels).
  * "router_wide_max" (default 384): passes of up to this many tokens run the router with one CTA per
  * token, which also produces the per-token maxima the 16/32-token tiles scale by; larger passes use
@@ -249,7 +249,7 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * "decode_wait_limit": SM clocks such a wait may take (default 4e8).  "decode_stall_test": 1 makes the
  * kernel's first wait expect a signal nobody sends, so that the bounded wait can be tested without
  * faulting the GPU.
- * "mxf4_prefill" (default 0): 1 runs passes of more than 384 tokens on tcgen05.mma.kind::mxf4 with the
+ * "mxf4_prefill" (default 0): 1 runs passes of more than 224 tokens on tcgen05.mma.kind::mxf4 with the
  * activations quantised to MXFP4 (blocks of 32, E8M0 scale 2^(floor(log2 amax) - 2), nearest e2m1, ties to
  * even).  Four-bit activations put the result ~20 % (mean relative) away from the unquantised one - far
  * outside the 2e-2 / 5e-3 contract - so it is an option; it agrees with an oracle that applies the same
@@ -258,7 +258,7 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * MMAs (tcgen05 cta_group::2, 256 weight rows per instruction): 0 never, 1 always, 2 for passes that route at
  * most 384 entries (96 tokens at top-4), where it measured 1-5 % faster per pass; results are bit-identical to
  * the one-CTA kernel's.
- * "pair_prefill" (default 1): 128-token tiles (passes above 384 tokens) on clusters of two CTAs: two adjacent
+ * "pair_prefill" (default 1): 128-token tiles (passes above 224 tokens) on clusters of two CTAs: two adjacent
  * weight tiles per pair, each CTA half of the token rows, M = 256 instructions; bit-identical to the one-CTA
  * kernel (0), measured 1.23 vs 1.36-1.40 ms per 4096-token pass.
  * "ep_peer" (default 0; expert-parallel handles, after neon_moe_ep_peer_import on every rank): 1 makes both

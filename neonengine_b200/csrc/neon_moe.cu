@@ -388,11 +388,13 @@ int load_matrix_tc(neon_moe_handle* h, const uint8_t* blocks, const uint8_t* sca
 }
 
 // Token-tile size: small and mid-size batches use 32-token tiles (16 up to 16 tokens) with the
-// activation terms stacked along N (one MMA per k-block reads the weight tile once); from 385 tokens
-// on, 128-token tiles with the terms as successive MMAs.  Measured per pass at the gpt-oss shapes
-// (32 vs 128-token tiles): T=96 135 vs 205 us, T=128 139 vs 208, T=256 189 vs 227, T=384 240 vs 251,
-// T=512 290 vs 270, T=1024 489 vs 474.
-int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= 384 ? 32 : 128); }
+// activation terms stacked along N (one MMA per k-block reads the weight tile once); from 225 tokens
+// on, 128-token tiles with the terms as successive MMAs (on CTA pairs).  Measured per pass at the gpt-oss
+// shapes (32 vs 128-token tiles): T=96 116 vs 149 us, T=128 123 vs 149, T=192 143 vs 158, T=256 173 vs 163,
+// T=320 218 vs 181, T=384 232 vs 191, T=512 306 vs 217, T=768 409 vs 259.  (With the one-CTA prefill kernel
+// the crossing was at 385 tokens.)
+constexpr int kSmallTileMaxTokens = 224;
+int tile_tokens_for(int T) { return T <= 16 ? 16 : (T <= kSmallTileMaxTokens ? 32 : 128); }
 int tile_tokens_for(const neon_moe_handle* h, int T) { return h->tile_override ? h->tile_override : tile_tokens_for(T); }
 
 template <int BN, int TERMS, bool GATE_UP, bool STACK, int KC, bool MX4 = false>

@@ -115,9 +115,9 @@ def _config1(shape, W, layer):
     assert count.sum() == 256 and count.max() > 3 * count[count > 0].min()  # loads are skewed
 
 
-@pytest.mark.parametrize("T", [2, 3, 5, 9, 17, 33, 100, 200, 384, 385])
+@pytest.mark.parametrize("T", [2, 3, 5, 9, 17, 33, 100, 200, 224, 225, 384, 385])
 def test_ragged_token_counts(full20b, T):
-    """Odd sizes either side of every switch of router kernel and token-tile size (16 / 64 / 384)."""
+    """Odd sizes either side of every switch of router kernel and token-tile size (16 / 64 / 224 / 384)."""
     shape, W, layer = full20b
     hidden = synth.make_hidden(T, W, 1, stream=T)
     toks = None if T <= 33 else np.arange(0, T, 7 if T <= 100 else 29, dtype=np.int32)
@@ -514,6 +514,7 @@ def test_two_sm_mma_decode_tiles(full20b, T):
     toks = None if T <= 64 else np.arange(1, T, 23, dtype=np.int32)
     layer.set_option("decode_fused", 0)
     layer.set_option("pair_mma", 0)
+    layer.set_option("tile_tokens", 0 if T <= 16 else 32)   # 32-token tiles also where 128-token ones are the default
     try:
         ref = run_device(layer, hidden, lb)[0]
         layer.set_option("pair_mma", 1)
@@ -521,6 +522,7 @@ def test_two_sm_mma_decode_tiles(full20b, T):
         np.testing.assert_array_equal(out, ref)
     finally:
         layer.set_option("pair_mma", 2)
+        layer.set_option("tile_tokens", 0)
         layer.set_option("decode_fused", 1)
 
 

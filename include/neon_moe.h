@@ -258,6 +258,8 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * MMAs (tcgen05 cta_group::2, 256 weight rows per instruction): 0 never, 1 always, 2 for passes that route at
  * most 384 entries (96 tokens at top-4), where it measured 1-5 % faster per pass; results are bit-identical to
  * the one-CTA kernel's.
+ * "dispatch_multi" (default 1): passes of more than 1024 (token, slot) entries sort them on one CTA per 1024
+ * entries (two launches) instead of one CTA for all; identical arrays.
  * "pair_prefill" (default 1): 128-token tiles (passes above 224 tokens) on clusters of two CTAs: two adjacent
  * weight tiles per pair, each CTA half of the token rows, M = 256 instructions; bit-identical to the one-CTA
  * kernel (0), measured 1.23 vs 1.36-1.40 ms per 4096-token pass.

@@ -212,6 +212,147 @@ __global__ void __launch_bounds__(1024) dispatch_tiles_kernel(const int32_t* __r
     build_tile_list(idx, n, e_lo, n_local, d, tile_tokens, tl, s_first);
 }
 
+// The same result from many CTAs, for prefill-sized passes (one CTA needs ~110 us for 32 768 entries).  Two
+// launches.  dispatch_count_kernel: CTA b counts the experts of entries [1024 b, 1024 b + 1024) into
+// blk_count[b][e]; the CTA that finishes last turns the counts into everything that does not depend on single
+// entries: count / offset per expert, the write position blk_base[b][e] of CTA b's first entry of expert e
+// (offset[e] + the counts of the CTAs before it: the sort stays stable), the first tile of every expert and the
+// tile list.  dispatch_place_kernel: every CTA ranks its entries again (same warp-match scheme) and writes perm,
+// inv and the tile of every sorted row.
+struct DispatchScratch {
+    int32_t* blk_count;   // [blocks][n_local]
+    int32_t* blk_base;    // [blocks][n_local]
+    int32_t* tile_first;  // [n_local + 1]
+    unsigned* done;       // [1] CTAs that have written their counts; left at zero
+};
+
+// Entry of thread tid of a 1024-entry chunk: its local expert (or -1), its rank among the entries of that expert
+// in its warp, and - in wc[warp][e] - the number of such entries in the warps before it (after the barriers).
+__device__ __forceinline__ void dispatch_rank_chunk(const int32_t* idx, int n, int e_lo, int n_local, int i, int* wc, int* cnt, int& e, int& rank) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int j = tid; j < 32 * n_local; j += 1024) wc[j] = 0;
+    e = -1;
+    if (i < n) {
+        e = __ldcg(idx + i) - e_lo;
+        if (e < 0 || e >= n_local) e = -1;
+    }
+    __syncthreads();
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) wc[warp * n_local + e] = __popc(peers);
+    __syncthreads();
+    for (int ee = tid; ee < n_local; ee += 1024) {
+        int run = 0;
+#pragma unroll 8
+        for (int w = 0; w < 32; ++w) {
+            const int c = wc[w * n_local + ee];
+            wc[w * n_local + ee] = run;
+            run += c;
+        }
+        cnt[ee] = run;
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(1024) dispatch_count_kernel(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
+                                                              DispatchArrays d, int tile_tokens, TileList tl, DispatchScratch sc) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int dsmem[];  // [32][n_local]
+    __shared__ int cnt[kMaxExperts], off[kMaxExperts + 1], first[kMaxExperts + 1];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, b = blockIdx.x, nb = gridDim.x;
+    int e, rank;
+    dispatch_rank_chunk(idx, n, e_lo, n_local, b * 1024 + tid, dsmem, cnt, e, rank);
+    for (int ee = tid; ee < n_local; ee += 1024) __stcg(sc.blk_count + (size_t)b * n_local + ee, cnt[ee]);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(sc.done, 1u) == (unsigned)(nb - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int ee = tid; ee < n_local; ee += 1024) {  // totals per expert
+        int run = 0;
+        for (int bb = 0; bb < nb; ++bb) run += __ldcg(sc.blk_count + (size_t)bb * n_local + ee);
+        cnt[ee] = run;
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scans of the counts and of the tile counts, 8 experts per lane
+        int c[8], tsum = 0, csum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int ee = lane * 8 + j;
+            c[j] = ee < n_local ? cnt[ee] : 0;
+            csum += c[j];
+            tsum += (c[j] + tile_tokens - 1) / tile_tokens;
+        }
+        int cpre = csum, tpre = tsum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int a = __shfl_up_sync(0xffffffffu, cpre, o), t2 = __shfl_up_sync(0xffffffffu, tpre, o);
+            if (lane >= o) { cpre += a; tpre += t2; }
+        }
+        int crun = cpre - csum, trun = tpre - tsum;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int ee = lane * 8 + j;
+            if (ee < n_local) {
+                off[ee] = crun;
+                first[ee] = trun;
+                d.count[ee] = c[j];
+                d.offset[ee] = crun;
+                sc.tile_first[ee] = trun;
+            }
+            crun += c[j];
+            trun += (c[j] + tile_tokens - 1) / tile_tokens;
+        }
+        if (lane == 31) {
+            off[n_local] = cpre;
+            first[n_local] = tpre;
+            d.offset[n_local] = cpre;
+            sc.tile_first[n_local] = tpre;
+            *tl.n_tiles = tpre;
+        }
+    }
+    __syncthreads();
+    for (int ee = tid; ee < n_local; ee += 1024) {
+        int run = off[ee];
+        for (int bb = 0; bb < nb; ++bb) {  // where every CTA's entries of this expert start
+            sc.blk_base[(size_t)bb * n_local + ee] = run;
+            run += __ldcg(sc.blk_count + (size_t)bb * n_local + ee);
+        }
+        const int lo = off[ee], c = cnt[ee];
+        int t = first[ee];
+        for (int r = 0; r < c; r += tile_tokens, ++t) {
+            tl.expert[t] = ee;
+            tl.row0[t] = lo + r;
+            tl.rows[t] = min(tile_tokens, c - r);
+        }
+    }
+    if (tid == 0) *sc.done = 0u;  // ready for the next pass
+}
+
+__global__ void __launch_bounds__(1024) dispatch_place_kernel(const int32_t* __restrict__ idx, int n, int e_lo, int n_local,
+                                                              DispatchArrays d, int tile_tokens, TileList tl, DispatchScratch sc) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int dsmem[];  // [32][n_local]
+    __shared__ int cnt[kMaxExperts];
+    const int tid = threadIdx.x, warp = tid >> 5, b = blockIdx.x, i = b * 1024 + tid;
+    int e, rank;
+    dispatch_rank_chunk(idx, n, e_lo, n_local, i, dsmem, cnt, e, rank);
+    if (i < n) {
+        if (e >= 0) {
+            const int pos = sc.blk_base[(size_t)b * n_local + e] + dsmem[warp * n_local + e] + rank;
+            d.perm[pos] = i;
+            d.inv[i] = pos;
+            tl.row_tile[pos] = sc.tile_first[e] + (pos - d.offset[e]) / tile_tokens;
+        } else {
+            d.inv[i] = -1;
+        }
+    }
+}
+
 // The same for at most 1024 entries (decode batches): one entry per thread, four barriers, all
 // scans done by warps in shared memory.  Identical results to dispatch_tiles_kernel.
 __device__ __forceinline__ void dispatch_tiles_small_body(const int32_t* idx, int n, int e_lo, int n_local, DispatchArrays d,

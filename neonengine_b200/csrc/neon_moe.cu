@@ -87,6 +87,9 @@ struct neon_moe_handle {
                                   // CTA run: more rebuilds of the token-operand tiles, longer combine)
     int decode_stall_test = 0;    // test hook: the kernel's first wait expects one arrival too many and must time out
     long long decode_wait_limit = kWaitLimitCycles;
+    int32_t *disp_blk_count = nullptr, *disp_blk_base = nullptr, *disp_tile_first = nullptr;  // many-CTA dispatch scratch
+    unsigned* disp_done = nullptr;
+    int dispatch_multi = 1;       // passes of more than 1024 entries: dispatch on one CTA per 1024 entries (0: one CTA)
     float *dec_router_part = nullptr, *dec_gu_part = nullptr, *dec_dn_part = nullptr;
     float* dec_y_part = nullptr;  // decode_sliced_kernel: [CTA][token][padded hidden] contributions to the output
     int dec_sliced_tokens = 0;    // largest pass decode_sliced_kernel can take (0: unavailable)
@@ -208,6 +211,7 @@ void free_all(neon_moe_handle* h) {
                     h->x_act, h->a_act, h->x_scale, h->x_amax, h->a_f32, h->tile_expert, h->tile_row0, h->tile_rows,
                     h->n_tiles, h->row_tile, h->s_idx, h->s_count, h->s_offset, h->s_perm, h->s_inv, h->all_counts_d,
                     h->row_expert, h->s_w, h->yrecv, h->yback, h->ones, h->xsend, h->xrecv,
+                    h->disp_blk_count, h->disp_blk_base, h->disp_tile_first, h->disp_done,
                     h->dec_router_part, h->dec_gu_part, h->dec_dn_part, h->dec_y_part, h->dec_counters, h->ep_bar_src, h->ep_bar_dst};
     for (void* p : ptrs)
         if (p) cudaFree(p);
@@ -777,6 +781,13 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         (rc = dev_alloc(h, &h->tile_row0, (size_t)h->tile_cap)) || (rc = dev_alloc(h, &h->tile_rows, (size_t)h->tile_cap)) ||
         (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
         return bail(rc);
+    {   // the many-CTA dispatch of prefill-sized passes: per-chunk expert counts and write positions
+        const size_t blocks = (n + 1023) / 1024;
+        if ((rc = dev_alloc(h, &h->disp_blk_count, blocks * h->n_local)) || (rc = dev_alloc(h, &h->disp_blk_base, blocks * h->n_local)) ||
+            (rc = dev_alloc(h, &h->disp_tile_first, (size_t)h->n_local + 1)) || (rc = dev_alloc(h, &h->disp_done, (size_t)4)))
+            return bail(rc);
+        if (cudaMemset(h->disp_done, 0, 16) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
+    }
     // one-launch decode pass: needs sm_100, one GPU holding all experts, at most 32 (token, slot) entries
     if (h->path == 2 && cfg->ep_size == 1 && cfg->n_experts <= h->n_sms && cfg->top_k <= kDecMaxEntries &&
         h->kp_h / kChunkK <= kDecCacheChunks && h->kp_i / kChunkK <= kDecCacheChunks) {
@@ -882,7 +893,13 @@ static int experts_core(neon_moe_handle* h, const void* hidden, int rows, int k_
         } else if (n <= 1024)
             launch_k(h->pdl != 0, dispatch_tiles_small_kernel, dim3(1), dim3(1024), (size_t)(32 * EL) * sizeof(int), st, idx, n,
                      e_lo, EL, d, tt, tl);
-        else
+        else if (h->dispatch_multi) {
+            const DispatchScratch sc{h->disp_blk_count, h->disp_blk_base, h->disp_tile_first, h->disp_done};
+            const dim3 grid((n + 1023) / 1024);
+            launch_k(h->pdl != 0, dispatch_count_kernel, grid, dim3(1024), (size_t)(32 * EL) * sizeof(int), st, idx, n, e_lo, EL, d, tt, tl, sc);
+            launch_k(h->pdl != 0, dispatch_place_kernel, grid, dim3(1024), (size_t)(32 * EL) * sizeof(int), st, idx, n, e_lo, EL, d, tt, tl, sc);
+            h->launches++;
+        } else
             launch_k(h->pdl != 0, dispatch_tiles_kernel, dim3(1), dim3(1024), (size_t)(33 * EL) * sizeof(int), st, idx, n, e_lo,
                      EL, d, tt, tl);
         if (!dispatched) h->launches++;
@@ -1628,6 +1645,8 @@ int neon_moe_set_option(neon_moe_handle* h, const char* name, int64_t value) {
     } else if (!strcmp(name, "pair_mma")) {
         if (value < 0 || value > 2) return fail(h, NEON_MOE_EINVAL, "pair_mma is 0 (never), 1 (always) or 2 (small passes)");
         h->pair_mma = (int)value;
+    } else if (!strcmp(name, "dispatch_multi")) {
+        h->dispatch_multi = value != 0;
     } else if (!strcmp(name, "pair_prefill")) {
         h->pair_prefill = value != 0;
     } else if (!strcmp(name, "mxf4_prefill")) {

@@ -546,6 +546,34 @@ def test_two_sm_mma_prefill_tiles(full20b_prefill, T):
         layer.set_option("pair_prefill", 1)
 
 
+@pytest.mark.parametrize("T", [257, 700, 4096])
+def test_many_cta_dispatch_equals_one_cta(full20b_prefill, T):
+    """Passes of more than 1024 entries sort their entries on one CTA per 1024 entries (counts per chunk, one
+    scan by the CTA that finishes last, placement by every CTA).  Counts, offsets, the stable permutation and
+    its inverse equal the one-CTA kernel's and the oracle's; outputs are bit-identical."""
+    shape, W, layer = full20b_prefill
+    hidden = synth.make_hidden(T, W, 500 + T)
+    layer.set_option("dispatch_multi", 0)
+    try:
+        ref = run_device(layer, hidden, None)[0]
+        d_ref = layer.read_dispatch()
+        layer.set_option("dispatch_multi", 1)
+        out = run_device(layer, hidden, None)[0]
+        d_new = layer.read_dispatch()
+        for a, b in zip(d_ref, d_new):
+            np.testing.assert_array_equal(a, b)
+        np.testing.assert_array_equal(out, ref)
+        again = run_device(layer, hidden, None)[0]      # the arrival counter was left at zero
+        np.testing.assert_array_equal(again, ref)
+        ridx, _ = oracle.route(hidden, W.router_w, W.router_b, shape.top_k)
+        count, offset, perm, inv = oracle.dispatch(ridx, shape.n_experts)
+        np.testing.assert_array_equal(d_new[0], count)
+        np.testing.assert_array_equal(d_new[2], perm)
+        assert layer.status() == 0
+    finally:
+        layer.set_option("dispatch_multi", 1)
+
+
 def test_two_sm_mma_instruction_self_check():
     """The library's self-check of the two-SM instruction form: M = 256 splits by CTA, the N operand is the
     concatenation of the two CTAs' halves, the multicast commit reaches both CTAs (no timeout)."""

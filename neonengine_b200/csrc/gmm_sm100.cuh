@@ -271,6 +271,7 @@ __global__ void __launch_bounds__(1024) dispatch_count_kernel(const int32_t* __r
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    const int tt = tile_tokens > 0 ? tile_tokens : 1;   // tile_tokens 0: the sort alone, no tile list (the sender's sort of expert parallelism)
     for (int ee = tid; ee < n_local; ee += 1024) {  // totals per expert
         int run = 0;
         for (int bb = 0; bb < nb; ++bb) run += __ldcg(sc.blk_count + (size_t)bb * n_local + ee);
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(1024) dispatch_count_kernel(const int32_t* __r
             const int ee = lane * 8 + j;
             c[j] = ee < n_local ? cnt[ee] : 0;
             csum += c[j];
-            tsum += (c[j] + tile_tokens - 1) / tile_tokens;
+            tsum += (c[j] + tt - 1) / tt;
         }
         int cpre = csum, tpre = tsum;
 #pragma unroll
@@ -304,14 +305,14 @@ __global__ void __launch_bounds__(1024) dispatch_count_kernel(const int32_t* __r
                 sc.tile_first[ee] = trun;
             }
             crun += c[j];
-            trun += (c[j] + tile_tokens - 1) / tile_tokens;
+            trun += (c[j] + tt - 1) / tt;
         }
         if (lane == 31) {
             off[n_local] = cpre;
             first[n_local] = tpre;
             d.offset[n_local] = cpre;
             sc.tile_first[n_local] = tpre;
-            *tl.n_tiles = tpre;
+            if (tile_tokens > 0) *tl.n_tiles = tpre;
         }
     }
     __syncthreads();
@@ -321,12 +322,14 @@ __global__ void __launch_bounds__(1024) dispatch_count_kernel(const int32_t* __r
             sc.blk_base[(size_t)bb * n_local + ee] = run;
             run += __ldcg(sc.blk_count + (size_t)bb * n_local + ee);
         }
-        const int lo = off[ee], c = cnt[ee];
-        int t = first[ee];
-        for (int r = 0; r < c; r += tile_tokens, ++t) {
-            tl.expert[t] = ee;
-            tl.row0[t] = lo + r;
-            tl.rows[t] = min(tile_tokens, c - r);
+        if (tile_tokens > 0) {
+            const int lo = off[ee], c = cnt[ee];
+            int t = first[ee];
+            for (int r = 0; r < c; r += tile_tokens, ++t) {
+                tl.expert[t] = ee;
+                tl.row0[t] = lo + r;
+                tl.rows[t] = min(tile_tokens, c - r);
+            }
         }
     }
     if (tid == 0) *sc.done = 0u;  // ready for the next pass
@@ -346,7 +349,7 @@ __global__ void __launch_bounds__(1024) dispatch_place_kernel(const int32_t* __r
             const int pos = sc.blk_base[(size_t)b * n_local + e] + dsmem[warp * n_local + e] + rank;
             d.perm[pos] = i;
             d.inv[i] = pos;
-            tl.row_tile[pos] = sc.tile_first[e] + (pos - d.offset[e]) / tile_tokens;
+            if (tile_tokens > 0) tl.row_tile[pos] = sc.tile_first[e] + (pos - d.offset[e]) / tile_tokens;
         } else {
             d.inv[i] = -1;
         }

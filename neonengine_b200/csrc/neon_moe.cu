@@ -782,9 +782,10 @@ int neon_moe_create(const neon_moe_config* cfg, neon_moe_handle** out) {
         (rc = dev_alloc(h, &h->n_tiles, (size_t)4)) || (rc = dev_alloc(h, &h->row_tile, n)))
         return bail(rc);
     {   // the many-CTA dispatch of prefill-sized passes: per-chunk expert counts and write positions
-        const size_t blocks = (n + 1023) / 1024;
-        if ((rc = dev_alloc(h, &h->disp_blk_count, blocks * h->n_local)) || (rc = dev_alloc(h, &h->disp_blk_base, blocks * h->n_local)) ||
-            (rc = dev_alloc(h, &h->disp_tile_first, (size_t)h->n_local + 1)) || (rc = dev_alloc(h, &h->disp_done, (size_t)4)))
+        // (sized for all experts: the sender's sort of expert parallelism runs over the global expert ids)
+        const size_t blocks = (std::max(n, (size_t)cfg->max_tokens * cfg->top_k) + 1023) / 1024;
+        if ((rc = dev_alloc(h, &h->disp_blk_count, blocks * cfg->n_experts)) || (rc = dev_alloc(h, &h->disp_blk_base, blocks * cfg->n_experts)) ||
+            (rc = dev_alloc(h, &h->disp_tile_first, (size_t)cfg->n_experts + 1)) || (rc = dev_alloc(h, &h->disp_done, (size_t)4)))
             return bail(rc);
         if (cudaMemset(h->disp_done, 0, 16) != cudaSuccess) return bail(fail(h, NEON_MOE_ECUDA, "cudaMemset failed"));
     }
@@ -1344,8 +1345,17 @@ static int ep_pass(neon_moe_handle* h, const uint16_t* hidden, int T, const floa
     CU(h, cudaEventRecord(h->ep_ev[0], st));
     DispatchArrays sd{h->s_count, h->s_offset, h->s_perm, h->s_inv};
     if (T > 0) launch_router(h, hidden, T, logit_bias, h->s_idx, h->s_w, nullptr, st);
-    dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->s_idx, n, 0, E, sd);
-    h->launches++;
+    if (n > 1024 && h->dispatch_multi && h->path == 2) {  // the sort alone (no tile list), one CTA per 1024 entries
+        const DispatchScratch sc{h->disp_blk_count, h->disp_blk_base, h->disp_tile_first, h->disp_done};
+        const TileList none{};
+        const dim3 grid((n + 1023) / 1024);
+        launch_k(false, dispatch_count_kernel, grid, dim3(1024), (size_t)(32 * E) * sizeof(int), st, (const int32_t*)h->s_idx, n, 0, E, sd, 0, none, sc);
+        launch_k(false, dispatch_place_kernel, grid, dim3(1024), (size_t)(32 * E) * sizeof(int), st, (const int32_t*)h->s_idx, n, 0, E, sd, 0, none, sc);
+        h->launches += 2;
+    } else {
+        dispatch_kernel<<<1, 1024, (size_t)(33 * E) * sizeof(int), st>>>(h->s_idx, n, 0, E, sd);
+        h->launches++;
+    }
     // 2. every rank learns every histogram; sizes are needed on the host to post the exchange
     NC(h, nc.AllGather(h->s_count, h->all_counts_d, (size_t)E, ncclInt32, h->comm, st));
     int32_t* all_counts = h->host_pinned;

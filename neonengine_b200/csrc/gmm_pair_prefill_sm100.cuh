@@ -201,9 +201,6 @@ gmm_pair_prefill_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_c
             const int tile = item / mp_tiles, m = 2 * (item - tile * mp_tiles) + (int)crank;
             const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
             const int b = iter & 1, aph = (iter >> 1) & 1;
-            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * L::kAccCols;
             const int npad = (rows + 7) & ~7;
             // GATE_UP: lanes 0..15 hold gate rows of channels ch, lanes 16..31 their linear rows
             const int ch = 64 * m + 16 * q + (lane & 15);
@@ -225,6 +222,10 @@ gmm_pair_prefill_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_c
                     tok_dst[k] = p.peer.n_ranks ? peer_row(p.peer, ent, p.hidden) : p.y + (size_t)(row0 + tix) * p.hidden;
                 }
             }
+            // (all of the above is independent of the accumulator: fetched before the wait for it)
+            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * L::kAccCols;
 #pragma unroll
             for (int k = 0; k < NW; ++k) {
                 const int jend = min(npad, 32 * (k + 1));

@@ -10,8 +10,10 @@
 //
 // Same data formats, same arithmetic and same epilogues as gmm_bs_kernel<..., STACK = true, KC = 2>
 // (gmm_sm100.cuh); what differs is the synchronisation:
-//   - the leader may issue a stage's MMAs when BOTH CTAs' copies have landed: the peer's MMA warp, which
-//     issues nothing, forwards each "stage full" of its own barrier to the leader's (remote arrive);
+//   - the leader may issue a stage's MMAs when BOTH CTAs' copies have landed: weights and weight scales of
+//     both CTAs report their bytes to the leader's stage barrier; the peer's token rows land on a barrier of
+//     its own, and the peer's MMA warp, which issues nothing, forwards that as a second arrival on the leader's
+//     stage barrier (remote arrive), so the leader waits for ONE barrier per stage;
 //   - MMA completion frees the stage and publishes the accumulator in both CTAs at once
 //     (tcgen05.commit ... multicast::cluster);
 //   - the leader reuses an accumulator buffer when the epilogue warps of both CTAs have read it (the
@@ -117,7 +119,7 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStage);
     uint64_t* empty = full + STAGES_MAX;
-    uint64_t* peer_full = empty + STAGES_MAX;  // leader: the peer CTA's token rows of the stage have landed; peer: its own barrier for them
+    uint64_t* peer_full = empty + STAGES_MAX;  // peer CTA only: its token rows of the stage have landed (forwarded to the leader's stage barrier)
     uint64_t* acc_full = peer_full + STAGES_MAX;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
@@ -130,7 +132,7 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const bool leader = crank == 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], leader ? 2 : 1);  // leader: its own producer's arrival + the peer's "token rows landed"
             mbar_init(&empty[s], 1);
             mbar_init(&peer_full[s], 1);
         }
@@ -216,7 +218,7 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int left = p.n_chunks; left > 0; left -= KC) {
                 const int ok = mbar_wait(&peer_full[s], ph, abort_flag, p.status, 3, kWaitLimitCycles);  // own token rows landed
                 if (!__all_sync(0xffffffffu, ok)) goto done;
-                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&peer_full[s]), 0));
+                if (lane == 0) mbar_arrive_cluster(full_leader + s * 8);  // the second arrival of the leader's stage barrier
                 __syncwarp();
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
@@ -233,8 +235,12 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tc_copy_sf_pair(tmem_base + SF_UNIT + 4, make_sf_desc(smem_u32(unit_atom)));
         }
         __syncwarp();
+        // the next item's row count is fetched one item ahead: a dependent global load at every item boundary cost
+        // the issuing warp 400-1300 clocks per item (12 stages of ~600)
+        int next_rows = pair < n_items ? p.tile_rows[pair / mp_tiles] : 0;
         for (int item = pair; item < n_items; item += n_pairs, ++iter) {
-            const int tile = item / mp_tiles, rows = p.tile_rows[tile];
+            const int rows = next_rows;
+            if (item + n_pairs < n_items) next_rows = p.tile_rows[(item + n_pairs) / mp_tiles];
             const int npad = (rows + 7) & ~7;
             const uint32_t idesc0 = make_idesc_bs_m(5, 0, 256, (uint32_t)(TERMS * npad), 0, 0);
             const int b = iter & 1, aph = (iter >> 1) & 1;
@@ -252,7 +258,6 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #ifdef NEON_MOE_INSTRUMENT
                 if (tracing) p.trace[ctr * 4 + 1] = clock64();
 #endif
-                ok = ok && mbar_wait_cluster(&peer_full[s], ph, abort_flag, p.status, 11, kWaitLimitCycles);
                 if (!__all_sync(0xffffffffu, ok)) goto done;
 #ifdef NEON_MOE_INSTRUMENT
                 if (tracing) p.trace[ctr * 4 + 2] = clock64();
@@ -295,9 +300,8 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int tile = item / mp_tiles, m = 2 * (item - tile * mp_tiles) + (int)crank;
             const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
             const int b = iter & 1, aph = (iter >> 1) & 1;
-            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * L::kAccCols;
+            // everything that does not depend on the accumulator is fetched BEFORE the wait for it (two rounds of
+            // dependent global loads otherwise sit between "accumulator ready" and "buffer returned")
             const int npad = (rows + 7) & ~7;
             const int ch = 64 * m + 16 * q + (lane & 15);
             const int row = 128 * m + 32 * q + lane;
@@ -314,6 +318,9 @@ gmm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     tok_dst = p.peer.n_ranks ? peer_row(p.peer, ent, p.hidden) : p.y + (size_t)(row0 + lane) * p.hidden;
                 }
             }
+            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * L::kAccCols;
             float vals[BN_MAX];
 #pragma unroll
             for (int j8 = 0; j8 < BN_MAX; j8 += 8) {

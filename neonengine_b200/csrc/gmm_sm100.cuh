@@ -1111,9 +1111,6 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             const int tile = item / p.m_tiles, m = item % p.m_tiles;
             const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
             const int b = iter & 1, aph = (iter >> 1) & 1;
-            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * L::kAccCols;
             const int npad = (rows + 7) & ~7;
             // GATE_UP: lanes 0..15 hold gate rows of channels ch, lanes 16..31 their linear rows
             const int ch = 64 * m + 16 * q + (lane & 15);
@@ -1140,6 +1137,11 @@ gmm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     tok_dst[k] = p.peer.n_ranks ? peer_row(p.peer, ent, p.hidden) : p.y + (size_t)(row0 + tix) * p.hidden;
                 }
             }
+            // everything above is independent of the accumulator and was fetched before the wait for it: the dependent
+            // global loads no longer sit between "accumulator ready" and "buffer returned"
+            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 4, kWaitLimitCycles)) goto done;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * L::kAccCols;
             // one token's value of this lane's row: bias, then SwiGLU (gate_up) or the routing weight (down)
             auto finish = [&](int tix, float acc, float w_tok, float* dst) {
                 const int pos = row0 + tix;

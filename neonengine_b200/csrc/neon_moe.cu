@@ -98,8 +98,9 @@ struct neon_moe_handle {
     int pair_ctas = 0;            // CTAs the paired kernel was last launched with (2 x resident clusters)
     // Decode tiles (16 / 32 tokens) on clusters of two CTAs with two-SM MMAs (tcgen05 cta_group::2): 0 never, 1 always,
     // 2 when the pass routes at most kPairMaxEntries entries.  Measured per pass at the gpt-oss shapes, single vs paired
-    // (Zipf / uniform routing): T=8 58.5 vs 56.6 / 79.3 vs 75.6 us, T=16 72.2 vs 68.6 / 94.2 vs 91.0, T=64 107.9 vs 103.1 /
-    // 115.8 vs 112.3, T=96 120.7 vs 118.2 / 118.9 vs 118.0, T=128 131.0 vs 131.3 / 123.6 vs 129.4, T=256 190 vs 193 / 180 vs 194.
+    // (Zipf / uniform routing): T=8 58.8 vs 53.7 / 79.6 vs 72.5 us, T=16 72.7 vs 66.0 / 94.6 vs 87.8, T=64 108.7 vs 99.8 /
+    // 116.4 vs 109.0, T=96 121.3 vs 114.4 / 119.5 vs 114.3, T=128 131.7 vs 126.1 / 124.3 vs 124.3, T=160 150.6 vs 147.7 /
+    // 133.6 vs 137.2, T=224 175 vs 177.5 / 160 vs 168.
     int pair_mma = 2;
     int pair_prefill = 1;         // 128-token tiles on CTA pairs (two-SM MMAs, each CTA half of the token rows); 0 = one CTA per tile
     int pass_entries = 0;         // routed entries of the pass being launched
@@ -510,7 +511,7 @@ int launch_gmm_pair_prefill(neon_moe_handle* h, const CUtensorMap& tm1, GmmParam
 // 5e-3).  The decode tiles keep four: they are bound by the weight stream, not by tensor work.
 constexpr int kDownTermsPrefill = 3;
 constexpr int kDecodeSmemBytes = 227 * 1024;  // everything an SM has: what the token-operand tiles leave goes to weight stages
-constexpr int kPairMaxEntries = 96 * 4;  // passes of up to 96 tokens at top-4 take the paired kernel
+constexpr int kPairMaxEntries = 128 * 4;  // passes of up to 128 tokens at top-4 take the paired kernel
 constexpr int kMx4Terms = 6;  // e2m1 terms per activation value on the packed 4-bit path
 
 template <int TERMS, bool GATE_UP>

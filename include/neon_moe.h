@@ -256,7 +256,7 @@ int neon_moe_status(neon_moe_handle* h, int* device_status_word);
  * quantisation to accumulation noise.
  * "pair_mma" (default 2): decode-sized tiles (16 / 32 tokens) on clusters of two CTAs whose leader issues two-SM
  * MMAs (tcgen05 cta_group::2, 256 weight rows per instruction): 0 never, 1 always, 2 for passes that route at
- * most 384 entries (96 tokens at top-4), where it measured 1-5 % faster per pass; results are bit-identical to
+ * most 512 entries (128 tokens at top-4), where it measured 3-9 % faster per pass; results are bit-identical to
  * the one-CTA kernel's.
  * "dispatch_multi" (default 1): passes of more than 1024 (token, slot) entries sort them on one CTA per 1024
  * entries (two launches) instead of one CTA for all; identical arrays.
